@@ -1,0 +1,410 @@
+#!/usr/bin/env python
+"""Benchmark of the CSR SpMV / SpMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload NAME] [--variant auto|binned|merge] [--scale F]
+
+One step = one y = alpha*A*x + beta*y (or Y = alpha*A*X + beta*Y) over the whole matrix.
+Default workload: fp32 CSR SpMV on a 4,194,304-row matrix with Poisson(16) row lengths and
+uniform random columns, alpha=1.5, beta=0.5 (per GPU; with N GPUs every rank owns such a
+row shard of an N-times taller matrix, x is replicated, y stays sharded: weak scaling).
+The metric is effective HBM GB/s on the algorithmic bytes
+    nnz*(sizeof(val)+4) + (rows+1)*sizeof(offset) + cols*sizeof(val) + rows*sizeof(val)*(1+[beta!=0])
+(SpMM: the A terms + cols*N*sizeof(B) + rows*N*sizeof(C)*(1+[beta!=0])).
+
+Rank 0 prints one JSON line.  `--impl reference` times the reference's own CPU code
+(oracle/_ref, or the C restatement when that library is absent) on the same configuration.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (kind, description)
+    "spmv_poisson16_f32": "CSR SpMV fp32, 4,194,304 rows, row length ~ Poisson(16), uniform columns, alpha=1.5 beta=0.5",
+    "spmv_rmat22_f32": "CSR SpMV fp32, R-MAT scale 22 edge factor 16 (0.57,0.19,0.19,0.05), alpha=1 beta=0",
+    "spmv_lap2d256_f64": "CSR SpMV fp64, 5-point Laplacian 256x256, alpha=1 beta=0",
+    "spmv_lap3d_f64_i64": "CSR SpMV fp64, 7-point Laplacian n^3 (n=512 at scale 1), int64 offsets, alpha=1 beta=0",
+    "spmm_s27_128_f32_n8": "CSR SpMM fp32, 27-point stencil 128^3, N=8",
+    "spmm_s27_128_f32_n32": "CSR SpMM fp32, 27-point stencil 128^3, N=32",
+    "spmm_s27_128_f32_n128": "CSR SpMM fp32, 27-point stencil 128^3, N=128",
+    "spmm_s27_128_bf16_n128": "CSR SpMM bf16 operands / fp32 accumulate (tcgen05), 27-point stencil 128^3, N=128",
+}
+DEFAULT_WORKLOAD = "spmv_poisson16_f32"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--variant", default="auto", choices=["auto", "binned", "merge"])
+    ap.add_argument("--scale", type=float, default=1.0,
+                    help="shrink the workload's row count by this factor (for profiler captures)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def make_workload(name, device, rank, scale):
+    """Returns dict(A=Csr, kind, n, alpha, beta, x_lo, dtype) for this rank's shard."""
+    import torch
+    from library_b200 import generators as G
+    seed = 1000 * rank
+    if name == "spmv_poisson16_f32":
+        rows = max(1024, int(4194304 * scale))
+        A = G.poisson_random(rows, rows, 16.0, dtype=torch.float32, device=device, seed=2 + seed)
+        return dict(A=A, kind="spmv", n=1, alpha=1.5, beta=0.5, lo=-1.0, dtype=torch.float32)
+    if name == "spmv_rmat22_f32":
+        sc = 22 + int(round(__import__("math").log2(scale))) if scale != 1.0 else 22
+        A = G.rmat(sc, 16, dtype=torch.float32, device=device, seed=3 + seed)
+        return dict(A=A, kind="spmv", n=1, alpha=1.0, beta=0.0, lo=0.0, dtype=torch.float32)
+    if name == "spmv_lap2d256_f64":
+        A = G.laplacian_2d_5pt(256, dtype=torch.float64, device=device)
+        return dict(A=A, kind="spmv", n=1, alpha=1.0, beta=0.0, lo=-1.0, dtype=torch.float64)
+    if name == "spmv_lap3d_f64_i64":
+        n = max(16, int(round(512 * scale ** (1.0 / 3.0))))
+        A = G.laplacian_3d_7pt(n, dtype=torch.float64, device=device, index64=True)
+        return dict(A=A, kind="spmv", n=1, alpha=1.0, beta=0.0, lo=-1.0, dtype=torch.float64)
+    if name.startswith("spmm_s27_128"):
+        n = int(name.rsplit("_n", 1)[1])
+        g = max(8, int(round(128 * scale ** (1.0 / 3.0))))
+        bf16 = "bf16" in name
+        A = G.stencil_3d_27pt(g, dtype=torch.float32, device=device, seed=4 + seed)
+        if bf16:
+            A.val = A.val.to(torch.bfloat16)
+        return dict(A=A, kind="spmm", n=n, alpha=1.0, beta=0.0, lo=-1.0,
+                    dtype=torch.bfloat16 if bf16 else torch.float32)
+    raise KeyError(name)
+
+
+def algorithmic_bytes(w):
+    from library_b200 import generators as G
+    A = w["A"]
+    vb = A.val.element_size()
+    ob = A.row_ptr.element_size()
+    if w["kind"] == "spmv":
+        return G.spmv_bytes(A.rows, A.cols, A.nnz, vb, ob, w["beta"] != 0)
+    yb = 4 if vb == 2 else vb
+    return G.spmm_bytes(A.rows, A.cols, A.nnz, w["n"], vb, ob, vb, yb, w["beta"] != 0)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self.stop = index, [], threading.Event()
+        self.th = threading.Thread(target=self._run, daemon=True)
+
+    def _once(self):
+        try:
+            out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                  "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+            f = [s.strip() for s in out.strip().split(",")]
+            if len(f) >= 7:
+                self.samples.append(f)
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self.stop.is_set():
+            self._once()
+            self.stop.wait(0.05)
+
+    def __enter__(self):
+        self.th.start()
+        return self
+
+    def __exit__(self, *a):
+        self.stop.set()
+        self.th.join(timeout=6)
+        if not self.samples:
+            self._once()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[3 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": float(self.samples[0][1]) if self.samples[0][1].replace(".", "").isdigit() else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def cpu_reference_time(w, repeats, threads):
+    """Per-call seconds of the reference's CPU code (or the C restatement) on host arrays."""
+    import numpy as np
+    import oracle
+    import torch
+    from library_b200 import generators as G
+    A = w["A"]
+    rp, ci = A.row_ptr.cpu().numpy(), A.col_idx.cpu().numpy()
+    ddt = torch.float32 if w["dtype"] == torch.bfloat16 else w["dtype"]
+    v = A.val.to(ddt).cpu().numpy()   # bf16 operands are timed as the fp32 CPU kernel
+    kind = "reference" if (oracle.have_ref() and rp.dtype == np.int32) else "port"
+    if w["kind"] == "spmv":
+        x = G.uniform((A.cols,), w["lo"], 1.0, dtype=ddt, seed=11).numpy()
+        y0 = G.uniform((A.rows,), -1.0, 1.0, dtype=ddt, seed=12).numpy()
+        if kind == "reference":
+            oracle.ref_set_threads(threads)
+            _, t = oracle.ref_spmv(rp, ci, v, x, w["alpha"], w["beta"], y0, repeats=repeats + 1)
+            return list(t[1:]), kind
+        os.environ["OMP_NUM_THREADS"] = str(threads)
+        ts = []
+        for _ in range(repeats + 1):
+            t0 = time.perf_counter()
+            oracle.spmv(rp, ci, v, x, w["alpha"], w["beta"], y0)
+            ts.append(time.perf_counter() - t0)
+        return ts[1:], kind
+    X = G.uniform((A.cols, w["n"]), w["lo"], 1.0, dtype=ddt, seed=11).numpy()
+    if kind == "reference":
+        oracle.ref_set_threads(threads)
+        _, t = oracle.ref_spmm(rp, ci, v, X, w["alpha"], w["beta"], None, repeats=repeats + 1)
+        return list(t[1:]), kind
+    ts = []
+    for _ in range(repeats + 1):
+        t0 = time.perf_counter()
+        oracle.spmm(rp, ci, v, X, w["alpha"], w["beta"])
+        ts.append(time.perf_counter() - t0)
+    return ts[1:], kind
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = make_workload(args.workload, "cpu", 0, args.scale)
+    nbytes = algorithmic_bytes(w)
+    cores = host_cores()
+    steps = max(1, min(args.steps, 20))
+    ts, kind = cpu_reference_time(w, steps + min(args.warmup, 2), cores)
+    ts = ts[min(args.warmup, 2):] or ts
+    sec = statistics.median(ts)
+    val = nbytes / sec / 1e9
+    A = w["A"]
+    flops = 2.0 * A.nnz * w["n"]
+    line = {
+        "impl": "reference", "metric": "effective HBM GB/s on algorithmic bytes (CSR SpMV/SpMM)",
+        "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": len(ts), "warmup": min(args.warmup, 2),
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": {4: "f32", 8: "f64", 2: "f32"}[A.val.element_size()], "data": "synthetic",
+        "gflops": flops / sec / 1e9,
+        "config": {"workload": args.workload, "description": WORKLOADS[args.workload], "rows": A.rows,
+                   "cols": A.cols, "nnz": A.nnz, "n": w["n"], "algorithmic_bytes": nbytes},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": kind,
+                         "sample": f"full matrix, {len(ts)} calls, median"},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from library_b200 import api
+    from library_b200 import generators as G
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.variant != "auto":
+        os.environ["ASP_SPMV_VARIANT"] = args.variant
+
+    w = make_workload(args.workload, dev, rank, args.scale)
+    A = w["A"]
+    nbytes = algorithmic_bytes(w)
+    h = api.Handle()
+    stream = torch.cuda.Stream()
+    h.set_stream(stream.cuda_stream)
+    Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr, A.col_idx, A.val)
+    ydt = torch.float32 if w["dtype"] == torch.bfloat16 else w["dtype"]
+
+    # x lives on rank 0 and is replicated over NVLink once: it is constant across the repeats
+    if w["kind"] == "spmv":
+        x = G.uniform((A.cols,), w["lo"], 1.0, dtype=w["dtype"], device=dev, seed=11)
+        y = G.uniform((A.rows,), -1.0, 1.0, dtype=ydt, device=dev, seed=12 + rank)
+    else:
+        x = G.uniform((A.cols, w["n"]), w["lo"], 1.0, dtype=w["dtype"], device=dev, seed=11)
+        y = torch.zeros((A.rows, w["n"]), dtype=ydt, device=dev)
+    if world > 1:
+        dist.broadcast(x, src=0)
+    torch.cuda.synchronize()
+
+    if w["kind"] == "spmv":
+        xd, yd = api.DnVec(x), api.DnVec(y)
+        buf = torch.empty(api.spmv_buffer_size(h, Am, xd, yd, w["alpha"], w["beta"]), dtype=torch.uint8, device=dev)
+        with torch.cuda.stream(stream):
+            Am.analyse(h)
+
+        def step():
+            api.spmv(h, Am, xd, yd, w["alpha"], w["beta"], buffer=buf)
+    else:
+        xd, yd = api.DnMat(x), api.DnMat(y)
+        with torch.cuda.stream(stream):
+            api.spmm_preprocess(h, Am, xd, yd)
+
+        def step():
+            api.spmm(h, Am, xd, yd, w["alpha"], w["beta"])
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # beta != 0 makes y drift over repeats; keep it bounded by restoring between phases
+    y_init = y.clone()
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    y.copy_(y_init)
+    barrier()
+    l0 = h.launches
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        ev0.record(stream)
+        for _ in range(args.steps):
+            step()
+        ev1.record(stream)
+        barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = h.launches - l0
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    tot = torch.tensor([float(nbytes), 2.0 * A.nnz * w["n"], float(A.rows), float(A.nnz)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+    ms = float(t.item())
+    ms_step = ms / args.steps
+    total_bytes, total_flops = float(tot[0]), float(tot[1])
+    value = total_bytes / (ms_step * 1e-3) / 1e9
+
+    # end to end through the public call with HOST buffers: H2D of the step's dense inputs from
+    # pinned memory (on rank 0, then the NVLink broadcast), the call, D2H of the result
+    e2e = None
+    if not args.no_e2e:
+        hx = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
+        hx.copy_(x)
+        hy_in = torch.empty(y.shape, dtype=y.dtype, pin_memory=True)
+        hy_in.copy_(y_init)
+        hy_out = torch.empty(y.shape, dtype=y.dtype, pin_memory=True)
+        reads_y = w["beta"] != 0
+
+        def e2e_step():
+            with torch.cuda.stream(stream):
+                if rank == 0 or world == 1:
+                    x.copy_(hx, non_blocking=True)
+                if world > 1:
+                    dist.broadcast(x, src=0)
+                if reads_y:
+                    y.copy_(hy_in, non_blocking=True)
+                step()
+                hy_out.copy_(y, non_blocking=True)
+        e_steps = max(3, min(args.steps, 20))
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(e_steps):
+            e2e_step()
+        e1.record(stream)
+        barrier()
+        et = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(et, op=dist.ReduceOp.MAX)
+        e_ms = float(et.item()) / e_steps
+        h2d = x.numel() * x.element_size() + (y.numel() * y.element_size() if reads_y else 0)
+        e2e = {"value": total_bytes / (e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e_ms,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": y.numel() * y.element_size(),
+               "note": "A resident in HBM (like the reference's created matrix handle); x (+y when beta!=0) from "
+                       "pinned host memory each step, y back to the host each step"}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            cores = host_cores()
+            reps = 10 if A.nnz > 10_000_000 else 50
+            ts, kind = cpu_reference_time(w, reps, cores)
+            sec = statistics.median(ts)
+            cpu = {"value": nbytes / sec / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
+                   "ms_per_step": sec * 1e3, "sample": f"the same matrix in full, {len(ts)} calls after 1 warm-up, median"}
+        except Exception as ex:  # the baseline must not take the bench line down with it
+            cpu = {"value": None, "unit": "GB/s", "cores": host_cores(), "kind": "port", "sample": f"failed: {ex}"}
+
+    if rank == 0:
+        peak, peak_src = measured_peak()
+        per_launch_ms = ms_step  # one call = one dominant kernel (+ a <1% carry fix-up for merge-path)
+        ach = nbytes / (per_launch_ms * 1e-3) / 1e9 if world == 1 else (total_bytes / world) / (per_launch_ms * 1e-3) / 1e9
+        variant = Am.last_variant() if w["kind"] == "spmv" else "rowblock"
+        line = {
+            "metric": "effective HBM GB/s on algorithmic bytes (CSR SpMV/SpMM)",
+            "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": {torch.float32: "f32", torch.float64: "f64", torch.bfloat16: "bf16"}[w["dtype"]],
+            "data": "synthetic", "gflops": total_flops / (ms_step * 1e-3) / 1e9,
+            "frac_of_nominal_8TBs": value / world / 8000.0,
+            "config": {"workload": args.workload, "description": WORKLOADS[args.workload],
+                       "rows_per_gpu": A.rows, "cols": A.cols, "nnz_per_gpu": A.nnz, "n": w["n"],
+                       "alpha": w["alpha"], "beta": w["beta"], "variant": variant,
+                       "algorithmic_bytes_per_gpu": nbytes, "l2": "inputs larger than L2 (126 MB), no flush"
+                       if nbytes > 126e6 else "L2-resident workload, no flush (the configuration is smaller than L2)",
+                       "sharding": "rows, nnz-balanced shards, x replicated by NCCL broadcast, y sharded"},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                         "peak_source": peak_src, "traffic": None},
+            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,360 @@
+/* alphasparse_b200.h - C ABI of the Blackwell (sm_100a) CSR SpMV / SpMM library.
+ *
+ * Every entry point is extern "C" with plain pointers and sizes.  Names, argument order,
+ * argument meaning and enum values are those of the AlphaSparse generic API for this path,
+ * so a caller of the reference recompiles against this header.  Each declaration cites the
+ * reference interface it replaces (path within the reference project : line).
+ *
+ * Conventions shared by all entry points
+ *   - descriptors capture caller-owned DEVICE pointers (no copy, never freed here);
+ *   - alpha / beta are HOST pointers to a value of the compute type, read synchronously;
+ *   - work is stream-ordered on handle->stream; SpMV / SpMM do not synchronise and do not
+ *     allocate once the matrix has been analysed (alphasparseSpMV_analysis /
+ *     alphasparseSpMM_preprocess; otherwise the first call analyses, which allocates the
+ *     plan with cudaMalloc and synchronises once);
+ *   - errors come back as alphasparseStatus_t, nothing is printed, nothing exits;
+ *   - beta == 0 means y / Y is written without being read.
+ * Not supported (ALPHA_SPARSE_STATUS_NOT_SUPPORTED): transposed A or B, index base one,
+ * formats other than CSR, column-major dense operands, value types other than
+ * fp32 / fp64 (and bf16 A,X with fp32 Y for SpMM).  There is no CPU fallback.
+ */
+#ifndef ALPHASPARSE_B200_H
+#define ALPHASPARSE_B200_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <cuda_runtime_api.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- enums: values identical to include/alphasparse/spdef.h ------------------------- */
+typedef enum { /* spdef.h:10-22 */
+  ALPHA_SPARSE_STATUS_SUCCESS = 0,
+  ALPHA_SPARSE_STATUS_NOT_INITIALIZED = 1,
+  ALPHA_SPARSE_STATUS_ALLOC_FAILED = 2,
+  ALPHA_SPARSE_STATUS_INVALID_VALUE = 3,
+  ALPHA_SPARSE_STATUS_EXECUTION_FAILED = 4,
+  ALPHA_SPARSE_STATUS_INTERNAL_ERROR = 5,
+  ALPHA_SPARSE_STATUS_NOT_SUPPORTED = 6,
+  ALPHA_SPARSE_STATUS_INVALID_POINTER = 7,
+  ALPHA_SPARSE_STATUS_INVALID_HANDLE = 8,
+  ALPHA_SPARSE_STATUS_INVALID_KERNEL_PARAM = 9,
+  ALPHA_SPARSE_STATUS_INVALID_SIZE = 10
+} alphasparseStatus_t;
+
+typedef enum { /* spdef.h:25-29 */
+  ALPHA_SPARSE_OPERATION_NON_TRANSPOSE = 0,
+  ALPHA_SPARSE_OPERATION_TRANSPOSE = 1,
+  ALPHA_SPARSE_OPERATION_CONJUGATE_TRANSPOSE = 2
+} alphasparseOperation_t;
+
+typedef enum { /* spdef.h:48-51 */
+  ALPHA_SPARSE_INDEX_BASE_ZERO = 0,
+  ALPHA_SPARSE_INDEX_BASE_ONE = 1
+} alphasparseIndexBase_t;
+
+typedef enum { /* spdef.h:83-86 */
+  ALPHASPARSE_ORDER_ROW = 0,
+  ALPHASPARSE_ORDER_COL = 1
+} alphasparseOrder_t;
+
+typedef enum { /* spdef.h:125-140 (only CSR is accepted on this path) */
+  ALPHA_SPARSE_FORMAT_COO = 0,
+  ALPHA_SPARSE_FORMAT_CSR = 1,
+  ALPHA_SPARSE_FORMAT_CSC = 2
+} alphasparseFormat_t;
+
+typedef enum { /* spdef.h:144-155 */
+  ALPHA_R_32F = 0,
+  ALPHA_R_64F = 1,
+  ALPHA_C_32F = 2,
+  ALPHA_C_64F = 3,
+  ALPHA_R_16F = 4,
+  ALPHA_R_16BF = 5,
+  ALPHA_C_16F = 6,
+  ALPHA_C_16BF = 7,
+  ALPHA_R_8I = 8,
+  ALPHA_R_32I = 9
+} alphasparseDataType;
+
+typedef enum { /* spdef.h:299-302 */
+  ALPHA_SPARSE_POINTER_MODE_HOST = 0,
+  ALPHA_SPARSE_POINTER_MODE_DVICE = 1
+} alphasparse_pointer_mode_t;
+
+typedef enum { /* spdef.h:304-308 */
+  ALPHA_SPARSE_LAYER_MODE_NONE = 0,
+  ALPHA_SPARSE_LAYER_MODE_LOG_TRACE = 1,
+  ALPHA_SPARSE_LAYER_MODE_LOG_BENCH = 2
+} alphasparse_layer_mode_t;
+
+typedef enum { /* spdef.h:310-314 */
+  ALPHA_SPARSE_INDEXTYPE_U16 = 1,
+  ALPHA_SPARSE_INDEXTYPE_I32 = 2,
+  ALPHA_SPARSE_INDEXTYPE_I64 = 3
+} alphasparseIndexType_t;
+
+/* spdef.h:345-365.  How this library maps them: DEFAULT picks from the analysed row-length
+ * statistics; SCALAR / VECTOR / ADAPTIVE / CSR_ADAPTIVE / LINE* select the row-length-binned
+ * kernel; MERGE / ROW_PARTITION / LOAD_BALANCE / FLAT* / CSR_STREAM select the merge-path
+ * kernel.  COO and ELL are other formats' algorithms and are rejected for CSR. */
+typedef enum {
+  ALPHA_SPARSE_SPMV_ALG_DEFAULT = 0,
+  ALPHA_SPARSE_SPMV_ALG_COO = 1,
+  ALPHA_SPARSE_SPMV_ALG_CSR_ADAPTIVE = 2,
+  ALPHA_SPARSE_SPMV_ALG_CSR_STREAM = 3,
+  ALPHA_SPARSE_SPMV_ALG_ELL = 4,
+  ALPHA_SPARSE_SPMV_ALG_SCALAR = 5,
+  ALPHA_SPARSE_SPMV_ALG_VECTOR = 6,
+  ALPHA_SPARSE_SPMV_ROW_PARTITION = 7,
+  ALPHA_SPARSE_SPMV_ADAPTIVE = 8,
+  ALPHA_SPARSE_SPMV_ALG_MERGE = 9,
+  ALPHA_SPARSE_SPMV_ALG_LINE = 10,
+  ALPHA_SPARSE_SPMV_ALG_FLAT1 = 11,
+  ALPHA_SPARSE_SPMV_ALG_FLAT4 = 12,
+  ALPHA_SPARSE_SPMV_ALG_FLAT8 = 13,
+  ALPHA_SPARSE_SPMV_ALG_ACC = 14,
+  ALPHA_SPARSE_SPMV_ALG_FLAT = 15,
+  ALPHA_SPARSE_SPMV_ALG_LINE_ENHANCE = 16,
+  ALPHA_SPARSE_SPMV_ALG_LOAD_BALANCE = 17,
+  ALPHA_SPARSE_SPMV_ALG_PFLAT = 18
+} alphasparseSpMVAlg_t;
+
+/* spdef.h:390-402.  DEFAULT picks per (N, row statistics); CSR_ALG1..5 select the SIMT
+ * row-block kernel; CSR_ALG6 (the matrix-unit algorithm of the HIP backend,
+ * hip/kernel/level3/alphasparse_spmm_tc4csr.h:228-255) selects the tcgen05 kernel and needs
+ * bf16 A and X with fp32 Y.  COO algorithms are rejected for CSR. */
+typedef enum {
+  ALPHASPARSE_SPMM_ALG_DEFAULT = 0,
+  ALPHASPARSE_SPMM_COO_ALG1 = 1,
+  ALPHASPARSE_SPMM_COO_ALG2 = 2,
+  ALPHASPARSE_SPMM_COO_ALG3 = 3,
+  ALPHASPARSE_SPMM_COO_ALG4 = 4,
+  ALPHASPARSE_SPMM_CSR_ALG1 = 5,
+  ALPHASPARSE_SPMM_CSR_ALG2 = 6,
+  ALPHASPARSE_SPMM_CSR_ALG3 = 7,
+  ALPHASPARSE_SPMM_CSR_ALG4 = 8,
+  ALPHASPARSE_SPMM_CSR_ALG5 = 9,
+  ALPHASPARSE_SPMM_CSR_ALG6 = 10
+} alphasparseSpMMAlg_t;
+
+/* ---- handle: include/alphasparse/handle.h:26-85 ------------------------------------- *
+ * Public like the reference's (its callers assign handle->stream directly, there is no
+ * setter); `stream` is honoured by every launch.  `impl` is private to the library.      */
+typedef struct alphasparse_handle_s {
+  int device;          /* the device that was current at creation (the reference hard-codes 0) */
+  int wavefront_size;  /* 32 */
+  int asic_rev;
+  cudaStream_t stream;
+  cudaStream_t streams[6];
+  alphasparse_pointer_mode_t pointer_mode; /* HOST only */
+  alphasparse_layer_mode_t layer_mode;
+  size_t buffer_size;
+  void* buffer;
+  float* sone;
+  double* done;
+  bool check_flag;
+  int* process;
+  void* pflat_analysis_data;
+  void* impl;
+} alphasparse_handle;
+typedef alphasparse_handle* alphasparseHandle_t;
+
+/* ---- descriptors: include/alphasparse/handle.h:395-435, 478-499 --------------------- */
+struct _alphasparseSpMatDescr {
+  bool init;
+  bool analysed;       /* true once a plan (row bins + merge-path partition) is attached */
+  int64_t rows, cols, nnz;
+  int64_t nwarps;
+  int* row_data;       /* set when row_type is I32 (reference field) */
+  int* col_data;
+  int* ind_data;
+  void* val_data;
+  const int* const_row_data;
+  const int* const_col_data;
+  const int* const_ind_data;
+  const void* const_val_data;
+  alphasparseIndexType_t row_type, col_type;
+  alphasparseDataType data_type;
+  alphasparseIndexBase_t idx_base;
+  alphasparseFormat_t format;
+  void* descr;
+  void* info;          /* the analysis plan, owned by the descriptor */
+  const void* row_offsets; /* row offsets of either width (I32 or I64); extension */
+  int64_t batch_count, batch_stride, offsets_batch_stride, columns_values_batch_stride;
+};
+struct _alphasparse_dnvec_descr {
+  bool init;
+  int64_t size;
+  void* values;
+  alphasparseDataType data_type;
+};
+struct _alphasparse_dnmat_descr {
+  bool init;
+  int64_t rows, cols, ld;
+  void* values;
+  alphasparseDataType data_type;
+  alphasparseOrder_t order;
+};
+typedef struct _alphasparseSpMatDescr* alphasparseSpMatDescr_t;
+typedef struct _alphasparse_dnvec_descr* alphasparseDnVecDescr_t;
+typedef struct _alphasparse_dnmat_descr* alphasparseDnMatDescr_t;
+
+/* ---- handle and stream -------------------------------------------------------------- */
+/* handle.h:520-524; cuda/util/handle.cu:52-73 (initHandle), :75-156 (alphasparseGetHandle),
+ * :161-175 (alphasparse_destory_handle, spelling kept). */
+alphasparseStatus_t initHandle(alphasparseHandle_t* handle);
+alphasparseStatus_t alphasparseGetHandle(alphasparseHandle_t* handle);
+alphasparseStatus_t alphasparse_destory_handle(alphasparseHandle_t handle);
+/* Extension: the reference has no accessor, callers write handle->stream (handle.h:37). */
+alphasparseStatus_t alphasparseSetStream(alphasparseHandle_t handle, cudaStream_t stream);
+alphasparseStatus_t alphasparseGetStream(alphasparseHandle_t handle, cudaStream_t* stream);
+
+/* ---- descriptors -------------------------------------------------------------------- */
+/* cuda/format/alphasparse_create_csr.h:6-63 is a header template with int sizes and int
+ * pointers; this is the C form with 64-bit sizes and void pointers.  Row offsets may be
+ * I32 or I64, column indices I32.  Pointer capture only. */
+alphasparseStatus_t alphasparseCreateCsr(alphasparseSpMatDescr_t* spMatDescr, int64_t rows,
+                                         int64_t cols, int64_t nnz, void* csrRowOffsets,
+                                         void* csrColInd, void* csrValues,
+                                         alphasparseIndexType_t csrRowOffsetsType,
+                                         alphasparseIndexType_t csrColIndType,
+                                         alphasparseIndexBase_t idxBase,
+                                         alphasparseDataType valueType);
+/* handle.h:593-597; cuda/util/handle.cu:657-693 */
+alphasparseStatus_t alphasparseCreateDnVec(alphasparseDnVecDescr_t* descr, int64_t size,
+                                           void* values, alphasparseDataType data_type);
+/* handle.h:599-606; cuda/util/handle.cu:696-738 */
+alphasparseStatus_t alphasparseCreateDnMat(alphasparseDnMatDescr_t* dnMatDescr, int64_t rows,
+                                           int64_t cols, int64_t ld, void* values,
+                                           alphasparseDataType valueType,
+                                           alphasparseOrder_t order);
+/* Extensions: the reference never frees its descriptors. */
+alphasparseStatus_t alphasparseDestroySpMat(alphasparseSpMatDescr_t spMatDescr);
+alphasparseStatus_t alphasparseDestroyDnVec(alphasparseDnVecDescr_t descr);
+alphasparseStatus_t alphasparseDestroyDnMat(alphasparseDnMatDescr_t descr);
+/* Re-point a dense descriptor without re-creating it (cuSPARSE-style; extension). */
+alphasparseStatus_t alphasparseDnVecSetValues(alphasparseDnVecDescr_t descr, void* values);
+alphasparseStatus_t alphasparseDnMatSetValues(alphasparseDnMatDescr_t descr, void* values);
+
+/* ---- SpMV: y = alpha*op(A)*x + beta*y ----------------------------------------------- */
+/* spapi.h:6895-6905; cuda/kernel/level2/alphasparse_spmv.cu:221-339 */
+alphasparseStatus_t alphasparseSpMV(alphasparseHandle_t handle, alphasparseOperation_t opA,
+                                    const void* alpha, alphasparseSpMatDescr_t matA,
+                                    alphasparseDnVecDescr_t vecX, const void* beta,
+                                    alphasparseDnVecDescr_t vecY,
+                                    alphasparseDataType computeType, alphasparseSpMVAlg_t alg,
+                                    void* externalBuffer);
+/* spapi.h:6907-6917; cuda/kernel/level2/alphasparse_spmv.cu:341-421.  The size covers the
+ * per-tile carry array of the merge-path kernel for this matrix, for any alg. */
+alphasparseStatus_t alphasparseSpMV_bufferSize(alphasparseHandle_t handle,
+                                               alphasparseOperation_t opA, const void* alpha,
+                                               alphasparseSpMatDescr_t matA,
+                                               alphasparseDnVecDescr_t vecX, const void* beta,
+                                               alphasparseDnVecDescr_t vecY,
+                                               alphasparseDataType computeType,
+                                               alphasparseSpMVAlg_t alg, size_t* bufferSize);
+/* spapi.h:6919-6923 (declared; the CUDA backend never defines it, the HIP backend returns
+ * NOT_SUPPORTED, hip/kernel/level2/alphasparse_spmv.hip:229-256).  Here it runs the
+ * preprocessing pass: row-length bins, merge-path tile partition, statistics. */
+alphasparseStatus_t alphasparseSpMV_analysis(alphasparseHandle_t handle,
+                                             alphasparseOperation_t opA,
+                                             alphasparseSpMatDescr_t matA,
+                                             alphasparseSpMVAlg_t alg);
+/* spapi.h:6925-6926 takes no matrix; it is kept and is a no-op.  The plan is released by
+ * alphasparseSpMV_clearMat or alphasparseDestroySpMat. */
+alphasparseStatus_t alphasparseSpMV_clear(alphasparseHandle_t handle, alphasparseSpMVAlg_t alg);
+alphasparseStatus_t alphasparseSpMV_clearMat(alphasparseHandle_t handle,
+                                             alphasparseSpMatDescr_t matA); /* extension */
+
+/* ---- SpMM: C = alpha*op(A)*op(B) + beta*C, B and C row-major ------------------------ */
+/* spapi.h:6963-6974; cuda/kernel/level3/alphasparse_spmm.cu:531-612 */
+alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t handle, alphasparseOperation_t opA,
+                                    alphasparseOperation_t opB, const void* alpha,
+                                    alphasparseSpMatDescr_t matA, alphasparseDnMatDescr_t matB,
+                                    const void* beta, alphasparseDnMatDescr_t matC,
+                                    alphasparseDataType computeType, alphasparseSpMMAlg_t alg,
+                                    void* externalBuffer);
+/* spapi.h:7017-7028; cuda/kernel/level3/alphasparse_spmm.cu:614-759 */
+alphasparseStatus_t alphasparseSpMM_bufferSize(alphasparseHandle_t handle,
+                                               alphasparseOperation_t opA,
+                                               alphasparseOperation_t opB, const void* alpha,
+                                               alphasparseSpMatDescr_t matA,
+                                               alphasparseDnMatDescr_t matB, const void* beta,
+                                               alphasparseDnMatDescr_t matC,
+                                               alphasparseDataType computeType,
+                                               alphasparseSpMMAlg_t alg, size_t* bufferSize);
+/* spapi.h:7004-7015; defined only by the HIP backend (alphasparse_spmm.hip:657-695). */
+alphasparseStatus_t alphasparseSpMM_preprocess(alphasparseHandle_t handle,
+                                               alphasparseOperation_t opA,
+                                               alphasparseOperation_t opB, const void* alpha,
+                                               alphasparseSpMatDescr_t matA,
+                                               alphasparseDnMatDescr_t matB, const void* beta,
+                                               alphasparseDnMatDescr_t matC,
+                                               alphasparseDataType computeType,
+                                               alphasparseSpMMAlg_t alg, size_t* bufferSize);
+
+/* ---- multi-GPU row partition (extension; the reference is single-device) ------------ */
+/* Contiguous row ranges of near-equal nnz, the rule of hygon/util/partition.cpp:83-96
+ * (device twin: cuda/kernel/level2/alphasparse_spmv_csr_row_partition.h:26-45) lifted to
+ * 64-bit: bounds[0]=0, bounds[parts]=rows, bounds[i]=first j in [0,rows-1] with
+ * row_end[j] >= (nnz/parts)*i.  row_offsets is a DEVICE pointer; bounds is a HOST array of
+ * parts+1 entries.  Synchronises handle->stream. */
+alphasparseStatus_t alphasparseCsrPartitionRowsByNnz(alphasparseHandle_t handle, int64_t rows,
+                                                     const void* row_offsets,
+                                                     alphasparseIndexType_t rowOffsetsType,
+                                                     int parts, int64_t* bounds);
+/* local_offsets[i] = row_offsets[row_begin+i] - row_offsets[row_begin] for
+ * i in [0, row_end-row_begin]; the output width may differ from the input width (a shard
+ * with fewer than 2^31 nnz can use I32).  Device pointers, stream-ordered. */
+alphasparseStatus_t alphasparseCsrRebaseRowOffsets(alphasparseHandle_t handle,
+                                                   const void* row_offsets,
+                                                   alphasparseIndexType_t inType,
+                                                   int64_t row_begin, int64_t row_end,
+                                                   void* local_offsets,
+                                                   alphasparseIndexType_t outType);
+
+/* ---- introspection (extension) ------------------------------------------------------ */
+/* Copies the analysed plan to host arrays for bit-exact comparison with a CPU twin.
+ * Any output pointer may be NULL.  stats[16]: see ASP_STAT_* below. */
+enum {
+  ASP_STAT_MAX_LEN = 0, ASP_STAT_EMPTY_ROWS = 1, ASP_STAT_NUM_SHORT = 2, ASP_STAT_NUM_MEDIUM = 3,
+  ASP_STAT_NUM_LONG = 4, ASP_STAT_GROUP_LANES = 5, ASP_STAT_MERGE_ITEMS = 6,
+  ASP_STAT_MERGE_TILES = 7, ASP_STAT_VARIANT = 8, ASP_STAT_IDENTITY_SHORT = 9,
+  ASP_STAT_NNZ_SHORT = 10, ASP_STAT_COUNT = 16
+};
+alphasparseStatus_t alphasparseCsrPlanGet(alphasparseHandle_t handle,
+                                          alphasparseSpMatDescr_t matA, int64_t* stats,
+                                          int32_t* bin_rows /* rows */,
+                                          int32_t* merge_tile_row /* tiles+1 */);
+/* Name of the SpMV kernel variant the last alphasparseSpMV call on this matrix ran
+ * ("binned" or "merge"), and how many kernels this library has launched on the handle. */
+const char* alphasparseCsrLastVariant(alphasparseSpMatDescr_t matA);
+int64_t alphasparseGetLaunchCount(alphasparseHandle_t handle);
+
+/* ---- timers the reference's test drivers call: handle.h:532-539, handle.cu:547-599 --- */
+double get_time_us(void);
+double get_avg_time_n(const double* times, int n);   /* outlier-filtered mean, handle.cu:556-573 */
+
+#ifdef __cplusplus
+} /* extern "C" */
+
+/* Source compatibility with the reference's template creator
+ * (cuda/format/alphasparse_create_csr.h:6-18). */
+template <typename T>
+inline alphasparseStatus_t alphasparseCreateCsr(alphasparseSpMatDescr_t* spMatDescr,
+                                                const int rows, const int cols, const int nnz,
+                                                int* csrRowOffsets, int* col_data, T* val_data,
+                                                const alphasparseIndexType_t csrRowOffsetsType,
+                                                const alphasparseIndexType_t csrColIndType,
+                                                const alphasparseIndexBase_t idxBase,
+                                                const alphasparseDataType valueType) {
+  return alphasparseCreateCsr(spMatDescr, (int64_t)rows, (int64_t)cols, (int64_t)nnz,
+                              (void*)csrRowOffsets, (void*)col_data, (void*)val_data,
+                              csrRowOffsetsType, csrColIndType, idxBase, valueType);
+}
+#endif
+#endif /* ALPHASPARSE_B200_H */

@@ -1,0 +1,254 @@
+"""ctypes bindings of libalphasparse_b200.so plus thin torch-tensor conveniences.
+
+The functions in ``lib`` are the C ABI declared in include/alphasparse_b200.h, bound one to
+one.  The classes below only hold descriptors and device pointers of torch tensors (torch is
+the allocator and stream provider here, nothing more).  There is no fallback: if the shared
+library is missing or a call returns a non-zero status, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libalphasparse_b200.so")
+
+# enums (include/alphasparse_b200.h)
+STATUS_SUCCESS = 0
+STATUS_NAMES = {
+    0: "SUCCESS", 1: "NOT_INITIALIZED", 2: "ALLOC_FAILED", 3: "INVALID_VALUE",
+    4: "EXECUTION_FAILED", 5: "INTERNAL_ERROR", 6: "NOT_SUPPORTED", 7: "INVALID_POINTER",
+    8: "INVALID_HANDLE", 9: "INVALID_KERNEL_PARAM", 10: "INVALID_SIZE",
+}
+OP_N, OP_T, OP_C = 0, 1, 2
+ORDER_ROW, ORDER_COL = 0, 1
+R_32F, R_64F, R_16F, R_16BF = 0, 1, 4, 5
+INDEX_I32, INDEX_I64 = 2, 3
+BASE_ZERO, BASE_ONE = 0, 1
+SPMV_ALG_DEFAULT, SPMV_ALG_COO, SPMV_ALG_VECTOR, SPMV_ALG_MERGE = 0, 1, 6, 9
+SPMM_ALG_DEFAULT, SPMM_CSR_ALG1, SPMM_CSR_ALG2, SPMM_CSR_ALG6 = 0, 5, 6, 10
+STAT_NAMES = ["max_len", "empty_rows", "num_short", "num_medium", "num_long", "group_lanes",
+              "merge_items", "merge_tiles", "variant", "identity_short", "nnz_short"]
+
+EXPORTS = [
+    "initHandle", "alphasparseGetHandle", "alphasparse_destory_handle", "alphasparseSetStream",
+    "alphasparseGetStream", "alphasparseCreateCsr", "alphasparseCreateDnVec",
+    "alphasparseCreateDnMat", "alphasparseDestroySpMat", "alphasparseDestroyDnVec",
+    "alphasparseDestroyDnMat", "alphasparseDnVecSetValues", "alphasparseDnMatSetValues",
+    "alphasparseSpMV", "alphasparseSpMV_bufferSize", "alphasparseSpMV_analysis",
+    "alphasparseSpMV_clear", "alphasparseSpMV_clearMat", "alphasparseSpMM",
+    "alphasparseSpMM_bufferSize", "alphasparseSpMM_preprocess",
+    "alphasparseCsrPartitionRowsByNnz", "alphasparseCsrRebaseRowOffsets", "alphasparseCsrPlanGet",
+    "alphasparseCsrLastVariant", "alphasparseGetLaunchCount", "get_time_us", "get_avg_time_n",
+]
+
+
+class AlphaSparseError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        super().__init__(f"{where}: ALPHA_SPARSE_STATUS_{STATUS_NAMES.get(status, status)}")
+
+
+_lib = None
+
+
+def load():
+    """Load the CUDA library.  Raises if it has not been built (python -m library_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python library_b200/build.py` "
+                              "(there is no CPU or PyTorch fallback)")
+        lib = C.CDLL(LIB_PATH)
+        for name in EXPORTS:
+            getattr(lib, name)  # AttributeError if a declared symbol is not exported
+        lib.alphasparseCsrLastVariant.restype = C.c_char_p
+        lib.alphasparseGetLaunchCount.restype = C.c_int64
+        lib.get_time_us.restype = C.c_double
+        lib.get_avg_time_n.restype = C.c_double
+        _lib = lib
+    return _lib
+
+
+def _check(st: int, where: str):
+    if st != STATUS_SUCCESS:
+        raise AlphaSparseError(st, where)
+
+
+def _dtype_code(dt: torch.dtype) -> int:
+    return {torch.float32: R_32F, torch.float64: R_64F, torch.bfloat16: R_16BF,
+            torch.float16: R_16F}[dt]
+
+
+def _scalar(value, code):
+    return C.c_double(value) if code == R_64F else C.c_float(value)
+
+
+class Handle:
+    """alphasparseHandle_t bound to the current CUDA device; work runs on torch's current stream
+    unless ``set_stream`` is called."""
+
+    def __init__(self):
+        self.lib = load()
+        self.h = C.c_void_p()
+        _check(self.lib.alphasparseGetHandle(C.byref(self.h)), "alphasparseGetHandle")
+        self.use_torch_stream()
+
+    def use_torch_stream(self):
+        self.set_stream(torch.cuda.current_stream().cuda_stream)
+
+    def set_stream(self, cuda_stream: int):
+        _check(self.lib.alphasparseSetStream(self.h, C.c_void_p(cuda_stream)), "alphasparseSetStream")
+
+    @property
+    def launches(self) -> int:
+        return int(self.lib.alphasparseGetLaunchCount(self.h))
+
+    def close(self):
+        if self.h:
+            self.lib.alphasparse_destory_handle(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class DnVec:
+    def __init__(self, t: torch.Tensor):
+        assert t.is_cuda and t.is_contiguous()
+        self.t = t
+        self.d = C.c_void_p()
+        _check(load().alphasparseCreateDnVec(C.byref(self.d), C.c_int64(t.numel()),
+                                             C.c_void_p(t.data_ptr()), _dtype_code(t.dtype)),
+               "alphasparseCreateDnVec")
+
+    def __del__(self):
+        if getattr(self, "d", None):
+            load().alphasparseDestroyDnVec(self.d)
+
+
+class DnMat:
+    def __init__(self, t: torch.Tensor):
+        assert t.is_cuda and t.dim() == 2 and t.stride(1) == 1
+        self.t = t
+        self.d = C.c_void_p()
+        _check(load().alphasparseCreateDnMat(C.byref(self.d), C.c_int64(t.shape[0]),
+                                             C.c_int64(t.shape[1]), C.c_int64(t.stride(0)),
+                                             C.c_void_p(t.data_ptr()), _dtype_code(t.dtype),
+                                             ORDER_ROW), "alphasparseCreateDnMat")
+
+    def __del__(self):
+        if getattr(self, "d", None):
+            load().alphasparseDestroyDnMat(self.d)
+
+
+class CsrMatrix:
+    """alphasparseSpMatDescr_t over three device tensors (kept alive by this object)."""
+
+    def __init__(self, rows, cols, row_ptr: torch.Tensor, col_idx: torch.Tensor, val: torch.Tensor):
+        assert row_ptr.is_cuda and col_idx.is_cuda and val.is_cuda
+        self.rows, self.cols, self.nnz = int(rows), int(cols), int(col_idx.numel())
+        self.row_ptr, self.col_idx, self.val = row_ptr, col_idx, val
+        rt = {torch.int32: INDEX_I32, torch.int64: INDEX_I64}[row_ptr.dtype]
+        assert col_idx.dtype == torch.int32
+        self.d = C.c_void_p()
+        _check(load().alphasparseCreateCsr(
+            C.byref(self.d), C.c_int64(rows), C.c_int64(cols), C.c_int64(self.nnz),
+            C.c_void_p(row_ptr.data_ptr()), C.c_void_p(col_idx.data_ptr()),
+            C.c_void_p(val.data_ptr()), rt, INDEX_I32, BASE_ZERO, _dtype_code(val.dtype)),
+            "alphasparseCreateCsr")
+
+    @classmethod
+    def from_csr(cls, m, device="cuda"):
+        m = m.to(device)
+        return cls(m.rows, m.cols, m.row_ptr, m.col_idx, m.val)
+
+    def analyse(self, handle: Handle):
+        _check(load().alphasparseSpMV_analysis(handle.h, OP_N, self.d, SPMV_ALG_DEFAULT),
+               "alphasparseSpMV_analysis")
+
+    def plan(self, handle: Handle):
+        """Host copy of the analysed plan: (stats dict, bin_rows, merge_tile_row) as numpy."""
+        import numpy as np
+        lib = load()
+        stats = (C.c_int64 * 16)()
+        _check(lib.alphasparseCsrPlanGet(handle.h, self.d, stats, None, None), "alphasparseCsrPlanGet")
+        s = {n: int(stats[i]) for i, n in enumerate(STAT_NAMES)}
+        bins = np.zeros(max(self.rows, 1), dtype=np.int32)
+        tiles = np.zeros(s["merge_tiles"] + 1, dtype=np.int32)
+        _check(lib.alphasparseCsrPlanGet(handle.h, self.d, None, bins.ctypes.data_as(C.c_void_p),
+                                         tiles.ctypes.data_as(C.c_void_p)), "alphasparseCsrPlanGet")
+        return s, bins[: self.rows], tiles
+
+    def last_variant(self) -> str:
+        return load().alphasparseCsrLastVariant(self.d).decode()
+
+    def __del__(self):
+        if getattr(self, "d", None):
+            load().alphasparseDestroySpMat(self.d)
+
+
+def spmv_buffer_size(handle: Handle, A: CsrMatrix, x: DnVec, y: DnVec, alpha=1.0, beta=0.0,
+                     alg=SPMV_ALG_DEFAULT) -> int:
+    code = _dtype_code(A.val.dtype)
+    a, b = _scalar(alpha, code), _scalar(beta, code)
+    size = C.c_size_t(0)
+    _check(load().alphasparseSpMV_bufferSize(handle.h, OP_N, C.byref(a), A.d, x.d, C.byref(b), y.d,
+                                             code, alg, C.byref(size)), "alphasparseSpMV_bufferSize")
+    return int(size.value)
+
+
+def spmv(handle: Handle, A: CsrMatrix, x: DnVec, y: DnVec, alpha=1.0, beta=0.0,
+         alg=SPMV_ALG_DEFAULT, buffer: torch.Tensor | None = None, op=OP_N):
+    """y = alpha*A*x + beta*y on handle's stream (asynchronous)."""
+    code = _dtype_code(A.val.dtype)
+    a, b = _scalar(alpha, code), _scalar(beta, code)
+    buf = C.c_void_p(buffer.data_ptr()) if buffer is not None else C.c_void_p()
+    _check(load().alphasparseSpMV(handle.h, op, C.byref(a), A.d, x.d, C.byref(b), y.d, code, alg, buf),
+           "alphasparseSpMV")
+
+
+def spmm(handle: Handle, A: CsrMatrix, B: DnMat, Cm: DnMat, alpha=1.0, beta=0.0,
+         alg=SPMM_ALG_DEFAULT, compute=None):
+    """C = alpha*A*B + beta*C (row-major B and C) on handle's stream (asynchronous)."""
+    code = _dtype_code(Cm.t.dtype) if compute is None else compute
+    a, b = _scalar(alpha, code), _scalar(beta, code)
+    _check(load().alphasparseSpMM(handle.h, OP_N, OP_N, C.byref(a), A.d, B.d, C.byref(b), Cm.d, code,
+                                  alg, C.c_void_p()), "alphasparseSpMM")
+
+
+def spmm_preprocess(handle: Handle, A: CsrMatrix, B: DnMat, Cm: DnMat, alg=SPMM_ALG_DEFAULT):
+    code = _dtype_code(Cm.t.dtype)
+    a, b = _scalar(1.0, code), _scalar(0.0, code)
+    size = C.c_size_t(0)
+    _check(load().alphasparseSpMM_preprocess(handle.h, OP_N, OP_N, C.byref(a), A.d, B.d, C.byref(b),
+                                             Cm.d, code, alg, C.byref(size)),
+           "alphasparseSpMM_preprocess")
+    return int(size.value)
+
+
+def partition_rows_by_nnz(handle: Handle, row_ptr: torch.Tensor, parts: int):
+    import numpy as np
+    rt = {torch.int32: INDEX_I32, torch.int64: INDEX_I64}[row_ptr.dtype]
+    out = np.zeros(parts + 1, dtype=np.int64)
+    _check(load().alphasparseCsrPartitionRowsByNnz(handle.h, C.c_int64(row_ptr.numel() - 1),
+                                                   C.c_void_p(row_ptr.data_ptr()), rt, parts,
+                                                   out.ctypes.data_as(C.c_void_p)),
+           "alphasparseCsrPartitionRowsByNnz")
+    return out
+
+
+def rebase_row_offsets(handle: Handle, row_ptr: torch.Tensor, row_begin: int, row_end: int,
+                       out_dtype=torch.int32) -> torch.Tensor:
+    it = {torch.int32: INDEX_I32, torch.int64: INDEX_I64}
+    out = torch.empty(row_end - row_begin + 1, dtype=out_dtype, device=row_ptr.device)
+    _check(load().alphasparseCsrRebaseRowOffsets(handle.h, C.c_void_p(row_ptr.data_ptr()),
+                                                 it[row_ptr.dtype], C.c_int64(row_begin),
+                                                 C.c_int64(row_end), C.c_void_p(out.data_ptr()),
+                                                 it[out_dtype]), "alphasparseCsrRebaseRowOffsets")
+    return out

@@ -1,0 +1,424 @@
+// The preprocessing pass of the CSR descriptor: row-length classes with per-class row lists
+// (stable, in row order), the merge-path tile partition, the statistics that pick the SpMV
+// variant, a structural validator, and the nnz-balanced row partition used to shard a matrix
+// across GPUs.
+//
+// The reference's CSR descriptor only records pointers
+// (cuda/format/alphasparse_create_csr.h:6-63).  Its kernels redo their partitioning on every
+// call: find_rows appends rows to bins with atomics, so the order depends on arrival
+// (cuda/kernel/level2/alphasparse_spmv_csr_adaptive2.h:6-48), and the merge-path search runs
+// per SpMV (alphasparse_spmv_csr_merge_ginkgo.h:133-158).  Here both are computed once,
+// deterministically, and kept in the descriptor.
+#include <cub/device/device_select.cuh>
+#include <thrust/iterator/counting_iterator.h>
+
+#include <new>
+
+#include "asp_internal.h"
+
+namespace asp {
+
+namespace {
+
+enum { C_SHORT = 0, C_MEDIUM, C_LONG, C_EMPTY, C_NNZ_SHORT, C_MAXLEN, C_BAD, C_COUNT };
+
+template <typename OffT>
+__global__ void __launch_bounds__(256) row_stats_kernel(const OffT* __restrict__ rp, int64_t rows,
+                                                        int64_t nnz,
+                                                        unsigned long long* __restrict__ ctr) {
+  unsigned long long loc[C_COUNT] = {0, 0, 0, 0, 0, 0, 0};
+  for (int64_t r = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; r < rows;
+       r += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t s = (int64_t)rp[r], e = (int64_t)rp[r + 1];
+    const int64_t len = e - s;
+    if (len < 0 || s < 0 || e > nnz) {
+      loc[C_BAD] = 1;
+      continue;
+    }
+    if (len <= kShortMax) {
+      loc[C_SHORT]++;
+      loc[C_NNZ_SHORT] += (unsigned long long)len;
+    } else if (len <= kMediumMax) {
+      loc[C_MEDIUM]++;
+    } else {
+      loc[C_LONG]++;
+    }
+    if (len == 0) loc[C_EMPTY]++;
+    if ((unsigned long long)len > loc[C_MAXLEN]) loc[C_MAXLEN] = (unsigned long long)len;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0 && rows > 0) {
+    if ((int64_t)rp[0] != 0 || (int64_t)rp[rows] != nnz) loc[C_BAD] = 1;
+  }
+#pragma unroll
+  for (int c = 0; c < C_COUNT; ++c) {
+    unsigned long long v = loc[c];
+    for (int o = 16; o > 0; o >>= 1) {
+      unsigned long long w = __shfl_xor_sync(0xffffffffu, v, o);
+      v = (c == C_MAXLEN || c == C_BAD) ? (v > w ? v : w) : v + w;
+    }
+    if ((threadIdx.x & 31) == 0 && v) {
+      if (c == C_MAXLEN || c == C_BAD) atomicMax(&ctr[c], v);
+      else atomicAdd(&ctr[c], v);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) col_check_kernel(const int32_t* __restrict__ col, int64_t nnz,
+                                                        int64_t cols,
+                                                        unsigned long long* __restrict__ bad) {
+  bool b = false;
+  for (int64_t k = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; k < nnz;
+       k += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t c = col[k];
+    b |= (c < 0 || (int64_t)c >= cols);
+  }
+  if (__any_sync(0xffffffffu, b) && (threadIdx.x & 31) == 0) atomicMax(bad, 1ull);
+}
+
+template <typename OffT>
+struct RowClassIs {
+  const OffT* rp;
+  int cls;
+  __device__ bool operator()(int32_t r) const {
+    const int64_t len = (int64_t)rp[r + 1] - (int64_t)rp[r];
+    const int c = len <= kShortMax ? C_SHORT : (len <= kMediumMax ? C_MEDIUM : C_LONG);
+    return c == cls;
+  }
+};
+
+// Merge-path coordinate of diagonal d in the merge of row_end[0..rows) with the entry indices
+// 0..nnz): the number of row ends consumed before the diagonal.  Same search as the
+// reference's merge_path_search (alphasparse_spmv_csr_merge_ginkgo.h:11-35).
+template <typename OffT>
+__global__ void __launch_bounds__(256) merge_tile_kernel(const OffT* __restrict__ rp, int64_t rows,
+                                                         int64_t nnz, int64_t tiles,
+                                                         int32_t* __restrict__ tile_row) {
+  const int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (t > tiles) return;
+  const OffT* row_end = rp + 1;
+  int64_t diag = t * (int64_t)kMergeItems;
+  if (diag > rows + nnz) diag = rows + nnz;
+  int64_t lo = diag > nnz ? diag - nnz : 0;
+  int64_t hi = diag < rows ? diag : rows;
+  while (lo < hi) {
+    const int64_t mid = (lo + hi) >> 1;
+    if ((int64_t)row_end[mid] <= diag - mid - 1) lo = mid + 1;
+    else hi = mid;
+  }
+  tile_row[t] = (int32_t)lo;
+}
+
+template <typename OffT>
+__global__ void partition_kernel(const OffT* __restrict__ rp, int64_t rows, int parts,
+                                 int64_t* __restrict__ bounds) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i > parts) return;
+  if (i == 0) {
+    bounds[0] = 0;
+    return;
+  }
+  if (i == parts || rows <= 0) {
+    bounds[i] = rows > 0 ? rows : 0;
+    return;
+  }
+  const OffT* row_end = rp + 1;
+  const int64_t nnz = (int64_t)row_end[rows - 1];
+  const int64_t v = (nnz / parts) * i;
+  int64_t l = 0, r = rows - 1;
+  while (r > l) {
+    const int64_t m = (l + r) / 2;
+    if ((int64_t)row_end[m] < v) l = m + 1;
+    else r = m;
+  }
+  bounds[i] = l;
+}
+
+template <typename InT, typename OutT>
+__global__ void __launch_bounds__(256) rebase_kernel(const InT* __restrict__ rp, int64_t row_begin,
+                                                     int64_t n, OutT* __restrict__ out) {
+  const int64_t base = (int64_t)rp[row_begin];
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = (OutT)((int64_t)rp[row_begin + i] - base);
+}
+
+inline int grid_for(int64_t n, int sm_count) {
+  int64_t g = (n + 255) / 256;
+  const int64_t cap = (int64_t)sm_count * 8;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+template <typename OffT>
+alphasparseStatus_t analyse_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, Plan* p) {
+  cudaStream_t st = h->stream;
+  const OffT* rp = reinterpret_cast<const OffT*>(A->row_offsets);
+  const int sms = impl(h)->sm_count;
+  unsigned long long* d_ctr = nullptr;
+  ASP_CUDA(cudaMalloc(&d_ctr, sizeof(unsigned long long) * (C_COUNT + 1)));
+  auto fail = [&](alphasparseStatus_t s) {
+    cudaFree(d_ctr);
+    return s;
+  };
+  if (cudaMemsetAsync(d_ctr, 0, sizeof(unsigned long long) * (C_COUNT + 1), st) != cudaSuccess)
+    return fail(ALPHA_SPARSE_STATUS_INTERNAL_ERROR);
+  unsigned long long ctr[C_COUNT + 1] = {0};
+  if (p->rows > 0) {
+    row_stats_kernel<OffT><<<grid_for(p->rows, sms), 256, 0, st>>>(rp, p->rows, p->nnz, d_ctr);
+    impl(h)->launches++;
+  }
+  if (cudaMemcpyAsync(ctr, d_ctr, sizeof(unsigned long long) * C_COUNT, cudaMemcpyDeviceToHost,
+                      st) != cudaSuccess ||
+      cudaStreamSynchronize(st) != cudaSuccess)
+    return fail(status_of(cudaGetLastError()));
+  if (ctr[C_BAD]) return fail(ALPHA_SPARSE_STATUS_INVALID_VALUE);
+  // Column range check only after the offsets are known to be sane.
+  if (p->nnz > 0) {
+    col_check_kernel<<<grid_for(p->nnz, sms), 256, 0, st>>>(A->const_col_data, p->nnz, p->cols,
+                                                            d_ctr + C_COUNT);
+    impl(h)->launches++;
+    if (cudaMemcpyAsync(&ctr[C_COUNT], d_ctr + C_COUNT, sizeof(unsigned long long),
+                        cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess)
+      return fail(status_of(cudaGetLastError()));
+    if (ctr[C_COUNT]) return fail(ALPHA_SPARSE_STATUS_INVALID_VALUE);
+  }
+  cudaFree(d_ctr);
+  d_ctr = nullptr;
+
+  p->n_short = (int64_t)ctr[C_SHORT];
+  p->n_medium = (int64_t)ctr[C_MEDIUM];
+  p->n_long = (int64_t)ctr[C_LONG];
+  p->empty_rows = (int64_t)ctr[C_EMPTY];
+  p->nnz_short = (int64_t)ctr[C_NNZ_SHORT];
+  p->max_len = (int64_t)ctr[C_MAXLEN];
+  p->identity_short = (p->n_short == p->rows);
+
+  // Lanes per short row: enough 16-byte loads to cover the mean short row in one pass.
+  {
+    const int vec = 16 / (int)elem_size(A->data_type == ALPHA_R_16BF ? ALPHA_R_32F : A->data_type);
+    const int64_t nonempty = p->n_short - p->empty_rows > 0 ? p->n_short - p->empty_rows : 1;
+    const double mean = (double)p->nnz_short / (double)nonempty;
+    int g = 2;
+    while (g < 32 && g * vec < mean) g <<= 1;
+    const int forced = env_int("ASP_GROUP_LANES", 0);
+    if (forced == 2 || forced == 4 || forced == 8 || forced == 16 || forced == 32) g = forced;
+    p->group_lanes = g;
+  }
+
+  // Per-class row lists, each in ascending row order.
+  if (p->rows > 0 && !p->identity_short) {
+    ASP_CUDA(cudaMalloc(&p->bin_rows, sizeof(int32_t) * p->rows));
+    int* d_num = nullptr;
+    ASP_CUDA(cudaMalloc(&d_num, sizeof(int)));
+    size_t tmp_bytes = 0;
+    thrust::counting_iterator<int32_t> it(0);
+    RowClassIs<OffT> pred{rp, C_SHORT};
+    cub::DeviceSelect::If(nullptr, tmp_bytes, it, p->bin_rows, d_num, (int)p->rows, pred, st);
+    void* tmp = nullptr;
+    if (cudaMalloc(&tmp, tmp_bytes ? tmp_bytes : 16) != cudaSuccess) {
+      cudaFree(d_num);
+      return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    const int64_t off[3] = {0, p->n_short, p->n_short + p->n_medium};
+    for (int c = 0; c < 3; ++c) {
+      pred.cls = c;
+      cub::DeviceSelect::If(tmp, tmp_bytes, it, p->bin_rows + off[c], d_num, (int)p->rows, pred, st);
+      impl(h)->launches++;
+    }
+    cudaError_t e = cudaStreamSynchronize(st);
+    cudaFree(tmp);
+    cudaFree(d_num);
+    if (e != cudaSuccess) return status_of(e);
+  }
+
+  // Merge-path tiles.
+  p->merge_tiles = (p->rows + p->nnz + kMergeItems - 1) / kMergeItems;
+  ASP_CUDA(cudaMalloc(&p->merge_tile_row, sizeof(int32_t) * (p->merge_tiles + 1)));
+  ASP_CUDA(cudaMalloc(&p->carry, sizeof(double) * (p->merge_tiles > 0 ? p->merge_tiles : 1)));
+  merge_tile_kernel<OffT><<<(int)((p->merge_tiles + 1 + 255) / 256), 256, 0, st>>>(
+      rp, p->rows, p->nnz, p->merge_tiles, p->merge_tile_row);
+  impl(h)->launches++;
+  ASP_CUDA(cudaGetLastError());
+  ASP_CUDA(cudaStreamSynchronize(st));
+
+  // Variant choice: the binned kernel gives every row of a class the same lane count, so it
+  // loses when lengths inside the matrix differ by orders of magnitude or when many rows are
+  // empty (idle groups); merge-path gives every CTA the same number of items regardless.
+  {
+    const double mean_all = p->rows > 0 ? (double)p->nnz / (double)p->rows : 0.0;
+    const bool skewed = (double)p->max_len > 16.0 * mean_all + kShortMax;
+    const bool sparse_rows = p->empty_rows * 4 > p->rows;
+    p->variant_auto = (skewed || sparse_rows) ? kVariantMerge : kVariantBinned;
+  }
+  return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+}  // namespace
+
+alphasparseStatus_t validate_csr(alphasparseSpMatDescr_t A) {
+  if (!A || !A->init) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+  if (A->format != ALPHA_SPARSE_FORMAT_CSR) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (A->idx_base != ALPHA_SPARSE_INDEX_BASE_ZERO) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (A->col_type != ALPHA_SPARSE_INDEXTYPE_I32) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (A->row_type != ALPHA_SPARSE_INDEXTYPE_I32 && A->row_type != ALPHA_SPARSE_INDEXTYPE_I64)
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (!A->row_offsets) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+void free_plan(Plan* p) {
+  if (!p) return;
+  cudaFree(p->bin_rows);
+  cudaFree(p->merge_tile_row);
+  cudaFree(p->carry);
+  if (p->spmm_tc) free_spmm_tc_plan(p->spmm_tc);
+  delete p;
+}
+
+alphasparseStatus_t analyse(alphasparseHandle_t h, alphasparseSpMatDescr_t A) {
+  alphasparseStatus_t s = validate_csr(A);
+  if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  if (A->info) {
+    free_plan(plan_of(A));
+    A->info = nullptr;
+    A->analysed = false;
+  }
+  Plan* p = new (std::nothrow) Plan();
+  if (!p) return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+  p->device = h->device;
+  p->rows = A->rows;
+  p->cols = A->cols;
+  p->nnz = A->nnz;
+  p->off64 = (A->row_type == ALPHA_SPARSE_INDEXTYPE_I64);
+  s = p->off64 ? analyse_t<int64_t>(h, A, p) : analyse_t<int32_t>(h, A, p);
+  if (s != ALPHA_SPARSE_STATUS_SUCCESS) {
+    free_plan(p);
+    return s;
+  }
+  A->info = p;
+  A->analysed = true;
+  return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+}  // namespace asp
+
+using namespace asp;
+
+extern "C" {
+
+alphasparseStatus_t alphasparseSpMV_analysis(alphasparseHandle_t h, alphasparseOperation_t opA,
+                                             alphasparseSpMatDescr_t A, alphasparseSpMVAlg_t) {
+  if (!h || !h->impl) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+  if (!A) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  if (opA != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  return analyse(h, A);
+}
+
+alphasparseStatus_t alphasparseSpMV_clear(alphasparseHandle_t h, alphasparseSpMVAlg_t) {
+  return h ? ALPHA_SPARSE_STATUS_SUCCESS : ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+}
+
+alphasparseStatus_t alphasparseSpMV_clearMat(alphasparseHandle_t h, alphasparseSpMatDescr_t A) {
+  if (!h) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+  if (!A) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  if (A->info) {
+    cudaStreamSynchronize(h->stream);
+    free_plan(plan_of(A));
+    A->info = nullptr;
+  }
+  A->analysed = false;
+  return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+alphasparseStatus_t alphasparseCsrPlanGet(alphasparseHandle_t h, alphasparseSpMatDescr_t A,
+                                          int64_t* stats, int32_t* bin_rows,
+                                          int32_t* merge_tile_row) {
+  if (!h) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+  if (!A) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  Plan* p = plan_of(A);
+  if (!p) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+  ASP_CUDA(cudaStreamSynchronize(h->stream));
+  if (stats) {
+    for (int i = 0; i < ASP_STAT_COUNT; ++i) stats[i] = 0;
+    stats[ASP_STAT_MAX_LEN] = p->max_len;
+    stats[ASP_STAT_EMPTY_ROWS] = p->empty_rows;
+    stats[ASP_STAT_NUM_SHORT] = p->n_short;
+    stats[ASP_STAT_NUM_MEDIUM] = p->n_medium;
+    stats[ASP_STAT_NUM_LONG] = p->n_long;
+    stats[ASP_STAT_GROUP_LANES] = p->group_lanes;
+    stats[ASP_STAT_MERGE_ITEMS] = kMergeItems;
+    stats[ASP_STAT_MERGE_TILES] = p->merge_tiles;
+    stats[ASP_STAT_VARIANT] = p->variant_auto;
+    stats[ASP_STAT_IDENTITY_SHORT] = p->identity_short ? 1 : 0;
+    stats[ASP_STAT_NNZ_SHORT] = p->nnz_short;
+  }
+  if (bin_rows && p->rows > 0) {
+    if (p->identity_short) {
+      for (int64_t i = 0; i < p->rows; ++i) bin_rows[i] = (int32_t)i;
+    } else {
+      ASP_CUDA(cudaMemcpy(bin_rows, p->bin_rows, sizeof(int32_t) * p->rows, cudaMemcpyDeviceToHost));
+    }
+  }
+  if (merge_tile_row)
+    ASP_CUDA(cudaMemcpy(merge_tile_row, p->merge_tile_row, sizeof(int32_t) * (p->merge_tiles + 1),
+                        cudaMemcpyDeviceToHost));
+  return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+const char* alphasparseCsrLastVariant(alphasparseSpMatDescr_t A) {
+  if (!A || !A->info) return "none";
+  switch (plan_of(A)->last_variant) {
+    case kVariantBinned: return "binned";
+    case kVariantMerge: return "merge";
+    default: return "none";
+  }
+}
+
+alphasparseStatus_t alphasparseCsrPartitionRowsByNnz(alphasparseHandle_t h, int64_t rows,
+                                                     const void* row_offsets,
+                                                     alphasparseIndexType_t rowT, int parts,
+                                                     int64_t* bounds) {
+  if (!h || !h->impl) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+  if (!row_offsets || !bounds) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  if (rows < 0 || parts < 1 || parts > 4096) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  if (rowT != ALPHA_SPARSE_INDEXTYPE_I32 && rowT != ALPHA_SPARSE_INDEXTYPE_I64)
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  int64_t* d = nullptr;
+  ASP_CUDA(cudaMalloc(&d, sizeof(int64_t) * (parts + 1)));
+  const int g = (parts + 1 + 127) / 128;
+  if (rowT == ALPHA_SPARSE_INDEXTYPE_I32)
+    partition_kernel<int32_t><<<g, 128, 0, h->stream>>>((const int32_t*)row_offsets, rows, parts, d);
+  else
+    partition_kernel<int64_t><<<g, 128, 0, h->stream>>>((const int64_t*)row_offsets, rows, parts, d);
+  impl(h)->launches++;
+  cudaError_t e = cudaMemcpyAsync(bounds, d, sizeof(int64_t) * (parts + 1), cudaMemcpyDeviceToHost,
+                                  h->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+  cudaFree(d);
+  return status_of(e);
+}
+
+alphasparseStatus_t alphasparseCsrRebaseRowOffsets(alphasparseHandle_t h, const void* row_offsets,
+                                                   alphasparseIndexType_t inT, int64_t row_begin,
+                                                   int64_t row_end, void* local,
+                                                   alphasparseIndexType_t outT) {
+  if (!h || !h->impl) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+  if (!row_offsets || !local) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  if (row_begin < 0 || row_end < row_begin) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  const int64_t n = row_end - row_begin + 1;
+  const int g = grid_for(n, impl(h)->sm_count);
+  const bool i64 = inT == ALPHA_SPARSE_INDEXTYPE_I64, o64 = outT == ALPHA_SPARSE_INDEXTYPE_I64;
+  if ((!i64 && inT != ALPHA_SPARSE_INDEXTYPE_I32) || (!o64 && outT != ALPHA_SPARSE_INDEXTYPE_I32))
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  cudaStream_t st = h->stream;
+  if (i64 && o64) rebase_kernel<<<g, 256, 0, st>>>((const int64_t*)row_offsets, row_begin, n, (int64_t*)local);
+  else if (i64) rebase_kernel<<<g, 256, 0, st>>>((const int64_t*)row_offsets, row_begin, n, (int32_t*)local);
+  else if (o64) rebase_kernel<<<g, 256, 0, st>>>((const int32_t*)row_offsets, row_begin, n, (int64_t*)local);
+  else rebase_kernel<<<g, 256, 0, st>>>((const int32_t*)row_offsets, row_begin, n, (int32_t*)local);
+  impl(h)->launches++;
+  return status_of(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -1,0 +1,100 @@
+// Internal declarations shared by the translation units of libalphasparse_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdlib>
+
+#include "alphasparse_b200.h"
+
+namespace asp {
+
+// ---- tuning constants of the preprocessing pass -----------------------------------------
+// Row classes of the binned SpMV, by number of entries L in a row:
+//   short  (L <= kShortMax)  : a group of G lanes per row (G = 2..32, one value per matrix)
+//   medium (L <= kMediumMax) : one warp per row
+//   long                     : one CTA per row
+constexpr int kShortMax = 64;
+constexpr int kMediumMax = 4096;
+constexpr int kThreads = 256;        // every SpMV / SpMM CTA
+constexpr int kShortUnroll = 2;      // rows in flight per lane group
+// Merge-path SpMV: each CTA consumes kMergeItems (rows + entries) of the merge list.
+constexpr int kMergeIpt = 8;
+constexpr int kMergeItems = kThreads * kMergeIpt;
+
+enum Variant { kVariantBinned = 0, kVariantMerge = 1 };
+
+struct HandleImpl {
+  int sm_count = 148;
+  int64_t launches = 0;
+  size_t smem_optin = 0;
+};
+
+// The analysis result attached to a CSR descriptor (matA->info).
+struct Plan {
+  int device = 0;
+  int64_t rows = 0, cols = 0, nnz = 0;
+  bool off64 = false;
+  // statistics
+  int64_t max_len = 0, empty_rows = 0;
+  int64_t n_short = 0, n_medium = 0, n_long = 0, nnz_short = 0;
+  int group_lanes = 4;
+  bool identity_short = false;      // every row is short: no row list is needed
+  int32_t* bin_rows = nullptr;      // device, rows entries: short | medium | long, each in row order
+  // merge path
+  int64_t merge_tiles = 0;
+  int32_t* merge_tile_row = nullptr;  // device, merge_tiles + 1
+  void* carry = nullptr;              // device, merge_tiles * 8 bytes (used when no external buffer)
+  int variant_auto = kVariantBinned;
+  int last_variant = -1;
+  // SpMM
+  void* spmm_tc = nullptr;            // plan of the tcgen05 variant (spmm_tc.cu)
+};
+
+inline HandleImpl* impl(alphasparseHandle_t h) { return reinterpret_cast<HandleImpl*>(h->impl); }
+inline Plan* plan_of(alphasparseSpMatDescr_t A) { return reinterpret_cast<Plan*>(A->info); }
+
+// cudaError -> status, the table of cuda/util/handle.cu:18-50 in the reference.
+inline alphasparseStatus_t status_of(cudaError_t e) {
+  switch (e) {
+    case cudaSuccess: return ALPHA_SPARSE_STATUS_SUCCESS;
+    case cudaErrorMemoryAllocation: return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    case cudaErrorInvalidValue: return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    case cudaErrorInvalidDevicePointer: return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+    case cudaErrorInvalidResourceHandle: return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+    case cudaErrorLaunchFailure:
+    case cudaErrorLaunchTimeout:
+    case cudaErrorLaunchOutOfResources: return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    default: return ALPHA_SPARSE_STATUS_INTERNAL_ERROR;
+  }
+}
+
+#define ASP_CUDA(call)                                   \
+  do {                                                   \
+    cudaError_t e_ = (call);                             \
+    if (e_ != cudaSuccess) return ::asp::status_of(e_);  \
+  } while (0)
+
+inline size_t elem_size(alphasparseDataType t) {
+  switch (t) {
+    case ALPHA_R_32F: return 4;
+    case ALPHA_R_64F: return 8;
+    case ALPHA_R_16BF: case ALPHA_R_16F: return 2;
+    default: return 0;
+  }
+}
+
+inline int env_int(const char* name, int dflt) {
+  const char* s = getenv(name);
+  return s && *s ? atoi(s) : dflt;
+}
+
+// analysis.cu
+alphasparseStatus_t analyse(alphasparseHandle_t h, alphasparseSpMatDescr_t A);
+void free_plan(Plan* p);
+alphasparseStatus_t validate_csr(alphasparseSpMatDescr_t A);
+
+// spmm_tc.cu
+void free_spmm_tc_plan(void* p);
+
+}  // namespace asp

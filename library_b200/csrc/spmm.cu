@@ -1,0 +1,266 @@
+// CSR SpMM  C = alpha*A*B + beta*C  with row-major B (cols x N) and C (rows x N) for sm_100a:
+// the SIMT row-block kernel, the dispatcher and the buffer-size / preprocess queries.
+//
+// Replaces, for CSR with opA = opB = N and row-major dense operands, the reference's
+// cuda/kernel/level3/alphasparse_spmm.cu:19-759 and the five algorithms of
+// alphasparse_spmm_csr.h (:109-198 row-balanced, :241-393 element-balanced, :395-533 merge,
+// :573-795 adaptive, :818-905 flat).  Differences that matter to a caller:
+//   - no atomics and no separate C *= beta pass (the reference's default algorithm scales C
+//     in a first kernel, alphasparse_spmm_csr.h:907-914,1067-1071, then accumulates with
+//     atomicAdd): a row of C is owned by one lane group, initialised with beta*C and
+//     accumulated in entry order with fma(alpha*a, b, c) - the order of the reference's CPU
+//     kernel (hygon/kernel/level3/mm/gemm/gemm_csr_row.hpp:33-56), so fp32/fp64 results are
+//     reproducible and equal to that kernel's;
+//   - indices into B and C are 64-bit (the reference multiplies int32, e.g. :907-914);
+//   - column-major B / C is rejected instead of transposing the caller's buffers in place
+//     (alphasparse_spmm.cu:134-162,274-283).
+#include <climits>
+#include <cstring>
+#include <type_traits>
+
+#include "asp_internal.h"
+
+namespace asp {
+
+alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A,
+                                alphasparseDnMatDescr_t B, alphasparseDnMatDescr_t C, float alpha,
+                                float beta, bool preprocess_only);
+bool spmm_tc_applicable(alphasparseSpMatDescr_t A, alphasparseDnMatDescr_t B,
+                        alphasparseDnMatDescr_t C);
+
+namespace {
+
+constexpr int kChunk = 1024;  // entries of A staged in shared memory per round
+
+template <typename T, int VN> struct Pack;
+template <> struct Pack<float, 4> { using V = float4; };
+template <> struct Pack<double, 2> { using V = double2; };
+template <> struct Pack<float, 1> { using V = float; };
+template <> struct Pack<double, 1> { using V = double; };
+
+template <typename T, int VN>
+__device__ __forceinline__ void load_pack(const T* p, T (&r)[VN]) {
+  if constexpr (VN == 1) {
+    r[0] = __ldg(p);
+  } else {
+    const typename Pack<T, VN>::V v = __ldg(reinterpret_cast<const typename Pack<T, VN>::V*>(p));
+    if constexpr (VN == 4) { r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w; }
+    else { r[0] = v.x; r[1] = v.y; }
+  }
+}
+
+template <typename T, int VN>
+__device__ __forceinline__ void store_pack(T* p, const T (&r)[VN]) {
+  if constexpr (VN == 1) {
+    *p = r[0];
+  } else if constexpr (VN == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(r[0], r[1], r[2], r[3]);
+  } else {
+    *reinterpret_cast<double2*>(p) = make_double2(r[0], r[1]);
+  }
+}
+
+// A CTA owns RB consecutive rows and one slab of LN*VN columns of C.  LN lanes share a row,
+// each lane keeps VN adjacent columns in registers.  The CTA's entries of A go through
+// shared memory kChunk at a time (coalesced loads, alpha folded into the value), and every
+// lane group then walks the part of its rows that lies in the chunk, reading (col, alpha*a)
+// as a shared-memory broadcast and the matching row segment of B with one vector load.
+template <typename T, typename OffT, int LN, int VN>
+__global__ void __launch_bounds__(kThreads)
+spmm_rowblock_kernel(const OffT* __restrict__ rp, const int* __restrict__ col,
+                     const T* __restrict__ val, const T* __restrict__ B, int64_t ldb,
+                     T* __restrict__ C, int64_t ldc, T alpha, T beta, int64_t rows, int64_t n) {
+  constexpr int NG = kThreads / LN;
+  constexpr int RPG = NG >= 32 ? 1 : 32 / NG;
+  constexpr int RB = NG * RPG;
+  __shared__ int s_col[kChunk];
+  __shared__ T s_val[kChunk];
+
+  const int lane = threadIdx.x % LN;
+  const int grp = threadIdx.x / LN;
+  const int64_t r0 = (int64_t)blockIdx.x * RB;
+  const int64_t r1 = r0 + RB < rows ? r0 + RB : rows;
+  const int64_t c0 = ((int64_t)blockIdx.y * LN + lane) * VN;
+  const bool col_ok = c0 < n;
+
+  int64_t rs[RPG], re[RPG];
+  T acc[RPG][VN];
+#pragma unroll
+  for (int i = 0; i < RPG; ++i) {
+    const int64_t r = r0 + (int64_t)grp * RPG + i;
+    rs[i] = r < rows ? (int64_t)rp[r] : 0;
+    re[i] = r < rows ? (int64_t)rp[r + 1] : 0;
+#pragma unroll
+    for (int v = 0; v < VN; ++v) acc[i][v] = T(0);
+    if (beta != T(0) && r < rows && col_ok) {
+      T c[VN];
+      load_pack<T, VN>(C + r * ldc + c0, c);
+#pragma unroll
+      for (int v = 0; v < VN; ++v) acc[i][v] = c[v] * beta;
+    }
+  }
+  const int64_t e0 = (int64_t)rp[r0], e1 = (int64_t)rp[r1];
+  for (int64_t base = e0; base < e1; base += kChunk) {
+    const int cnt = (int)(e1 - base < kChunk ? e1 - base : kChunk);
+    for (int i = threadIdx.x; i < cnt; i += kThreads) {
+      s_col[i] = __ldcs(col + base + i);
+      s_val[i] = alpha * __ldcs(val + base + i);
+    }
+    __syncthreads();
+    if (col_ok) {
+#pragma unroll
+      for (int i = 0; i < RPG; ++i) {
+        const int lo = (int)((rs[i] > base ? rs[i] : base) - base);
+        const int hi = (int)((re[i] < base + cnt ? re[i] : base + cnt) - base);
+#pragma unroll 4
+        for (int k = lo; k < hi; ++k) {
+          const T a = s_val[k];
+          T b[VN];
+          load_pack<T, VN>(B + (int64_t)s_col[k] * ldb + c0, b);
+#pragma unroll
+          for (int v = 0; v < VN; ++v) acc[i][v] = fma(a, b[v], acc[i][v]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (col_ok) {
+#pragma unroll
+    for (int i = 0; i < RPG; ++i) {
+      const int64_t r = r0 + (int64_t)grp * RPG + i;
+      if (r < rows) store_pack<T, VN>(C + r * ldc + c0, acc[i]);
+    }
+  }
+}
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+template <typename T, typename OffT, int LN, int VN>
+alphasparseStatus_t launch_rb(alphasparseHandle_t h, alphasparseSpMatDescr_t A, const T* B,
+                              int64_t ldb, T* C, int64_t ldc, T alpha, T beta, int64_t n) {
+  constexpr int NG = kThreads / LN;
+  constexpr int RB = NG * (NG >= 32 ? 1 : 32 / NG);
+  const int64_t gx = (A->rows + RB - 1) / RB;
+  const int64_t gy = (n + (int64_t)LN * VN - 1) / ((int64_t)LN * VN);
+  if (gx > INT_MAX || gy > 65535) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  spmm_rowblock_kernel<T, OffT, LN, VN><<<dim3((unsigned)gx, (unsigned)gy), kThreads, 0, h->stream>>>(
+      reinterpret_cast<const OffT*>(A->row_offsets), A->const_col_data,
+      reinterpret_cast<const T*>(A->const_val_data), B, ldb, C, ldc, alpha, beta, A->rows, n);
+  impl(h)->launches++;
+  return status_of(cudaGetLastError());
+}
+
+template <typename T, typename OffT>
+alphasparseStatus_t spmm_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, const T* B, int64_t ldb,
+                           T* C, int64_t ldc, T alpha, T beta, int64_t n) {
+  constexpr int VN = 16 / (int)sizeof(T);
+  if (A->rows == 0 || n == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+  const bool vec = (n % VN == 0) && (ldb % VN == 0) && (ldc % VN == 0) && aligned(B, 16) && aligned(C, 16);
+  if (!vec) return launch_rb<T, OffT, 32, 1>(h, A, B, ldb, C, ldc, alpha, beta, n);
+  const int64_t lanes = n / VN;
+  if (lanes <= 1) return launch_rb<T, OffT, 1, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
+  if (lanes <= 2) return launch_rb<T, OffT, 2, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
+  if (lanes <= 4) return launch_rb<T, OffT, 4, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
+  if (lanes <= 8) return launch_rb<T, OffT, 8, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
+  if (lanes <= 16) return launch_rb<T, OffT, 16, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
+  return launch_rb<T, OffT, 32, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
+}
+
+alphasparseStatus_t check_spmm_args(alphasparseHandle_t h, alphasparseOperation_t opA,
+                                    alphasparseOperation_t opB, const void* alpha,
+                                    alphasparseSpMatDescr_t A, alphasparseDnMatDescr_t B,
+                                    const void* beta, alphasparseDnMatDescr_t C,
+                                    alphasparseDataType computeType) {
+  if (!h || !h->impl) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+  if (!alpha || !beta || !A || !B || !C) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  if (h->pointer_mode != ALPHA_SPARSE_POINTER_MODE_HOST) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (opA != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE || opB != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE)
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  alphasparseStatus_t s = validate_csr(A);
+  if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  if (!B->init || !C->init) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+  if (B->order != ALPHASPARSE_ORDER_ROW || C->order != ALPHASPARSE_ORDER_ROW)
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (B->rows != A->cols || C->rows != A->rows || B->cols != C->cols) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  if (B->ld < B->cols || C->ld < C->cols) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  if (!B->values || !C->values) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  const bool plain = (A->data_type == ALPHA_R_32F || A->data_type == ALPHA_R_64F) &&
+                     B->data_type == A->data_type && C->data_type == A->data_type &&
+                     computeType == A->data_type;
+  const bool mixed = A->data_type == ALPHA_R_16BF && B->data_type == ALPHA_R_16BF &&
+                     C->data_type == ALPHA_R_32F && computeType == ALPHA_R_32F;
+  if (!plain && !mixed) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+}  // namespace
+}  // namespace asp
+
+using namespace asp;
+
+extern "C" {
+
+alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t h, alphasparseOperation_t opA,
+                                    alphasparseOperation_t opB, const void* alpha,
+                                    alphasparseSpMatDescr_t A, alphasparseDnMatDescr_t B,
+                                    const void* beta, alphasparseDnMatDescr_t C,
+                                    alphasparseDataType computeType, alphasparseSpMMAlg_t alg,
+                                    void* /*externalBuffer*/) {
+  alphasparseStatus_t s = check_spmm_args(h, opA, opB, alpha, A, B, beta, C, computeType);
+  if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  if (!A->info) {
+    s = analyse(h, A);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  }
+  const int64_t n = C->cols;
+  if (A->data_type == ALPHA_R_16BF) {
+    // bf16 operands exist only for the tensor-core variant.
+    if (!spmm_tc_applicable(A, B, C)) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    return spmm_tc_run(h, A, B, C, *(const float*)alpha, *(const float*)beta, false);
+  }
+  if (alg == ALPHASPARSE_SPMM_CSR_ALG6) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;  // needs bf16 operands
+  const bool o64 = A->row_type == ALPHA_SPARSE_INDEXTYPE_I64;
+  if (A->data_type == ALPHA_R_32F) {
+    const float al = *(const float*)alpha, be = *(const float*)beta;
+    return o64 ? spmm_t<float, int64_t>(h, A, (const float*)B->values, B->ld, (float*)C->values, C->ld, al, be, n)
+               : spmm_t<float, int32_t>(h, A, (const float*)B->values, B->ld, (float*)C->values, C->ld, al, be, n);
+  }
+  const double al = *(const double*)alpha, be = *(const double*)beta;
+  return o64 ? spmm_t<double, int64_t>(h, A, (const double*)B->values, B->ld, (double*)C->values, C->ld, al, be, n)
+             : spmm_t<double, int32_t>(h, A, (const double*)B->values, B->ld, (double*)C->values, C->ld, al, be, n);
+}
+
+alphasparseStatus_t alphasparseSpMM_bufferSize(alphasparseHandle_t h, alphasparseOperation_t opA,
+                                               alphasparseOperation_t opB, const void* alpha,
+                                               alphasparseSpMatDescr_t A, alphasparseDnMatDescr_t B,
+                                               const void* beta, alphasparseDnMatDescr_t C,
+                                               alphasparseDataType computeType,
+                                               alphasparseSpMMAlg_t, size_t* bufferSize) {
+  if (!bufferSize) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  alphasparseStatus_t s = check_spmm_args(h, opA, opB, alpha, A, B, beta, C, computeType);
+  if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  *bufferSize = 256;  // no kernel of this path needs caller scratch; non-zero so cudaMalloc returns a pointer
+  return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+alphasparseStatus_t alphasparseSpMM_preprocess(alphasparseHandle_t h, alphasparseOperation_t opA,
+                                               alphasparseOperation_t opB, const void* alpha,
+                                               alphasparseSpMatDescr_t A, alphasparseDnMatDescr_t B,
+                                               const void* beta, alphasparseDnMatDescr_t C,
+                                               alphasparseDataType computeType,
+                                               alphasparseSpMMAlg_t, size_t* bufferSize) {
+  alphasparseStatus_t s = check_spmm_args(h, opA, opB, alpha, A, B, beta, C, computeType);
+  if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  if (bufferSize) *bufferSize = 256;
+  if (!A->info) {
+    s = analyse(h, A);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  }
+  if (A->data_type == ALPHA_R_16BF) {
+    if (!spmm_tc_applicable(A, B, C)) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    return spmm_tc_run(h, A, B, C, 0.f, 0.f, true);
+  }
+  return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,507 @@
+// CSR SpMV  y = alpha*A*x + beta*y  for sm_100a: the row-length-binned kernel and the
+// merge-path kernel, the dispatcher and the buffer-size query.
+//
+// Replaces, for CSR with opA = N, the reference's dispatcher
+// cuda/kernel/level2/alphasparse_spmv.cu:21-421 and its kernel headers
+// alphasparse_spmv_csr_{scalar,vector,adaptive2,line_enhance,flat,merge_ginkgo,
+// row_partition_ginkgo}.h.  Differences that matter to a caller:
+//   - every launch goes to handle->stream (several reference variants use the default
+//     stream or call cudaDeviceSynchronize, e.g. alphasparse_spmv_csr_merge_ginkgo.h:206,219
+//     and alphasparse_spmv_csr_row_partition_ginkgo.h:411,482);
+//   - partitioning is read from the analysed plan instead of being recomputed per call;
+//   - no atomics on y: a row is summed by one lane group, warp or CTA, and the merge-path
+//     kernel passes partial sums of rows that straddle CTAs through a carry array that a
+//     second small kernel adds in tile order, so results are reproducible run to run.
+#include <climits>
+#include <cstring>
+#include <type_traits>
+
+#include "asp_internal.h"
+
+namespace asp {
+namespace {
+
+template <typename T> struct VecTraits;
+template <> struct VecTraits<float> {
+  static constexpr int N = 4;
+  using V = float4;
+  using I = int4;
+};
+template <> struct VecTraits<double> {
+  static constexpr int N = 2;
+  using V = double2;
+  using I = int2;
+};
+
+template <typename OffT>
+using idx_t = typename std::conditional<std::is_same<OffT, int32_t>::value, uint32_t, int64_t>::type;
+
+// One 16-byte load of values and the matching column indices at entry k (k a multiple of
+// N), streamed past L1 and marked evict-first in L2 so that A does not displace x.  The last
+// partial chunk of the arrays, or arrays that are not 16-byte aligned (VL = false), are read
+// element by element.
+template <typename T, bool VL, typename IdxT>
+__device__ __forceinline__ void load_chunk(const T* __restrict__ val, const int* __restrict__ col,
+                                           IdxT k, IdxT nnz, T (&v)[VecTraits<T>::N],
+                                           int (&c)[VecTraits<T>::N]) {
+  constexpr int N = VecTraits<T>::N;
+  if (VL && k + N <= nnz) {
+    typename VecTraits<T>::V vv = __ldcs(reinterpret_cast<const typename VecTraits<T>::V*>(val + k));
+    typename VecTraits<T>::I cc = __ldcs(reinterpret_cast<const typename VecTraits<T>::I*>(col + k));
+    if constexpr (N == 4) {
+      v[0] = vv.x; v[1] = vv.y; v[2] = vv.z; v[3] = vv.w;
+      c[0] = cc.x; c[1] = cc.y; c[2] = cc.z; c[3] = cc.w;
+    } else {
+      v[0] = vv.x; v[1] = vv.y;
+      c[0] = cc.x; c[1] = cc.y;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      const bool in = k + j < nnz;
+      v[j] = in ? __ldcs(val + k + j) : T(0);
+      c[j] = in ? __ldcs(col + k + j) : 0;
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ T finish(T alpha, T sum, T beta, const T* y) {
+  return beta == T(0) ? alpha * sum : fma(alpha, sum, beta * (*y));
+}
+
+// ------------------------------------------------------------------------------------------
+// Row-length-binned kernel.  One launch; CTA index ranges select the class:
+//   [0, cta_short)                     short rows : G lanes per row, kShortUnroll rows in flight
+//   [cta_short, cta_short+cta_medium)  medium rows: one warp per row
+//   the rest                           long rows  : one CTA per row
+// Every lane reads 16-byte chunks that start at a multiple of N entries (the row start is
+// rounded down and the leading entries masked), so the loads of neighbouring lanes and of
+// neighbouring rows coalesce into full lines.
+// ------------------------------------------------------------------------------------------
+template <typename T, typename OffT>
+struct BinnedArgs {
+  const OffT* rp;
+  const int* col;
+  const T* val;
+  const T* x;
+  T* y;
+  T alpha, beta;
+  const int32_t* rows_short;   // nullptr: row i of the class is row i of the matrix
+  const int32_t* rows_medium;
+  const int32_t* rows_long;
+  int64_t n_short, n_medium, n_long, nnz;
+  int cta_short, cta_medium;
+};
+
+template <typename T, typename OffT, int G, bool VL>
+__global__ void __launch_bounds__(kThreads) spmv_binned_kernel(const BinnedArgs<T, OffT> a) {
+  constexpr int N = VecTraits<T>::N;
+  using IdxT = idx_t<OffT>;
+  const IdxT nnz = (IdxT)a.nnz;
+  const int b = blockIdx.x;
+  if (b < a.cta_short) {
+    constexpr int NG = kThreads / G;
+    constexpr int U = kShortUnroll;
+    const int lane = threadIdx.x & (G - 1);
+    const int grp = threadIdx.x / G;
+    const int64_t base = (int64_t)b * (NG * U);
+    int32_t row[U];
+    IdxT s[U], e[U], k[U];
+    T sum[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = base + u * NG + grp;
+      row[u] = i < a.n_short ? (a.rows_short ? a.rows_short[i] : (int32_t)i) : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      s[u] = row[u] >= 0 ? (IdxT)a.rp[row[u]] : 0;
+      e[u] = row[u] >= 0 ? (IdxT)a.rp[row[u] + 1] : 0;
+      k[u] = (s[u] & ~(IdxT)(N - 1)) + (IdxT)(lane * N);
+      sum[u] = T(0);
+    }
+    bool more = true;
+    while (more) {
+      more = false;
+      T v[U][N];
+      int c[U][N];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (k[u] < e[u]) load_chunk<T, VL, IdxT>(a.val, a.col, k[u], nnz, v[u], c[u]);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (k[u] < e[u]) {
+#pragma unroll
+          for (int j = 0; j < N; ++j) {
+            const IdxT kk = k[u] + j;
+            if (kk >= s[u] && kk < e[u]) sum[u] = fma(v[u][j], __ldg(a.x + c[u][j]), sum[u]);
+          }
+          k[u] += (IdxT)(G * N);
+          more |= k[u] < e[u];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int o = G / 2; o > 0; o >>= 1) sum[u] += __shfl_xor_sync(0xffffffffu, sum[u], o);
+      if (lane == 0 && row[u] >= 0) a.y[row[u]] = finish(a.alpha, sum[u], a.beta, a.y + row[u]);
+    }
+  } else if (b < a.cta_short + a.cta_medium) {
+    const int lane = threadIdx.x & 31;
+    const int64_t i = (int64_t)(b - a.cta_short) * (kThreads / 32) + (threadIdx.x >> 5);
+    if (i >= a.n_medium) return;  // whole warp leaves together
+    const int32_t row = a.rows_medium[i];
+    const IdxT s = (IdxT)a.rp[row], e = (IdxT)a.rp[row + 1];
+    T sum = T(0);
+    for (IdxT k = (s & ~(IdxT)(N - 1)) + (IdxT)(lane * N); k < e; k += 32 * N) {
+      T v[N];
+      int c[N];
+      load_chunk<T, VL, IdxT>(a.val, a.col, k, nnz, v, c);
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        const IdxT kk = k + j;
+        if (kk >= s && kk < e) sum = fma(v[j], __ldg(a.x + c[j]), sum);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) a.y[row] = finish(a.alpha, sum, a.beta, a.y + row);
+  } else {
+    __shared__ T s_part[kThreads / 32];
+    const int64_t i = (int64_t)(b - a.cta_short - a.cta_medium);
+    const int32_t row = a.rows_long[i];
+    const IdxT s = (IdxT)a.rp[row], e = (IdxT)a.rp[row + 1];
+    T sum = T(0);
+    for (IdxT k = (s & ~(IdxT)(N - 1)) + (IdxT)(threadIdx.x * N); k < e; k += kThreads * N) {
+      T v[N];
+      int c[N];
+      load_chunk<T, VL, IdxT>(a.val, a.col, k, nnz, v, c);
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        const IdxT kk = k + j;
+        if (kk >= s && kk < e) sum = fma(v[j], __ldg(a.x + c[j]), sum);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      T tot = T(0);
+#pragma unroll
+      for (int w = 0; w < kThreads / 32; ++w) tot += s_part[w];
+      a.y[row] = finish(a.alpha, tot, a.beta, a.y + row);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Merge-path kernel (Merrill & Garland's decomposition; the reference's version is
+// alphasparse_spmv_csr_merge_ginkgo.h:36-131).  CTA t owns items [t*kMergeItems, ...) of the
+// merge of the row-end offsets with the entry indices; its start coordinate comes from the
+// plan.  The CTA (1) streams its entries with coalesced 16-byte loads, multiplies by the
+// gathered x and parks the products in shared memory, (2) every thread walks kMergeIpt items
+// of the merge list serially, (3) a block-wide segmented scan hands partial sums of rows that
+// span threads forward, and the sum that leaves the tile goes to carry[t].
+// ------------------------------------------------------------------------------------------
+template <typename T, typename OffT, bool VL>
+__global__ void __launch_bounds__(kThreads)
+spmv_merge_kernel(const OffT* __restrict__ rp, const int* __restrict__ col,
+                  const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y, T alpha,
+                  T beta, int64_t rows, int64_t nnz64, const int32_t* __restrict__ tile_row,
+                  T* __restrict__ carry) {
+  constexpr int N = VecTraits<T>::N;
+  constexpr int IPT = kMergeIpt;
+  constexpr int ITEMS = kMergeItems;
+  constexpr int CH = ITEMS / (N * kThreads) + 1;
+  using IdxT = idx_t<OffT>;
+  __shared__ T s_prod[ITEMS];
+  __shared__ int s_rowend[ITEMS + 1];
+  __shared__ T s_wval[kThreads / 32];
+  __shared__ int s_wflag[kThreads / 32];
+
+  const int tid = threadIdx.x;
+  const int64_t t = blockIdx.x;
+  const int row_s = tile_row[t], row_e = tile_row[t + 1];
+  const int64_t diag_s = t * (int64_t)ITEMS;
+  int64_t diag_e = diag_s + ITEMS;
+  if (diag_e > rows + nnz64) diag_e = rows + nnz64;
+  const IdxT nz_s = (IdxT)(diag_s - row_s), nz_e = (IdxT)(diag_e - row_e);
+  const int tile_rows = row_e - row_s;
+  const int tile_nnz = (int)(nz_e - nz_s);
+  const IdxT nnz = (IdxT)nnz64;
+
+  // (1) products
+  {
+    const IdxT a0 = nz_s & ~(IdxT)(N - 1);
+    T v[CH][N];
+    int c[CH][N];
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const IdxT k = a0 + (IdxT)((i * kThreads + tid) * N);
+      if (k < nz_e) load_chunk<T, VL, IdxT>(val, col, k, nnz, v[i], c[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const IdxT k = a0 + (IdxT)((i * kThreads + tid) * N);
+      if (k < nz_e) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          const IdxT kk = k + j;
+          if (kk >= nz_s && kk < nz_e) s_prod[(int)(kk - nz_s)] = v[i][j] * __ldg(x + c[i][j]);
+        }
+      }
+    }
+  }
+  // row ends relative to the tile's first entry; the row still open at the tile end gets a
+  // sentinel so that the walk below only consumes entries once the row ends run out
+  for (int i = tid; i <= tile_rows; i += kThreads)
+    s_rowend[i] = i < tile_rows ? (int)((int64_t)rp[row_s + i + 1] - (int64_t)nz_s) : INT_MAX;
+  __syncthreads();
+
+  // (2) per-thread walk
+  const int tile_items = tile_rows + tile_nnz;
+  int d = tid * IPT;
+  if (d > tile_items) d = tile_items;
+  int d_end = d + IPT;
+  if (d_end > tile_items) d_end = tile_items;
+  int lo = d > tile_nnz ? d - tile_nnz : 0;
+  int hi = d < tile_rows ? d : tile_rows;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (s_rowend[mid] <= d - mid - 1) lo = mid + 1;
+    else hi = mid;
+  }
+  int i = lo, j = d - lo;
+  T running = T(0), first_val = T(0);
+  int first_row = -1;
+#pragma unroll
+  for (int it = 0; it < IPT; ++it) {
+    if (d + it < d_end) {
+      if (j < s_rowend[i]) {
+        running += s_prod[j];
+        ++j;
+      } else {
+        if (first_row < 0) {
+          first_row = i;
+          first_val = running;
+        } else {
+          y[row_s + i] = finish(alpha, running, beta, y + row_s + i);
+        }
+        running = T(0);
+        ++i;
+      }
+    }
+  }
+
+  // (3) segmented scan of the carry-outs: a thread that finished a row starts a new segment
+  const int lane = tid & 31, warp = tid >> 5;
+  int flag = first_row >= 0 ? 1 : 0;
+  T sv = running;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const T pv = __shfl_up_sync(0xffffffffu, sv, o);
+    const int pf = __shfl_up_sync(0xffffffffu, flag, o);
+    if (lane >= o) {
+      if (!flag) sv += pv;
+      flag |= pf;
+    }
+  }
+  if (lane == 31) {
+    s_wval[warp] = sv;
+    s_wflag[warp] = flag;
+  }
+  T ev = __shfl_up_sync(0xffffffffu, sv, 1);
+  int ef = __shfl_up_sync(0xffffffffu, flag, 1);
+  if (lane == 0) {
+    ev = T(0);
+    ef = 0;
+  }
+  __syncthreads();
+  T pv = T(0);  // sum flowing in from the warps before this one
+  for (int w = 0; w < warp; ++w) pv = s_wflag[w] ? s_wval[w] : pv + s_wval[w];
+  const T carry_in = ef ? ev : pv + ev;
+  if (first_row >= 0) {
+    const int r = row_s + first_row;
+    y[r] = finish(alpha, carry_in + first_val, beta, y + r);
+  }
+  if (tid == kThreads - 1) carry[t] = flag ? sv : pv + sv;
+}
+
+// Adds the sums that left tiles to the rows they belong to.  Tile t's carry belongs to row
+// tile_row[t+1].  The thread of the first tile of a run of tiles that all end inside the same
+// row adds the whole run, in tile order.
+template <typename T>
+__global__ void __launch_bounds__(256) spmv_merge_fixup_kernel(const int32_t* __restrict__ tile_row,
+                                                               const T* __restrict__ carry,
+                                                               int64_t tiles, int64_t rows,
+                                                               T* __restrict__ y, T alpha) {
+  const int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (t >= tiles) return;
+  const int32_t r = tile_row[t + 1];
+  if (r >= rows) return;
+  if (t > 0 && tile_row[t] == r) return;
+  T sum = T(0);
+  for (int64_t u = t; u < tiles && tile_row[u + 1] == r; ++u) sum += carry[u];
+  y[r] = fma(alpha, sum, y[r]);
+}
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+template <typename T, typename OffT, bool VL>
+alphasparseStatus_t launch_binned(alphasparseHandle_t h, const Plan* p, const BinnedArgs<T, OffT>& a0) {
+  BinnedArgs<T, OffT> a = a0;
+  const int g = p->group_lanes;
+  const int rows_per_cta = (kThreads / g) * kShortUnroll;
+  const int64_t cs = (p->n_short + rows_per_cta - 1) / rows_per_cta;
+  const int64_t cm = (p->n_medium + (kThreads / 32) - 1) / (kThreads / 32);
+  const int64_t total = cs + cm + p->n_long;
+  if (total > INT_MAX) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  if (total == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+  a.cta_short = (int)cs;
+  a.cta_medium = (int)cm;
+  const dim3 grid((unsigned)total), block(kThreads);
+  switch (g) {
+    case 2: spmv_binned_kernel<T, OffT, 2, VL><<<grid, block, 0, h->stream>>>(a); break;
+    case 4: spmv_binned_kernel<T, OffT, 4, VL><<<grid, block, 0, h->stream>>>(a); break;
+    case 8: spmv_binned_kernel<T, OffT, 8, VL><<<grid, block, 0, h->stream>>>(a); break;
+    case 16: spmv_binned_kernel<T, OffT, 16, VL><<<grid, block, 0, h->stream>>>(a); break;
+    default: spmv_binned_kernel<T, OffT, 32, VL><<<grid, block, 0, h->stream>>>(a); break;
+  }
+  impl(h)->launches++;
+  return status_of(cudaGetLastError());
+}
+
+template <typename T, typename OffT>
+alphasparseStatus_t spmv_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, Plan* p, const T* x,
+                           T* y, T alpha, T beta, int variant, void* ext) {
+  const OffT* rp = reinterpret_cast<const OffT*>(A->row_offsets);
+  const int* col = A->const_col_data;
+  const T* val = reinterpret_cast<const T*>(A->const_val_data);
+  const bool vl = aligned(val, 16) && aligned(col, 16);
+  if (p->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+  if (variant == kVariantBinned) {
+    BinnedArgs<T, OffT> a;
+    a.rp = rp; a.col = col; a.val = val; a.x = x; a.y = y; a.alpha = alpha; a.beta = beta;
+    a.rows_short = p->identity_short ? nullptr : p->bin_rows;
+    a.rows_medium = p->identity_short ? nullptr : p->bin_rows + p->n_short;
+    a.rows_long = p->identity_short ? nullptr : p->bin_rows + p->n_short + p->n_medium;
+    a.n_short = p->n_short; a.n_medium = p->n_medium; a.n_long = p->n_long; a.nnz = p->nnz;
+    a.cta_short = a.cta_medium = 0;
+    return vl ? launch_binned<T, OffT, true>(h, p, a) : launch_binned<T, OffT, false>(h, p, a);
+  }
+  T* carry = reinterpret_cast<T*>(ext ? ext : p->carry);
+  if (p->merge_tiles > INT_MAX) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  const dim3 grid((unsigned)p->merge_tiles), block(kThreads);
+  if (vl)
+    spmv_merge_kernel<T, OffT, true><<<grid, block, 0, h->stream>>>(
+        rp, col, val, x, y, alpha, beta, p->rows, p->nnz, p->merge_tile_row, carry);
+  else
+    spmv_merge_kernel<T, OffT, false><<<grid, block, 0, h->stream>>>(
+        rp, col, val, x, y, alpha, beta, p->rows, p->nnz, p->merge_tile_row, carry);
+  spmv_merge_fixup_kernel<T><<<(unsigned)((p->merge_tiles + 255) / 256), 256, 0, h->stream>>>(
+      p->merge_tile_row, carry, p->merge_tiles, p->rows, y, alpha);
+  impl(h)->launches += 2;
+  return status_of(cudaGetLastError());
+}
+
+int variant_for(const Plan* p, alphasparseSpMVAlg_t alg) {
+  const char* f = getenv("ASP_SPMV_VARIANT");
+  if (f && !strcmp(f, "binned")) return kVariantBinned;
+  if (f && !strcmp(f, "merge")) return kVariantMerge;
+  switch (alg) {
+    case ALPHA_SPARSE_SPMV_ALG_SCALAR:
+    case ALPHA_SPARSE_SPMV_ALG_VECTOR:
+    case ALPHA_SPARSE_SPMV_ADAPTIVE:
+    case ALPHA_SPARSE_SPMV_ALG_CSR_ADAPTIVE:
+    case ALPHA_SPARSE_SPMV_ALG_LINE:
+    case ALPHA_SPARSE_SPMV_ALG_LINE_ENHANCE:
+    case ALPHA_SPARSE_SPMV_ALG_ACC:
+      return kVariantBinned;
+    case ALPHA_SPARSE_SPMV_ALG_MERGE:
+    case ALPHA_SPARSE_SPMV_ROW_PARTITION:
+    case ALPHA_SPARSE_SPMV_ALG_LOAD_BALANCE:
+    case ALPHA_SPARSE_SPMV_ALG_CSR_STREAM:
+    case ALPHA_SPARSE_SPMV_ALG_FLAT:
+    case ALPHA_SPARSE_SPMV_ALG_FLAT1:
+    case ALPHA_SPARSE_SPMV_ALG_FLAT4:
+    case ALPHA_SPARSE_SPMV_ALG_FLAT8:
+    case ALPHA_SPARSE_SPMV_ALG_PFLAT:
+      return kVariantMerge;
+    default:
+      return p->variant_auto;
+  }
+}
+
+alphasparseStatus_t check_spmv_args(alphasparseHandle_t h, alphasparseOperation_t opA,
+                                    const void* alpha, alphasparseSpMatDescr_t A,
+                                    alphasparseDnVecDescr_t x, const void* beta,
+                                    alphasparseDnVecDescr_t y, alphasparseDataType computeType) {
+  if (!h || !h->impl) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+  if (!alpha || !beta || !A || !x || !y) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  if (h->pointer_mode != ALPHA_SPARSE_POINTER_MODE_HOST) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (opA != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  alphasparseStatus_t s = validate_csr(A);
+  if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  if (!x->init || !y->init) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+  if (A->data_type != ALPHA_R_32F && A->data_type != ALPHA_R_64F) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (x->data_type != A->data_type || y->data_type != A->data_type || computeType != A->data_type)
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (x->size != A->cols || y->size != A->rows) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  if ((A->cols > 0 && !x->values) || (A->rows > 0 && !y->values)) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+}  // namespace
+}  // namespace asp
+
+using namespace asp;
+
+extern "C" {
+
+alphasparseStatus_t alphasparseSpMV(alphasparseHandle_t h, alphasparseOperation_t opA,
+                                    const void* alpha, alphasparseSpMatDescr_t A,
+                                    alphasparseDnVecDescr_t x, const void* beta,
+                                    alphasparseDnVecDescr_t y, alphasparseDataType computeType,
+                                    alphasparseSpMVAlg_t alg, void* externalBuffer) {
+  alphasparseStatus_t s = check_spmv_args(h, opA, alpha, A, x, beta, y, computeType);
+  if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  if (!A->info) {
+    s = analyse(h, A);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  }
+  Plan* p = plan_of(A);
+  if (p->rows != A->rows || p->nnz != A->nnz || p->cols != A->cols) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+  const int variant = variant_for(p, alg);
+  p->last_variant = variant;
+  const bool o64 = A->row_type == ALPHA_SPARSE_INDEXTYPE_I64;
+  if (A->data_type == ALPHA_R_32F) {
+    const float al = *(const float*)alpha, be = *(const float*)beta;
+    return o64 ? spmv_t<float, int64_t>(h, A, p, (const float*)x->values, (float*)y->values, al, be, variant, externalBuffer)
+               : spmv_t<float, int32_t>(h, A, p, (const float*)x->values, (float*)y->values, al, be, variant, externalBuffer);
+  }
+  const double al = *(const double*)alpha, be = *(const double*)beta;
+  return o64 ? spmv_t<double, int64_t>(h, A, p, (const double*)x->values, (double*)y->values, al, be, variant, externalBuffer)
+             : spmv_t<double, int32_t>(h, A, p, (const double*)x->values, (double*)y->values, al, be, variant, externalBuffer);
+}
+
+alphasparseStatus_t alphasparseSpMV_bufferSize(alphasparseHandle_t h, alphasparseOperation_t opA,
+                                               const void* alpha, alphasparseSpMatDescr_t A,
+                                               alphasparseDnVecDescr_t x, const void* beta,
+                                               alphasparseDnVecDescr_t y,
+                                               alphasparseDataType computeType,
+                                               alphasparseSpMVAlg_t, size_t* bufferSize) {
+  if (!bufferSize) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  alphasparseStatus_t s = check_spmv_args(h, opA, alpha, A, x, beta, y, computeType);
+  if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  // One carry slot per merge-path tile, in 64-bit arithmetic (the reference adds rows+nnz in
+  // int, cuda/kernel/level2/alphasparse_spmv.cu:357).
+  const int64_t tiles = (A->rows + A->nnz + kMergeItems - 1) / kMergeItems;
+  size_t bytes = (size_t)(tiles > 0 ? tiles : 1) * elem_size(A->data_type);
+  *bufferSize = (bytes + 255) & ~(size_t)255;
+  return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,155 @@
+/* TEST INFRASTRUCTURE ONLY: the CPU oracle for the CSR SpMV / SpMM path.
+ *
+ * A plain-C restatement of the arithmetic the reference's x86 (hygon) backend performs for
+ * y = alpha*A*x + beta*y and Y = alpha*A*X + beta*Y on a general CSR matrix.  Only tests,
+ * the smoke check and the CPU-baseline leg of the benchmark may load this library; the
+ * product (the CUDA library) never does.
+ *
+ * Pinning: the reference holds no golden vectors for this path (its tests are differential
+ * against MKL / cuSPARSE).  The pin is the reference code itself: oracle/Makefile compiles
+ * the hygon sources in place into oracle/_ref/libasp_ref.so, tests/golden/make_golden.py ran
+ * it on seeded inputs and committed input seeds + output digests/vectors, and
+ * tests/test_oracle.py checks this restatement against those vectors (bit-exact for SpMV,
+ * where the summation order below is the assembly's) and against the live library when it
+ * is present.
+ *
+ * Reference code restated (paths within the reference project):
+ *   hygon/kernel/level2/mv/gemv/gemv_csr.hpp:14-78        row loop, one call per thread range
+ *   hygon/kernel/level2/mv/gemv/csrmv/gemv_csr_serial_fma_fp64_u4.S:47-150
+ *        fp64 row: four FMA partial sums p0..p3 over groups of four entries,
+ *        s = (p0+p2)+(p1+p3), then up to three scalar-FMA tail entries,
+ *        y = fma(alpha, s, beta*y)
+ *   hygon/kernel/level2/mv/gemv/csrmv/gemv_sload_shuffle_shuffle_reduce_128.S:15-185
+ *        fp32 row: the same with s = (p0+p1)+(p2+p3)
+ *   hygon/kernel/level3/mm/gemm/gemm_csr_row.hpp:15-73,124-158
+ *        Y[r,:] *= beta, then for each entry of row r in storage order
+ *        Y[r,c] = fma(alpha*a, X[col,c], Y[r,c])
+ *   hygon/util/partition.cpp:83-96    balanced_partition_row_by_nnz (lifted to int64 here)
+ *
+ * The reference is int32-only; the _i64 variants take 64-bit row offsets with the same
+ * per-row arithmetic, for matrices whose nnz does not fit 32 bits.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stddef.h>
+#include <string.h>
+
+#define DEF_SPMV_F64(NAME, OFF_T)                                                          \
+  void NAME(int64_t rows, const OFF_T* row_ptr, const int32_t* col, const double* val,     \
+            const double* x, double alpha, double beta, double* y) {                       \
+    _Pragma("omp parallel for schedule(static)")                                           \
+    for (int64_t i = 0; i < rows; ++i) {                                                   \
+      int64_t k = (int64_t)row_ptr[i], e = (int64_t)row_ptr[i + 1];                        \
+      double p0 = 0, p1 = 0, p2 = 0, p3 = 0, s = 0;                                        \
+      if (k < e - 3) {                                                                     \
+        for (; k < e - 3; k += 4) {                                                        \
+          p0 = fma(val[k], x[col[k]], p0);                                                 \
+          p1 = fma(val[k + 1], x[col[k + 1]], p1);                                         \
+          p2 = fma(val[k + 2], x[col[k + 2]], p2);                                         \
+          p3 = fma(val[k + 3], x[col[k + 3]], p3);                                         \
+        }                                                                                  \
+        s = (p0 + p2) + (p1 + p3);                                                         \
+      }                                                                                    \
+      for (; k < e; ++k) s = fma(val[k], x[col[k]], s);                                    \
+      y[i] = fma(alpha, s, beta * y[i]);                                                   \
+    }                                                                                      \
+  }
+
+#define DEF_SPMV_F32(NAME, OFF_T)                                                          \
+  void NAME(int64_t rows, const OFF_T* row_ptr, const int32_t* col, const float* val,      \
+            const float* x, float alpha, float beta, float* y) {                           \
+    _Pragma("omp parallel for schedule(static)")                                           \
+    for (int64_t i = 0; i < rows; ++i) {                                                   \
+      int64_t k = (int64_t)row_ptr[i], e = (int64_t)row_ptr[i + 1];                        \
+      float p0 = 0, p1 = 0, p2 = 0, p3 = 0, s = 0;                                         \
+      if (k < e - 3) {                                                                     \
+        for (; k < e - 3; k += 4) {                                                        \
+          p0 = fmaf(val[k], x[col[k]], p0);                                                \
+          p1 = fmaf(val[k + 1], x[col[k + 1]], p1);                                        \
+          p2 = fmaf(val[k + 2], x[col[k + 2]], p2);                                        \
+          p3 = fmaf(val[k + 3], x[col[k + 3]], p3);                                        \
+        }                                                                                  \
+        s = (p0 + p1) + (p2 + p3);                                                         \
+      }                                                                                    \
+      for (; k < e; ++k) s = fmaf(val[k], x[col[k]], s);                                   \
+      y[i] = fmaf(alpha, s, beta * y[i]);                                                  \
+    }                                                                                      \
+  }
+
+DEF_SPMV_F64(oracle_spmv_f64_i32, int32_t)
+DEF_SPMV_F64(oracle_spmv_f64_i64, int64_t)
+DEF_SPMV_F32(oracle_spmv_f32_i32, int32_t)
+DEF_SPMV_F32(oracle_spmv_f32_i64, int64_t)
+
+/* Row-major SpMM, X is cols x n with leading dimension ldx, Y is rows x n with ldy. */
+#define DEF_SPMM(NAME, T, OFF_T, FMA)                                                      \
+  void NAME(int64_t rows, const OFF_T* row_ptr, const int32_t* col, const T* val,          \
+            const T* X, int64_t n, int64_t ldx, T alpha, T beta, T* Y, int64_t ldy) {      \
+    _Pragma("omp parallel for schedule(static)")                                           \
+    for (int64_t i = 0; i < rows; ++i) {                                                   \
+      T* yr = Y + i * ldy;                                                                 \
+      for (int64_t c = 0; c < n; ++c) yr[c] = yr[c] * beta;                                \
+      for (int64_t k = (int64_t)row_ptr[i]; k < (int64_t)row_ptr[i + 1]; ++k) {            \
+        const T a = alpha * val[k];                                                        \
+        const T* xr = X + (int64_t)col[k] * ldx;                                           \
+        for (int64_t c = 0; c < n; ++c) yr[c] = FMA(a, xr[c], yr[c]);                      \
+      }                                                                                    \
+    }                                                                                      \
+  }
+
+DEF_SPMM(oracle_spmm_f32_i32, float, int32_t, fmaf)
+DEF_SPMM(oracle_spmm_f32_i64, float, int64_t, fmaf)
+DEF_SPMM(oracle_spmm_f64_i32, double, int32_t, fma)
+DEF_SPMM(oracle_spmm_f64_i64, double, int64_t, fma)
+
+/* bf16 operands (A values and X stored as the upper 16 bits of an IEEE float), fp32
+ * accumulation and fp32 Y: the arithmetic of the tensor-core SpMM variant, which the
+ * reference does not have (its bf16 dispatch is commented out,
+ * cuda/kernel/level3/alphasparse_spmm.cu:597-610).  Same loop as above after widening. */
+static inline float bf16_to_f32(uint16_t h) {
+  uint32_t u = (uint32_t)h << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+void oracle_spmm_bf16_i32(int64_t rows, const int32_t* row_ptr, const int32_t* col,
+                          const uint16_t* val, const uint16_t* X, int64_t n, int64_t ldx,
+                          float alpha, float beta, float* Y, int64_t ldy) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < rows; ++i) {
+    float* yr = Y + i * ldy;
+    for (int64_t c = 0; c < n; ++c) yr[c] = yr[c] * beta;
+    for (int64_t k = row_ptr[i]; k < row_ptr[i + 1]; ++k) {
+      const float a = alpha * bf16_to_f32(val[k]);
+      const uint16_t* xr = X + (int64_t)col[k] * ldx;
+      for (int64_t c = 0; c < n; ++c) yr[c] = fmaf(a, bf16_to_f32(xr[c]), yr[c]);
+    }
+  }
+}
+
+/* Contiguous row ranges of near-equal nnz: bound[0]=0, bound[parts]=rows and
+ * bound[i] = first index j in [0, rows-1] with row_end[j] >= (nnz/parts)*i, where
+ * row_end = row_ptr+1 (hygon/util/partition.cpp:83-96 with lower_bound_int :41-57). */
+#define DEF_PARTITION(NAME, OFF_T)                                                         \
+  void NAME(const OFF_T* row_ptr, int64_t rows, int64_t parts, int64_t* bound) {           \
+    const OFF_T* row_end = row_ptr + 1;                                                    \
+    bound[0] = 0;                                                                          \
+    if (rows <= 0) {                                                                       \
+      for (int64_t i = 1; i <= parts; ++i) bound[i] = 0;                                   \
+      return;                                                                              \
+    }                                                                                      \
+    int64_t nnz = (int64_t)row_end[rows - 1];                                              \
+    int64_t ave = nnz / parts;                                                             \
+    for (int64_t i = 1; i < parts; ++i) {                                                  \
+      int64_t l = 0, r = rows - 1, v = ave * i;                                            \
+      while (r > l) {                                                                      \
+        int64_t m = (l + r) / 2;                                                           \
+        if ((int64_t)row_end[m] < v) l = m + 1; else r = m;                                \
+      }                                                                                    \
+      bound[i] = l;                                                                        \
+    }                                                                                      \
+    bound[parts] = rows;                                                                   \
+  }
+
+DEF_PARTITION(oracle_partition_rows_by_nnz_i32, int32_t)
+DEF_PARTITION(oracle_partition_rows_by_nnz_i64, int64_t)

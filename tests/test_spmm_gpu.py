@@ -1,0 +1,114 @@
+"""CUDA SpMM through the C ABI against the CPU oracle and the reference-made golden vectors.
+
+The SIMT kernel accumulates every C element in the same order and with the same fma as the
+reference's CPU kernel, so fp32 / fp64 results are compared bit for bit as well as within the
+stated tolerance (relative L2 1e-5 fp32, 1e-12 fp64)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import load_golden, rel_l2
+from library_b200 import api
+from library_b200 import generators as G
+
+pytestmark = pytest.mark.gpu
+TOL = {np.dtype(np.float32): 1e-5, np.dtype(np.float64): 1e-12}
+MM_CASES = sorted(k for k, c in load_golden().items() if c["kind"] == "mm")
+
+
+def run_spmm(handle, rp, ci, v, X, alpha, beta, Y0, cols, ldx=None, ldy=None):
+    dev = "cuda"
+    A = api.CsrMatrix(len(rp) - 1, cols, torch.from_numpy(rp).to(dev), torch.from_numpy(ci).to(dev),
+                      torch.from_numpy(v).to(dev))
+    n = X.shape[1]
+    Xt = torch.from_numpy(X).to(dev)
+    Yt = torch.from_numpy(np.array(Y0, copy=True)).to(dev)
+    if ldx:
+        buf = torch.zeros(X.shape[0], ldx, dtype=Xt.dtype, device=dev)
+        buf[:, :n] = Xt
+        Xt = buf[:, :n]
+    if ldy:
+        buf = torch.full((Y0.shape[0], ldy), 7.0, dtype=Yt.dtype, device=dev)
+        buf[:, :n] = Yt
+        Yt = buf[:, :n]
+    handle.use_torch_stream()
+    api.spmm(handle, A, api.DnMat(Xt), api.DnMat(Yt), alpha, beta)
+    torch.cuda.synchronize()
+    if ldy:
+        assert bool((buf[:, n:] == 7.0).all())  # padding untouched
+    return Yt.cpu().numpy()
+
+
+@pytest.mark.parametrize("name", MM_CASES)
+def test_golden(handle, golden, name):
+    c = golden[name]
+    Y = run_spmm(handle, c["rp"], c["ci"], c["v"], c["x"], c["alpha"], c["beta"], c["y0"], c["cols"])
+    assert rel_l2(Y, c["y"]) <= TOL[c["v"].dtype]
+    assert np.array_equal(Y, c["y"])
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("n", [1, 3, 4, 8, 20, 32, 64, 128, 130, 256])
+def test_stencil_against_oracle(handle, dtype, n):
+    t = torch.float32 if dtype == np.float32 else torch.float64
+    A = G.stencil_3d_27pt(12, seed=4, dtype=t)
+    rp, ci, v = A.numpy()
+    X = G.uniform((A.cols, n), -1, 1, dtype=t, seed=60 + n).numpy()
+    Y0 = G.uniform((A.rows, n), -1, 1, dtype=t, seed=61 + n).numpy()
+    for alpha, beta in ((1.0, 0.0), (0.5, -1.5)):
+        want = oracle.spmm(rp, ci, v, X, alpha, beta, Y0)
+        got = run_spmm(handle, rp, ci, v, X, alpha, beta, Y0, A.cols)
+        assert rel_l2(got, want) <= TOL[np.dtype(dtype)]
+        assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("n", [8, 32])
+def test_skewed_and_long_rows(handle, n):
+    """Empty rows and rows longer than the shared-memory staging chunk."""
+    A = G.rmat(13, 16, seed=71)
+    rp, ci, v = A.numpy()
+    assert np.diff(rp).max() > 1024 and (np.diff(rp) == 0).any()
+    X = G.uniform((A.cols, n), -1, 1, seed=72).numpy()
+    Y0 = G.uniform((A.rows, n), -1, 1, seed=73).numpy()
+    want = oracle.spmm(rp, ci, v, X, 1.0, 1.0, Y0)
+    got = run_spmm(handle, rp, ci, v, X, 1.0, 1.0, Y0, A.cols)
+    assert np.array_equal(got, want)
+
+
+def test_leading_dimensions_and_i64_offsets(handle):
+    A = G.poisson_random(700, 900, mean_len=6, seed=81)
+    rp, ci, v = A.numpy()
+    X = G.uniform((A.cols, 12), -1, 1, seed=82).numpy()
+    Y0 = G.uniform((A.rows, 12), -1, 1, seed=83).numpy()
+    want = oracle.spmm(rp, ci, v, X, 2.0, 0.5, Y0)
+    assert np.array_equal(run_spmm(handle, rp, ci, v, X, 2.0, 0.5, Y0, A.cols, ldx=16, ldy=20), want)
+    assert np.array_equal(run_spmm(handle, rp, ci, v, X, 2.0, 0.5, Y0, A.cols, ldx=13, ldy=12), want)
+    assert np.array_equal(run_spmm(handle, rp.astype(np.int64), ci, v, X, 2.0, 0.5, Y0, A.cols), want)
+
+
+def test_status_codes(handle):
+    import ctypes as C
+    lib = api.load()
+    A = G.poisson_random(10, 12, mean_len=3, seed=91)
+    Am = api.CsrMatrix.from_csr(A)
+    B = api.DnMat(torch.zeros(12, 8, device="cuda"))
+    Cm = api.DnMat(torch.zeros(10, 8, device="cuda"))
+    one = C.c_float(1.0)
+
+    def call(opa=0, opb=0, b=B.d, c=Cm.d, ct=api.R_32F, alg=0):
+        return lib.alphasparseSpMM(handle.h, opa, opb, C.byref(one), Am.d, b, C.byref(one), c, ct, alg, None)
+    assert call() == 0
+    assert call(opa=1) == 6 and call(opb=1) == 6
+    assert call(b=api.DnMat(torch.zeros(11, 8, device="cuda")).d) == 10
+    assert call(c=api.DnMat(torch.zeros(10, 4, device="cuda")).d) == 10
+    assert call(ct=api.R_64F) == 6
+    d = C.c_void_p()
+    t = torch.zeros(12, 8, device="cuda")
+    assert lib.alphasparseCreateDnMat(C.byref(d), C.c_int64(12), C.c_int64(8), C.c_int64(12),
+                                      C.c_void_p(t.data_ptr()), api.R_32F, api.ORDER_COL) == 0
+    assert call(b=d) == 6  # column-major operands are not supported
+    lib.alphasparseDestroyDnMat(d)
+    size = C.c_size_t()
+    assert lib.alphasparseSpMM_bufferSize(handle.h, 0, 0, C.byref(one), Am.d, B.d, C.byref(one), Cm.d,
+                                          api.R_32F, 0, C.byref(size)) == 0 and size.value > 0

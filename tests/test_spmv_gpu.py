@@ -1,0 +1,275 @@
+"""CUDA SpMV through the C ABI against the CPU oracle (the restated arithmetic of the
+reference's hygon CSR mv) and against the golden vectors made by the reference's own code.
+
+Tolerances (relative L2): fp32 1e-5, fp64 1e-12.  Preprocessing output is compared bit for bit
+with the numpy twin in tests/preprocess_twin.py.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import preprocess_twin as twin
+from conftest import load_golden, rel_l2
+from library_b200 import api
+from library_b200 import generators as G
+
+pytestmark = pytest.mark.gpu
+TOL = {np.dtype(np.float32): 1e-5, np.dtype(np.float64): 1e-12}
+MV_CASES = sorted(k for k, c in load_golden().items() if c["kind"] == "mv")
+VARIANTS = ["binned", "merge"]
+
+
+def run_spmv(handle, rp, ci, v, x, alpha, beta, y0, cols, variant=None, alg=api.SPMV_ALG_DEFAULT,
+             use_buffer=False):
+    dev = "cuda"
+    A = api.CsrMatrix(len(rp) - 1, cols, torch.from_numpy(rp).to(dev), torch.from_numpy(ci).to(dev),
+                      torch.from_numpy(v).to(dev))
+    xd = api.DnVec(torch.from_numpy(x).to(dev))
+    yt = torch.from_numpy(np.array(y0, copy=True)).to(dev)
+    yd = api.DnVec(yt)
+    buf = None
+    if use_buffer:
+        buf = torch.empty(api.spmv_buffer_size(handle, A, xd, yd, alpha, beta, alg), dtype=torch.uint8, device=dev)
+    old = os.environ.pop("ASP_SPMV_VARIANT", None)
+    if variant:
+        os.environ["ASP_SPMV_VARIANT"] = variant
+    try:
+        handle.use_torch_stream()
+        api.spmv(handle, A, xd, yd, alpha, beta, alg=alg, buffer=buf)
+        torch.cuda.synchronize()
+    finally:
+        os.environ.pop("ASP_SPMV_VARIANT", None)
+        if old is not None:
+            os.environ["ASP_SPMV_VARIANT"] = old
+    return yt.cpu().numpy(), A
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("name", MV_CASES)
+def test_golden(handle, golden, name, variant):
+    c = golden[name]
+    y, A = run_spmv(handle, c["rp"], c["ci"], c["v"], c["x"], c["alpha"], c["beta"], c["y0"], c["cols"], variant)
+    assert A.last_variant() == variant
+    assert rel_l2(y, c["y"]) <= TOL[c["v"].dtype]
+
+
+def _mk(kind, dtype):
+    t = torch.float32 if dtype == np.float32 else torch.float64
+    if kind == "lap2d":
+        return G.laplacian_2d_5pt(96, dtype=t)
+    if kind == "poisson":
+        return G.poisson_random(50000, mean_len=16, seed=21, dtype=t)
+    if kind == "poisson_wide":
+        return G.poisson_random(3000, 100000, mean_len=300, seed=22, dtype=t)
+    if kind == "rmat":
+        return G.rmat(15, 16, seed=23, dtype=t)
+    if kind == "s27":
+        return G.stencil_3d_27pt(24, seed=24, dtype=t)
+    if kind == "lap3d_i64":
+        return G.laplacian_3d_7pt(40, dtype=t, index64=True)
+    if kind == "tiny":
+        return G.poisson_random(3, 5, mean_len=2, seed=25, dtype=t)
+    raise KeyError(kind)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("kind", ["lap2d", "poisson", "poisson_wide", "rmat", "s27", "lap3d_i64", "tiny"])
+def test_against_oracle(handle, kind, dtype, variant):
+    A = _mk(kind, dtype)
+    rp, ci, v = A.numpy()
+    t = torch.float32 if dtype == np.float32 else torch.float64
+    x = G.uniform((A.cols,), -1, 1, dtype=t, seed=31).numpy()
+    y0 = G.uniform((A.rows,), -1, 1, dtype=t, seed=32).numpy()
+    for alpha, beta in ((1.0, 0.0), (1.5, 0.5)):
+        want = oracle.spmv(rp, ci, v, x, alpha, beta, y0)
+        got, _ = run_spmv(handle, rp, ci, v, x, alpha, beta, y0, A.cols, variant, use_buffer=(beta != 0))
+        assert rel_l2(got, want) <= TOL[np.dtype(dtype)], (kind, alpha, beta)
+
+
+def _skewed(dtype):
+    """Empty rows, a few rows far beyond the CTA-per-row threshold, unaligned row starts."""
+    rng = np.random.default_rng(5)
+    rows, cols = 5000, 40000
+    lens = rng.integers(0, 12, size=rows)
+    lens[rng.random(rows) < 0.4] = 0
+    lens[7] = 30000
+    lens[8] = 1
+    lens[4000] = 5000
+    lens[4999] = 4097
+    lens[123] = 65
+    lens[124] = 64
+    rp = np.zeros(rows + 1, dtype=np.int32)
+    rp[1:] = np.cumsum(lens)
+    ci = np.concatenate([np.sort(rng.choice(cols, size=l, replace=False)) for l in lens]).astype(np.int32)
+    v = rng.standard_normal(rp[-1]).astype(dtype)
+    return rp, ci, v, cols
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_skewed_rows(handle, dtype, variant):
+    rp, ci, v, cols = _skewed(dtype)
+    rng = np.random.default_rng(6)
+    x = rng.uniform(-1, 1, cols).astype(dtype)
+    y0 = rng.uniform(-1, 1, len(rp) - 1).astype(dtype)
+    for alpha, beta in ((1.0, 0.0), (-2.0, 0.25)):
+        want = oracle.spmv(rp, ci, v, x, alpha, beta, y0)
+        got, _ = run_spmv(handle, rp, ci, v, x, alpha, beta, y0, cols, variant)
+        assert rel_l2(got, want) <= TOL[np.dtype(dtype)]
+        # rows with no entries: exactly beta*y0
+        empty = np.diff(rp) == 0
+        assert np.array_equal(got[empty], (np.array(beta, dtype) * y0[empty]) if beta else np.zeros(empty.sum(), dtype))
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_one_row_spanning_many_tiles(handle, variant):
+    """A single row of 50,000 entries between empty rows: the merge-path carry chain."""
+    rows, cols, L = 9, 60000, 50000
+    rp = np.array([0, 0, 0, L, L, L, L + 3, L + 3, L + 3, L + 3], dtype=np.int32)
+    rng = np.random.default_rng(9)
+    ci = np.concatenate([np.sort(rng.choice(cols, L, replace=False)), [1, 5, 9]]).astype(np.int32)
+    v = rng.standard_normal(L + 3)
+    x = rng.uniform(-1, 1, cols)
+    y0 = rng.uniform(-1, 1, rows)
+    want = oracle.spmv(rp, ci, v, x, 0.5, 2.0, y0)
+    got, _ = run_spmv(handle, rp, ci, v, x, 0.5, 2.0, y0, cols, variant)
+    assert rel_l2(got, want) <= 1e-12
+
+
+def test_unaligned_arrays_use_scalar_loads(handle):
+    """Value / column arrays that do not start on a 16-byte boundary."""
+    A = G.poisson_random(4000, mean_len=9, seed=41)
+    rp, ci, v = A.numpy()
+    x = G.uniform((A.cols,), -1, 1, seed=42).numpy()
+    want = oracle.spmv(rp, ci, v, x, 1.0, 0.0)
+    dev = "cuda"
+    cbuf = torch.zeros(len(ci) + 1, dtype=torch.int32, device=dev)
+    vbuf = torch.zeros(len(v) + 1, dtype=torch.float32, device=dev)
+    cbuf[1:] = torch.from_numpy(ci).to(dev)
+    vbuf[1:] = torch.from_numpy(v).to(dev)
+    for variant in VARIANTS:
+        Am = api.CsrMatrix(A.rows, A.cols, torch.from_numpy(rp).to(dev), cbuf[1:], vbuf[1:])
+        xd = api.DnVec(torch.from_numpy(x).to(dev))
+        yt = torch.zeros(A.rows, dtype=torch.float32, device=dev)
+        os.environ["ASP_SPMV_VARIANT"] = variant
+        try:
+            api.spmv(handle, Am, xd, api.DnVec(yt))
+        finally:
+            os.environ.pop("ASP_SPMV_VARIANT")
+        torch.cuda.synchronize()
+        assert rel_l2(yt.cpu().numpy(), want) <= 1e-5
+
+
+def test_beta_zero_does_not_read_y(handle):
+    A = G.laplacian_2d_5pt(20, dtype=torch.float32)
+    rp, ci, v = A.numpy()
+    x = np.ones(A.cols, np.float32)
+    y0 = np.full(A.rows, np.nan, np.float32)
+    for variant in VARIANTS:
+        got, _ = run_spmv(handle, rp, ci, v, x, 1.0, 0.0, y0, A.cols, variant)
+        assert np.isfinite(got).all()
+
+
+@pytest.mark.parametrize("kind", ["lap2d", "poisson", "rmat", "lap3d_i64"])
+def test_preprocessing_bit_exact(handle, kind):
+    A = _mk(kind, np.float32)
+    Am = api.CsrMatrix.from_csr(A)
+    Am.analyse(handle)
+    stats, bins, tiles = Am.plan(handle)
+    rp, _, _ = A.numpy()
+    want_stats, want_bins, want_tiles = twin.plan(rp, 4)
+    assert stats == want_stats
+    assert np.array_equal(bins, want_bins)
+    assert np.array_equal(tiles, want_tiles)
+
+
+def test_preprocessing_skewed_bit_exact(handle):
+    rp, ci, v, cols = _skewed(np.float64)
+    dev = "cuda"
+    Am = api.CsrMatrix(len(rp) - 1, cols, torch.from_numpy(rp).to(dev), torch.from_numpy(ci).to(dev),
+                       torch.from_numpy(v).to(dev))
+    Am.analyse(handle)
+    stats, bins, tiles = Am.plan(handle)
+    want_stats, want_bins, want_tiles = twin.plan(rp, 8)
+    assert stats == want_stats and np.array_equal(bins, want_bins) and np.array_equal(tiles, want_tiles)
+    assert stats["num_long"] == 3 and stats["num_medium"] == 1 and stats["variant"] == 1
+
+
+def test_results_reproducible_run_to_run(handle):
+    A = _mk("rmat", np.float32)
+    rp, ci, v = A.numpy()
+    x = G.uniform((A.cols,), 0, 1, seed=51).numpy()
+    for variant in VARIANTS:
+        a, _ = run_spmv(handle, rp, ci, v, x, 1.0, 0.0, np.zeros(A.rows, np.float32), A.cols, variant)
+        b, _ = run_spmv(handle, rp, ci, v, x, 1.0, 0.0, np.zeros(A.rows, np.float32), A.cols, variant)
+        assert np.array_equal(a, b)
+
+
+def test_alg_enum_selects_variant(handle):
+    A = _mk("poisson", np.float32)
+    rp, ci, v = A.numpy()
+    x = G.uniform((A.cols,), -1, 1, seed=52).numpy()
+    y0 = np.zeros(A.rows, np.float32)
+    _, Am = run_spmv(handle, rp, ci, v, x, 1.0, 0.0, y0, A.cols, alg=api.SPMV_ALG_MERGE)
+    assert Am.last_variant() == "merge"
+    _, Am = run_spmv(handle, rp, ci, v, x, 1.0, 0.0, y0, A.cols, alg=api.SPMV_ALG_VECTOR)
+    assert Am.last_variant() == "binned"
+    # the reference's own CSR tests pass ALG_COO (cuda/test/level2/spmv_csr_r_f32_test.cu:238): still computed
+    got, _ = run_spmv(handle, rp, ci, v, x, 1.0, 0.0, y0, A.cols, alg=api.SPMV_ALG_COO)
+    assert rel_l2(got, oracle.spmv(rp, ci, v, x, 1.0, 0.0)) <= 1e-5
+
+
+def test_status_codes(handle):
+    import ctypes as C
+    lib = api.load()
+    A = _mk("tiny", np.float32)
+    Am = api.CsrMatrix.from_csr(A)
+    x = api.DnVec(torch.zeros(A.cols, device="cuda"))
+    y = api.DnVec(torch.zeros(A.rows, device="cuda"))
+    one = C.c_float(1.0)
+
+    def call(op=0, a=C.byref(one), mat=Am.d, vx=x.d, b=C.byref(one), vy=y.d, ct=api.R_32F):
+        return lib.alphasparseSpMV(handle.h, op, a, mat, vx, b, vy, ct, 0, None)
+    assert call() == 0
+    assert call(op=api.OP_T) == 6
+    assert call(a=None) == 7
+    assert call(mat=None) == 7
+    assert call(ct=api.R_64F) == 6
+    bad = api.DnVec(torch.zeros(A.cols + 1, device="cuda"))
+    assert call(vx=bad.d) == 10
+    xd = api.DnVec(torch.zeros(A.cols, device="cuda", dtype=torch.float64))
+    assert call(vx=xd.d) == 6
+
+
+def test_invalid_structure_is_rejected_not_run(handle):
+    """Column index out of range and decreasing offsets come back as INVALID_VALUE from analysis."""
+    rp = torch.tensor([0, 2, 4], dtype=torch.int32, device="cuda")
+    ci = torch.tensor([0, 1, 0, 7], dtype=torch.int32, device="cuda")
+    v = torch.ones(4, device="cuda")
+    Am = api.CsrMatrix(2, 3, rp, ci, v)
+    with pytest.raises(api.AlphaSparseError) as e:
+        Am.analyse(handle)
+    assert e.value.status == 3
+    rp2 = torch.tensor([0, 3, 2, 4], dtype=torch.int32, device="cuda")
+    Am2 = api.CsrMatrix(3, 8, rp2, ci, v)
+    with pytest.raises(api.AlphaSparseError) as e:
+        Am2.analyse(handle)
+    assert e.value.status == 3
+
+
+def test_partition_and_rebase_match_oracle(handle):
+    A = _mk("rmat", np.float32)
+    rp, _, _ = A.numpy()
+    for dt in (torch.int32, torch.int64):
+        rpd = torch.from_numpy(rp).to("cuda").to(dt)
+        for parts in (1, 2, 4, 8):
+            got = api.partition_rows_by_nnz(handle, rpd, parts)
+            assert np.array_equal(got, oracle.partition_rows_by_nnz(rp, parts))
+        b = api.partition_rows_by_nnz(handle, rpd, 4)
+        loc = api.rebase_row_offsets(handle, rpd, int(b[1]), int(b[2]), torch.int32)
+        torch.cuda.synchronize()
+        assert np.array_equal(loc.cpu().numpy(), rp[b[1]:b[2] + 1] - rp[b[1]])
