@@ -102,49 +102,68 @@ def algorithmic_bytes(w):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Reads SM clock and clock-event (throttle) reasons through NVML while the timed region
+    runs (read-only queries; nothing on the GPU is changed)."""
 
     def __init__(self, index):
         self.index, self.samples, self.stop = index, [], threading.Event()
         self.th = threading.Thread(target=self._run, daemon=True)
+        self.nv = self.dev = None
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if vis:
+                ids = [v for v in vis.split(",") if v.strip() != ""]
+                if index < len(ids) and ids[index].strip().isdigit():
+                    phys = int(ids[index])
+            self.nv = pynvml
+            self.dev = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.dev, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
 
     def _once(self):
+        if self.nv is None:
+            return
         try:
-            out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                  "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
-            f = [s.strip() for s in out.strip().split(",")]
-            if len(f) >= 7:
-                self.samples.append(f)
+            nv = self.nv
+            mhz = float(nv.nvmlDeviceGetClockInfo(self.dev, nv.NVML_CLOCK_SM))
+            try:
+                r = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.dev))
+            except Exception:
+                r = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.dev))
+            self.samples.append((mhz, r))
         except Exception:
             pass
 
     def _run(self):
         while not self.stop.is_set():
             self._once()
-            self.stop.wait(0.05)
+            self.stop.wait(0.002)
 
     def __enter__(self):
+        self._once()
         self.th.start()
         return self
 
     def __exit__(self, *a):
         self.stop.set()
-        self.th.join(timeout=6)
-        if not self.samples:
-            self._once()
+        self.th.join(timeout=2)
+        self._once()
 
     def summary(self):
         if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
-        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[3 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": float(self.samples[0][1]) if self.samples[0][1].replace(".", "").isdigit() else None,
-                "reasons": reasons, "samples": len(self.samples)}
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"], "samples": 0}
+        bits = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+                0x4: "sw_power_cap"}
+        seen = 0
+        for _, r in self.samples:
+            seen |= r
+        return {"sm_mhz": statistics.median(m for m, _ in self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": [n for b, n in bits.items() if seen & b], "samples": len(self.samples)}
 
 
 def measured_peak():
