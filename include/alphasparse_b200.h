@@ -270,6 +270,33 @@ alphasparseStatus_t alphasparseSpMV_clear(alphasparseHandle_t handle, alphaspars
 alphasparseStatus_t alphasparseSpMV_clearMat(alphasparseHandle_t handle,
                                              alphasparseSpMatDescr_t matA); /* extension */
 
+/* No counterpart in the reference.  y = alpha*A*x + beta*y on raw CSR device arrays for callers
+ * that must not allocate device memory around the call (a solver loop on a GPU whose memory a
+ * framework's pool has claimed in full, or a latency-critical loop that cannot take the device
+ * synchronisation and late failure of cudaMalloc / cudaFree).  Such callers cannot use
+ * alphasparseSpMV either, because matrix analysis allocates the plan; so this call takes no
+ * handle and no descriptor, runs the merge-path kernel, and keeps its scratch (per-tile start
+ * rows and carry-outs, 786,688 bytes) in a fixed device array inside the library image, which
+ * every GPU that loads the library holds until the process exits.  It calls no cudaMalloc,
+ * cudaFree or any other allocating routine.
+ *   - Limit: rows + nnz <= ALPHASPARSE_SPMV_NOALLOC_MAX_ITEMS, else ALPHA_SPARSE_STATUS_INVALID_SIZE.
+ *   - fp32 / fp64 values, I32 / I64 row offsets, I32 zero-based columns; alpha, beta host pointers.
+ *   - The CSR structure is NOT validated (validation needs scratch of its own): offsets must be
+ *     non-decreasing from 0 to nnz and columns inside [0, cols).
+ *   - The first call on each device looks the array's device address up once (with that device
+ *     current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array.  Nothing in it has to be cleared between calls
+ *     (every slot a call reads it has written first), but two calls whose kernels overlap on the
+ *     GPU - different streams, or different host threads - race on it: keep calls on one device
+ *     stream-ordered with respect to each other. */
+#define ALPHASPARSE_SPMV_NOALLOC_MAX_ITEMS 134217728 /* 65,536 tiles of 2,048 merge items */
+alphasparseStatus_t alphasparseSpMVCsrNoAlloc(cudaStream_t stream, int64_t rows, int64_t cols,
+                                              int64_t nnz, const void* csrRowOffsets,
+                                              alphasparseIndexType_t csrRowOffsetsType,
+                                              const int32_t* csrColInd, const void* csrValues,
+                                              alphasparseDataType valueType, const void* alpha,
+                                              const void* x, const void* beta, void* y);
+
 /* ---- SpMM: C = alpha*op(A)*op(B) + beta*C, B and C row-major ------------------------ */
 /* spapi.h:6963-6974; cuda/kernel/level3/alphasparse_spmm.cu:531-612 */
 alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t handle, alphasparseOperation_t opA,

@@ -42,6 +42,7 @@ EXPORTS = [
     "alphasparseSpMM_bufferSize", "alphasparseSpMM_preprocess",
     "alphasparseCsrPartitionRowsByNnz", "alphasparseCsrRebaseRowOffsets", "alphasparseCsrPlanGet",
     "alphasparseCsrLastVariant", "alphasparseGetLaunchCount", "get_time_us", "get_avg_time_n",
+    "alphasparseSpMVCsrNoAlloc",
 ]
 
 
@@ -252,3 +253,21 @@ def rebase_row_offsets(handle: Handle, row_ptr: torch.Tensor, row_begin: int, ro
                                                  C.c_int64(row_end), C.c_void_p(out.data_ptr()),
                                                  it[out_dtype]), "alphasparseCsrRebaseRowOffsets")
     return out
+
+
+NOALLOC_MAX_ITEMS = 134217728
+
+
+def spmv_csr_noalloc(row_ptr: torch.Tensor, col_idx: torch.Tensor, val: torch.Tensor, x: torch.Tensor,
+                     y: torch.Tensor, alpha=1.0, beta=0.0, cols=None, stream=None) -> int:
+    """alphasparseSpMVCsrNoAlloc on torch tensors; returns the status instead of raising so that
+    callers can test the size limit."""
+    code = _dtype_code(val.dtype)
+    a, b = _scalar(alpha, code), _scalar(beta, code)
+    rt = {torch.int32: INDEX_I32, torch.int64: INDEX_I64}[row_ptr.dtype]
+    st = torch.cuda.current_stream().cuda_stream if stream is None else stream
+    return int(load().alphasparseSpMVCsrNoAlloc(
+        C.c_void_p(st), C.c_int64(row_ptr.numel() - 1), C.c_int64(x.numel() if cols is None else cols),
+        C.c_int64(col_idx.numel()), C.c_void_p(row_ptr.data_ptr()), rt, C.c_void_p(col_idx.data_ptr()),
+        C.c_void_p(val.data_ptr()), code, C.byref(a), C.c_void_p(x.data_ptr()), C.byref(b),
+        C.c_void_p(y.data_ptr())))

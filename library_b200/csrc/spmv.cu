@@ -14,6 +14,7 @@
 //     second small kernel adds in tile order, so results are reproducible run to run.
 #include <climits>
 #include <cstring>
+#include <mutex>
 #include <type_traits>
 
 #include "asp_internal.h"
@@ -505,3 +506,110 @@ alphasparseStatus_t alphasparseSpMV_bufferSize(alphasparseHandle_t h, alphaspars
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free SpMV entry point.
+//
+// alphasparseSpMV needs an analysed matrix, and analysis allocates the plan with cudaMalloc.
+// Some callers may not allocate device memory at all around the call: an iterative solver
+// running on a GPU whose memory a framework's pool has already claimed in full, or a
+// latency-critical loop that cannot accept the implicit device synchronisation and the
+// late failure mode of cudaMalloc / cudaFree.  For them this entry point runs the merge-path
+// kernel on raw CSR arrays and keeps its two scratch arrays - the per-tile merge-path start
+// rows and the per-tile carry-outs - in one fixed device array that is part of the library
+// image.  Every GPU that loads the library holds these 786,688 bytes until the process exits.
+// ------------------------------------------------------------------------------------------
+namespace asp {
+namespace {
+
+constexpr int64_t kNoAllocMaxTiles = ALPHASPARSE_SPMV_NOALLOC_MAX_ITEMS / kMergeItems;
+constexpr size_t kNoAllocTileBytes = (((size_t)(kNoAllocMaxTiles + 1) * sizeof(int32_t)) + 255) & ~(size_t)255;
+constexpr size_t kNoAllocBytes = kNoAllocTileBytes + (size_t)kNoAllocMaxTiles * sizeof(double);
+static_assert(ALPHASPARSE_SPMV_NOALLOC_MAX_ITEMS % kMergeItems == 0, "limit must be whole tiles");
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+// In host code g_noalloc_scratch is only a handle for the symbol; the address kernels can use
+// comes from cudaGetSymbolAddress, asked once per device with that device current.
+constexpr int kNoAllocMaxDevices = 64;
+void* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+std::mutex g_noalloc_mu;
+
+template <typename OffT>
+__global__ void __launch_bounds__(256) noalloc_tile_search_kernel(const OffT* __restrict__ rp,
+                                                                  int64_t rows, int64_t nnz,
+                                                                  int64_t tiles,
+                                                                  int32_t* __restrict__ tile_row) {
+  const int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (t > tiles) return;
+  const OffT* row_end = rp + 1;
+  int64_t diag = t * (int64_t)kMergeItems;
+  if (diag > rows + nnz) diag = rows + nnz;
+  int64_t lo = diag > nnz ? diag - nnz : 0;
+  int64_t hi = diag < rows ? diag : rows;
+  while (lo < hi) {
+    const int64_t mid = (lo + hi) >> 1;
+    if ((int64_t)row_end[mid] <= diag - mid - 1) lo = mid + 1;
+    else hi = mid;
+  }
+  tile_row[t] = (int32_t)lo;
+}
+
+template <typename T, typename OffT>
+alphasparseStatus_t spmv_noalloc_t(cudaStream_t st, int64_t rows, int64_t nnz, const OffT* rp,
+                                   const int* col, const T* val, const T* x, T* y, T alpha, T beta,
+                                   void* scratch) {
+  const int64_t tiles = (rows + nnz + kMergeItems - 1) / kMergeItems;
+  int32_t* tile_row = reinterpret_cast<int32_t*>(scratch);
+  T* carry = reinterpret_cast<T*>(reinterpret_cast<unsigned char*>(scratch) + kNoAllocTileBytes);
+  noalloc_tile_search_kernel<OffT><<<(unsigned)((tiles + 1 + 255) / 256), 256, 0, st>>>(rp, rows, nnz, tiles, tile_row);
+  const bool vl = aligned(val, 16) && aligned(col, 16);
+  if (vl)
+    spmv_merge_kernel<T, OffT, true><<<(unsigned)tiles, kThreads, 0, st>>>(rp, col, val, x, y, alpha, beta, rows, nnz, tile_row, carry);
+  else
+    spmv_merge_kernel<T, OffT, false><<<(unsigned)tiles, kThreads, 0, st>>>(rp, col, val, x, y, alpha, beta, rows, nnz, tile_row, carry);
+  spmv_merge_fixup_kernel<T><<<(unsigned)((tiles + 255) / 256), 256, 0, st>>>(tile_row, carry, tiles, rows, y, alpha);
+  return status_of(cudaGetLastError());
+}
+
+}  // namespace
+}  // namespace asp
+
+extern "C" alphasparseStatus_t alphasparseSpMVCsrNoAlloc(
+    cudaStream_t stream, int64_t rows, int64_t cols, int64_t nnz, const void* csrRowOffsets,
+    alphasparseIndexType_t csrRowOffsetsType, const int32_t* csrColInd, const void* csrValues,
+    alphasparseDataType valueType, const void* alpha, const void* x, const void* beta, void* y) {
+  if (rows < 0 || cols < 0 || nnz < 0 || rows >= (int64_t(1) << 31) || cols >= (int64_t(1) << 31))
+    return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  // The scratch array is fixed: refuse anything that needs more tiles than it holds.
+  if (rows + nnz > (int64_t)ALPHASPARSE_SPMV_NOALLOC_MAX_ITEMS) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  if (!alpha || !beta || !csrRowOffsets) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  if ((nnz > 0 && (!csrColInd || !csrValues)) || (cols > 0 && !x) || (rows > 0 && !y))
+    return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  const bool o64 = csrRowOffsetsType == ALPHA_SPARSE_INDEXTYPE_I64;
+  if (!o64 && csrRowOffsetsType != ALPHA_SPARSE_INDEXTYPE_I32) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (valueType != ALPHA_R_32F && valueType != ALPHA_R_64F) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+
+  int dev = 0;
+  ASP_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+      void* p = nullptr;
+      ASP_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));  // first call on this device only
+      g_noalloc_ptr[dev] = p;
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  if (valueType == ALPHA_R_32F) {
+    const float al = *(const float*)alpha, be = *(const float*)beta;
+    return o64 ? spmv_noalloc_t<float, int64_t>(stream, rows, nnz, (const int64_t*)csrRowOffsets, csrColInd, (const float*)csrValues, (const float*)x, (float*)y, al, be, scratch)
+               : spmv_noalloc_t<float, int32_t>(stream, rows, nnz, (const int32_t*)csrRowOffsets, csrColInd, (const float*)csrValues, (const float*)x, (float*)y, al, be, scratch);
+  }
+  const double al = *(const double*)alpha, be = *(const double*)beta;
+  return o64 ? spmv_noalloc_t<double, int64_t>(stream, rows, nnz, (const int64_t*)csrRowOffsets, csrColInd, (const double*)csrValues, (const double*)x, (double*)y, al, be, scratch)
+             : spmv_noalloc_t<double, int32_t>(stream, rows, nnz, (const int32_t*)csrRowOffsets, csrColInd, (const double*)csrValues, (const double*)x, (double*)y, al, be, scratch);
+}
