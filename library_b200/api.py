@@ -30,7 +30,7 @@ BASE_ZERO, BASE_ONE = 0, 1
 SPMV_ALG_DEFAULT, SPMV_ALG_COO, SPMV_ALG_VECTOR, SPMV_ALG_MERGE = 0, 1, 6, 9
 SPMM_ALG_DEFAULT, SPMM_CSR_ALG1, SPMM_CSR_ALG2, SPMM_CSR_ALG6 = 0, 5, 6, 10
 STAT_NAMES = ["max_len", "empty_rows", "num_short", "num_medium", "num_long", "group_lanes",
-              "merge_items", "merge_tiles", "variant", "identity_short", "nnz_short"]
+              "merge_items", "merge_tiles", "variant", "identity_short", "nnz_short", "device_error"]
 
 EXPORTS = [
     "initHandle", "alphasparseGetHandle", "alphasparse_destory_handle", "alphasparseSetStream",

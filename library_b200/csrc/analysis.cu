@@ -91,12 +91,12 @@ struct RowClassIs {
 // reference's merge_path_search (alphasparse_spmv_csr_merge_ginkgo.h:11-35).
 template <typename OffT>
 __global__ void __launch_bounds__(256) merge_tile_kernel(const OffT* __restrict__ rp, int64_t rows,
-                                                         int64_t nnz, int64_t tiles,
+                                                         int64_t nnz, int64_t tiles, int items,
                                                          int32_t* __restrict__ tile_row) {
   const int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (t > tiles) return;
   const OffT* row_end = rp + 1;
-  int64_t diag = t * (int64_t)kMergeItems;
+  int64_t diag = t * (int64_t)items;
   if (diag > rows + nnz) diag = rows + nnz;
   int64_t lo = diag > nnz ? diag - nnz : 0;
   int64_t hi = diag < rows ? diag : rows;
@@ -237,8 +237,10 @@ alphasparseStatus_t analyse_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, 
   p->merge_tiles = (p->rows + p->nnz + kMergeItems - 1) / kMergeItems;
   ASP_CUDA(cudaMalloc(&p->merge_tile_row, sizeof(int32_t) * (p->merge_tiles + 1)));
   ASP_CUDA(cudaMalloc(&p->carry, sizeof(double) * (p->merge_tiles > 0 ? p->merge_tiles : 1)));
+  ASP_CUDA(cudaMalloc(&p->dev_err, sizeof(int)));
+  ASP_CUDA(cudaMemsetAsync(p->dev_err, 0, sizeof(int), st));
   merge_tile_kernel<OffT><<<(int)((p->merge_tiles + 1 + 255) / 256), 256, 0, st>>>(
-      rp, p->rows, p->nnz, p->merge_tiles, p->merge_tile_row);
+      rp, p->rows, p->nnz, p->merge_tiles, kMergeItems, p->merge_tile_row);
   impl(h)->launches++;
   ASP_CUDA(cudaGetLastError());
   ASP_CUDA(cudaStreamSynchronize(st));
@@ -273,6 +275,7 @@ void free_plan(Plan* p) {
   cudaFree(p->bin_rows);
   cudaFree(p->merge_tile_row);
   cudaFree(p->carry);
+  cudaFree(p->dev_err);
   if (p->spmm_tc) free_spmm_tc_plan(p->spmm_tc);
   delete p;
 }
@@ -353,6 +356,9 @@ alphasparseStatus_t alphasparseCsrPlanGet(alphasparseHandle_t h, alphasparseSpMa
     stats[ASP_STAT_VARIANT] = p->variant_auto;
     stats[ASP_STAT_IDENTITY_SHORT] = p->identity_short ? 1 : 0;
     stats[ASP_STAT_NNZ_SHORT] = p->nnz_short;
+    int e = 0;
+    if (p->dev_err) ASP_CUDA(cudaMemcpy(&e, p->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
+    stats[ASP_STAT_DEVICE_ERROR] = e;
   }
   if (bin_rows && p->rows > 0) {
     if (p->identity_short) {

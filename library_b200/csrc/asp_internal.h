@@ -45,6 +45,7 @@ struct Plan {
   int64_t merge_tiles = 0;
   int32_t* merge_tile_row = nullptr;  // device, merge_tiles + 1
   void* carry = nullptr;              // device, merge_tiles * 8 bytes (used when no external buffer)
+  int* dev_err = nullptr;             // device flag a kernel raises when a bounded wait expires
   int variant_auto = kVariantBinned;
   int last_variant = -1;
   // SpMM

@@ -95,7 +95,7 @@ struct BinnedArgs {
   int cta_short, cta_medium;
 };
 
-template <typename T, typename OffT, int G, bool VL>
+template <typename T, typename OffT, int G, bool VL, int U>
 __global__ void __launch_bounds__(kThreads) spmv_binned_kernel(const BinnedArgs<T, OffT> a) {
   constexpr int N = VecTraits<T>::N;
   using IdxT = idx_t<OffT>;
@@ -103,7 +103,6 @@ __global__ void __launch_bounds__(kThreads) spmv_binned_kernel(const BinnedArgs<
   const int b = blockIdx.x;
   if (b < a.cta_short) {
     constexpr int NG = kThreads / G;
-    constexpr int U = kShortUnroll;
     const int lane = threadIdx.x & (G - 1);
     const int grp = threadIdx.x / G;
     const int64_t base = (int64_t)b * (NG * U);
@@ -202,26 +201,49 @@ __global__ void __launch_bounds__(kThreads) spmv_binned_kernel(const BinnedArgs<
 // Merge-path kernel (Merrill & Garland's decomposition; the reference's version is
 // alphasparse_spmv_csr_merge_ginkgo.h:36-131).  CTA t owns items [t*kMergeItems, ...) of the
 // merge of the row-end offsets with the entry indices; its start coordinate comes from the
-// plan.  The CTA (1) streams its entries with coalesced 16-byte loads, multiplies by the
-// gathered x and parks the products in shared memory, (2) every thread walks kMergeIpt items
-// of the merge list serially, (3) a block-wide segmented scan hands partial sums of rows that
-// span threads forward, and the sum that leaves the tile goes to carry[t].
+// plan.  The CTA
+//   (1) streams its entries with coalesced 16-byte loads, multiplies by the gathered x and
+//       parks the products in shared memory (index skewed by one slot per 32 so that rows of
+//       any stride read without bank conflicts);
+//   (2) reduces rows.  If every row segment in the tile is short (<= kMergeShortSeg entries)
+//       thread i sums segment i straight from shared memory and writes y[row_s+i] coalesced.
+//       Otherwise every thread walks kMergeIpt items of the merge list serially and a
+//       block-wide segmented scan hands partial sums of rows that span threads forward.
+//   (3) the sum of the row still open at the tile's end goes to carry[t]; the fix-up kernel
+//       adds carries to their rows in tile order.
 // ------------------------------------------------------------------------------------------
+constexpr int kMergeShortSeg = 64;
+#ifndef ASP_TILE_MIN_CTAS
+#define ASP_TILE_MIN_CTAS 6
+#endif
+constexpr int kTileMinCtas = ASP_TILE_MIN_CTAS;
+#ifndef ASP_TILE_SHORT_SEG
+#define ASP_TILE_SHORT_SEG 32
+#endif
+#ifndef ASP_MERGE_MIN_CTAS
+#define ASP_MERGE_MIN_CTAS 6
+#endif
+constexpr int kMergeMinCtas = ASP_MERGE_MIN_CTAS;
+#ifndef ASP_MERGE_THREADS
+#define ASP_MERGE_THREADS 256
+#endif
+constexpr int kMergeThreads = ASP_MERGE_THREADS;
+__device__ __forceinline__ int skew(int i) { return i + (i >> 5); }
+
 template <typename T, typename OffT, bool VL>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kMergeThreads, kMergeMinCtas)
 spmv_merge_kernel(const OffT* __restrict__ rp, const int* __restrict__ col,
                   const T* __restrict__ val, const T* __restrict__ x, T* __restrict__ y, T alpha,
                   T beta, int64_t rows, int64_t nnz64, const int32_t* __restrict__ tile_row,
                   T* __restrict__ carry) {
   constexpr int N = VecTraits<T>::N;
-  constexpr int IPT = kMergeIpt;
+  constexpr int IPT = kMergeItems / kMergeThreads;
   constexpr int ITEMS = kMergeItems;
-  constexpr int CH = ITEMS / (N * kThreads) + 1;
-  using IdxT = idx_t<OffT>;
-  __shared__ T s_prod[ITEMS];
+  constexpr int CH = ITEMS / (N * kMergeThreads) + 1;
+  __shared__ T s_prod[ITEMS + ITEMS / 32 + 1];
   __shared__ int s_rowend[ITEMS + 1];
-  __shared__ T s_wval[kThreads / 32];
-  __shared__ int s_wflag[kThreads / 32];
+  __shared__ T s_wval[kMergeThreads / 32];
+  __shared__ int s_wflag[kMergeThreads / 32];
 
   const int tid = threadIdx.x;
   const int64_t t = blockIdx.x;
@@ -229,40 +251,71 @@ spmv_merge_kernel(const OffT* __restrict__ rp, const int* __restrict__ col,
   const int64_t diag_s = t * (int64_t)ITEMS;
   int64_t diag_e = diag_s + ITEMS;
   if (diag_e > rows + nnz64) diag_e = rows + nnz64;
-  const IdxT nz_s = (IdxT)(diag_s - row_s), nz_e = (IdxT)(diag_e - row_e);
+  const int64_t nz_s = diag_s - row_s, nz_e = diag_e - row_e;
   const int tile_rows = row_e - row_s;
   const int tile_nnz = (int)(nz_e - nz_s);
-  const IdxT nnz = (IdxT)nnz64;
 
-  // (1) products
+  // The row end this thread will publish, requested before the entry loads so that both
+  // round trips to HBM overlap.
+  OffT my_end = 0;
+  if (tid < tile_rows) my_end = rp[row_s + tid + 1];
+
+  // (1) products.  All indices below are 32-bit offsets from the tile's aligned first entry.
   {
-    const IdxT a0 = nz_s & ~(IdxT)(N - 1);
+    const int64_t a0 = nz_s & ~(int64_t)(N - 1);
+    const T* __restrict__ tval = val + a0;
+    const int* __restrict__ tcol = col + a0;
+    const int lo = (int)(nz_s - a0);                 // first entry of the tile
+    const int hi = lo + tile_nnz;                    // one past its last entry
+    const int64_t rem = nnz64 - a0;                  // entries left in the arrays
+    const int lim = rem > (int64_t)(ITEMS + 2 * N) ? ITEMS + 2 * N : (int)rem;
     T v[CH][N];
     int c[CH][N];
 #pragma unroll
     for (int i = 0; i < CH; ++i) {
-      const IdxT k = a0 + (IdxT)((i * kThreads + tid) * N);
-      if (k < nz_e) load_chunk<T, VL, IdxT>(val, col, k, nnz, v[i], c[i]);
+      const int k = (i * kMergeThreads + tid) * N;
+      if (k < hi) load_chunk<T, VL, int>(tval, tcol, k, lim, v[i], c[i]);
     }
 #pragma unroll
     for (int i = 0; i < CH; ++i) {
-      const IdxT k = a0 + (IdxT)((i * kThreads + tid) * N);
-      if (k < nz_e) {
+      const int k = (i * kMergeThreads + tid) * N;
+      if (k < hi) {
 #pragma unroll
         for (int j = 0; j < N; ++j) {
-          const IdxT kk = k + j;
-          if (kk >= nz_s && kk < nz_e) s_prod[(int)(kk - nz_s)] = v[i][j] * __ldg(x + c[i][j]);
+          const int kk = k + j;
+          if (kk >= lo && kk < hi) s_prod[skew(kk - lo)] = v[i][j] * __ldg(x + c[i][j]);
         }
       }
     }
   }
-  // row ends relative to the tile's first entry; the row still open at the tile end gets a
-  // sentinel so that the walk below only consumes entries once the row ends run out
-  for (int i = tid; i <= tile_rows; i += kThreads)
-    s_rowend[i] = i < tile_rows ? (int)((int64_t)rp[row_s + i + 1] - (int64_t)nz_s) : INT_MAX;
+  // Row ends relative to the tile's first entry.  Rows row_s .. row_e-1 end inside the tile.
+  if (tid < tile_rows) s_rowend[tid] = (int)((int64_t)my_end - nz_s);
+  for (int i = tid + kMergeThreads; i < tile_rows; i += kMergeThreads)
+    s_rowend[i] = (int)((int64_t)rp[row_s + i + 1] - nz_s);
+  if (tid == 0) s_rowend[tile_rows] = INT_MAX;  // the row still open at the tile's end never "ends" here
   __syncthreads();
+  bool long_seg = false;
+  for (int i = tid; i <= tile_rows; i += kMergeThreads) {
+    const int b = i == 0 ? 0 : s_rowend[i - 1];
+    const int e = i < tile_rows ? s_rowend[i] : tile_nnz;
+    long_seg |= (e - b) > kMergeShortSeg;
+  }
+  const int any_long = __syncthreads_or(long_seg ? 1 : 0);
 
-  // (2) per-thread walk
+  if (!any_long) {
+    // (2a) one thread per row segment
+    for (int i = tid; i <= tile_rows; i += kMergeThreads) {
+      const int b = i == 0 ? 0 : s_rowend[i - 1];
+      const int e = i < tile_rows ? s_rowend[i] : tile_nnz;
+      T sum = T(0);
+      for (int k = b; k < e; ++k) sum += s_prod[skew(k)];
+      if (i < tile_rows) y[row_s + i] = finish(alpha, sum, beta, y + row_s + i);
+      else carry[t] = sum;
+    }
+    return;
+  }
+
+  // (2b) per-thread walk
   const int tile_items = tile_rows + tile_nnz;
   int d = tid * IPT;
   if (d > tile_items) d = tile_items;
@@ -282,7 +335,7 @@ spmv_merge_kernel(const OffT* __restrict__ rp, const int* __restrict__ col,
   for (int it = 0; it < IPT; ++it) {
     if (d + it < d_end) {
       if (j < s_rowend[i]) {
-        running += s_prod[j];
+        running += s_prod[skew(j)];
         ++j;
       } else {
         if (first_row < 0) {
@@ -297,7 +350,7 @@ spmv_merge_kernel(const OffT* __restrict__ rp, const int* __restrict__ col,
     }
   }
 
-  // (3) segmented scan of the carry-outs: a thread that finished a row starts a new segment
+  // segmented scan of the carry-outs: a thread that finished a row starts a new segment
   const int lane = tid & 31, warp = tid >> 5;
   int flag = first_row >= 0 ? 1 : 0;
   T sv = running;
@@ -328,7 +381,249 @@ spmv_merge_kernel(const OffT* __restrict__ rp, const int* __restrict__ col,
     const int r = row_s + first_row;
     y[r] = finish(alpha, carry_in + first_val, beta, y + r);
   }
-  if (tid == kThreads - 1) carry[t] = flag ? sv : pv + sv;
+  if (tid == kMergeThreads - 1) carry[t] = flag ? sv : pv + sv;
+}
+
+// ------------------------------------------------------------------------------------------
+// TMA-staged merge-path kernel (the default for 16-byte aligned arrays).  Same tiles and the
+// same carry protocol as spmv_merge_kernel, different data path:
+//   (1) one elected thread asks the copy engine for the tile's value and column slices
+//       (two 1-D bulk copies, cp.async.bulk, completion counted on an mbarrier); no register
+//       or load/store-unit work is spent on streaming A.  Bulk copies need 16-byte aligned
+//       source, destination and size, so a slice is widened to multiples of four entries,
+//       clipped to the last full group of four of the array, and the elected thread fetches
+//       the at most three entries beyond that with plain loads.
+//   (2) while the copies fly, thread i reads the offsets of row segment i straight from
+//       global memory (coalesced).
+//   (3a) if every segment of the tile is short, thread i walks segment i: column and value
+//       from shared memory, x gathered from global memory - for banded matrices the 32 lanes
+//       of a warp then read 32 neighbouring x entries - and the sum stays in a register.
+//       No product array, no second pass.
+//   (3b) otherwise products are formed in place, entry-parallel, and the serial walk with the
+//       block-wide segmented scan of spmv_merge_kernel takes over.
+// The wait on the mbarrier is bounded; on expiry the CTA raises *err and leaves.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+constexpr int kTileSlot = kMergeItems + 8;     // entries per staged array (widening adds < 8)
+constexpr int kTileShortSeg = ASP_TILE_SHORT_SEG;
+constexpr uint32_t kTileMaxTries = 1u << 22;
+
+template <typename T, typename OffT>
+__global__ void __launch_bounds__(kThreads, kTileMinCtas)
+spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const T* __restrict__ val,
+                 const T* __restrict__ x, T* __restrict__ y, T alpha, T beta, int64_t rows,
+                 int64_t nnz, const int32_t* __restrict__ tile_row, T* __restrict__ carry,
+                 int* __restrict__ err) {
+  constexpr int ITEMS = kMergeItems;
+  constexpr int IPT = kMergeIpt;
+  __shared__ __align__(128) T s_val[kTileSlot];
+  __shared__ __align__(128) int s_col[kTileSlot];
+  __shared__ int s_rowend[ITEMS + 1];
+  __shared__ __align__(8) uint64_t s_bar;
+  __shared__ T s_wval[kThreads / 32];
+  __shared__ int s_wflag[kThreads / 32];
+
+  const int tid = threadIdx.x;
+  const int64_t t = blockIdx.x;
+  const int row_s = tile_row[t], row_e = tile_row[t + 1];
+  const int64_t total = rows + nnz;
+  const int64_t diag_s = t * (int64_t)ITEMS;
+  const int64_t diag_e = diag_s + ITEMS < total ? diag_s + ITEMS : total;
+  const int64_t nz_s = diag_s - row_s, nz_e = diag_e - row_e;
+  const int tile_rows = row_e - row_s;
+  const int tile_nnz = (int)(nz_e - nz_s);
+  const int64_t a0 = nz_s & ~(int64_t)3;
+  const int lo = (int)(nz_s - a0);
+
+  if (tid == 0) {
+    mbar_init(&s_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const int64_t nnz4 = nnz & ~(int64_t)3;
+    int64_t a1 = (nz_e + 3) & ~(int64_t)3;
+    if (a1 > nnz4) a1 = nnz4;
+    if (a1 < a0) a1 = a0;
+    const uint32_t cnt = (uint32_t)(a1 - a0);
+    mbar_expect_tx(&s_bar, cnt * (uint32_t)(sizeof(T) + sizeof(int)));
+    if (cnt) {
+      bulk_g2s(s_val, val + a0, cnt * (uint32_t)sizeof(T), &s_bar);
+      bulk_g2s(s_col, col + a0, cnt * (uint32_t)sizeof(int), &s_bar);
+    }
+    for (int64_t e = a1 > nz_s ? a1 : nz_s; e < nz_e; ++e) {  // past the last full group of four
+      s_val[e - a0] = val[e];
+      s_col[e - a0] = col[e];
+    }
+  }
+  // (2) this thread's first row segment, from global memory while the copies are in flight
+  int seg_b = 0, seg_e = 0;
+  bool long_seg = false;
+  if (tid <= tile_rows) {
+    seg_b = tid == 0 ? 0 : (int)((int64_t)rp[row_s + tid] - nz_s);
+    seg_e = tid < tile_rows ? (int)((int64_t)rp[row_s + tid + 1] - nz_s) : tile_nnz;
+    long_seg = (seg_e - seg_b) > kTileShortSeg;
+  }
+  for (int i = tid + kThreads; i <= tile_rows; i += kThreads) {
+    const int b = (int)((int64_t)rp[row_s + i] - nz_s);
+    const int e = i < tile_rows ? (int)((int64_t)rp[row_s + i + 1] - nz_s) : tile_nnz;
+    long_seg |= (e - b) > kTileShortSeg;
+  }
+  __syncthreads();  // the barrier is initialised (and thread 0's plain stores are visible)
+  bool failed = false;
+  {
+    uint32_t tries = 0;
+    while (!mbar_try_wait(&s_bar, 0)) {
+      if (++tries > kTileMaxTries) {
+        failed = true;
+        break;
+      }
+    }
+  }
+  const int vote = __syncthreads_or((long_seg ? 1 : 0) | (failed ? 2 : 0));
+  if (vote & 2) {
+    if (tid == 0) atomicExch(err, 1);
+    __nanosleep(1000000);  // let a copy still in flight land before the CTA's memory is released
+    return;
+  }
+  const T* sv = s_val + lo;
+  const int* sc = s_col + lo;
+
+  if (!(vote & 1)) {
+    // (3a) one thread per row segment, four entries in flight at a time
+    for (int i = tid; i <= tile_rows; i += kThreads) {
+      int b, e;
+      if (i == tid) {
+        b = seg_b;
+        e = seg_e;
+      } else {
+        b = (int)((int64_t)rp[row_s + i] - nz_s);
+        e = i < tile_rows ? (int)((int64_t)rp[row_s + i + 1] - nz_s) : tile_nnz;
+      }
+      T sum = T(0);
+      int k = b;
+      for (; k + 4 <= e; k += 4) {
+        const int c0 = sc[k], c1 = sc[k + 1], c2 = sc[k + 2], c3 = sc[k + 3];
+        const T x0 = __ldg(x + c0), x1 = __ldg(x + c1), x2 = __ldg(x + c2), x3 = __ldg(x + c3);
+        sum = fma(sv[k], x0, sum);
+        sum = fma(sv[k + 1], x1, sum);
+        sum = fma(sv[k + 2], x2, sum);
+        sum = fma(sv[k + 3], x3, sum);
+      }
+      if (k < e) {
+        const int c0 = sc[k];
+        const int c1 = k + 1 < e ? sc[k + 1] : c0;
+        const int c2 = k + 2 < e ? sc[k + 2] : c0;
+        const T x0 = __ldg(x + c0), x1 = __ldg(x + c1), x2 = __ldg(x + c2);
+        sum = fma(sv[k], x0, sum);
+        if (k + 1 < e) sum = fma(sv[k + 1], x1, sum);
+        if (k + 2 < e) sum = fma(sv[k + 2], x2, sum);
+      }
+      if (i < tile_rows) y[row_s + i] = finish(alpha, sum, beta, y + row_s + i);
+      else carry[t] = sum;
+    }
+    return;
+  }
+
+  // (3b) products in place, then the serial walk
+  T* sp = s_val + lo;
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) {
+    const int e = i * kThreads + tid;
+    if (e < tile_nnz) sp[e] = sp[e] * __ldg(x + sc[e]);
+  }
+  for (int i = tid; i < tile_rows; i += kThreads) s_rowend[i] = (int)((int64_t)rp[row_s + i + 1] - nz_s);
+  if (tid == 0) s_rowend[tile_rows] = INT_MAX;
+  __syncthreads();
+  const int tile_items = tile_rows + tile_nnz;
+  int d = tid * IPT;
+  if (d > tile_items) d = tile_items;
+  int d_end = d + IPT;
+  if (d_end > tile_items) d_end = tile_items;
+  int wl = d > tile_nnz ? d - tile_nnz : 0;
+  int wh = d < tile_rows ? d : tile_rows;
+  while (wl < wh) {
+    const int mid = (wl + wh) >> 1;
+    if (s_rowend[mid] <= d - mid - 1) wl = mid + 1;
+    else wh = mid;
+  }
+  int i = wl, j = d - wl;
+  T running = T(0), first_val = T(0);
+  int first_row = -1;
+#pragma unroll
+  for (int it = 0; it < IPT; ++it) {
+    if (d + it < d_end) {
+      if (j < s_rowend[i]) {
+        running += sp[j];
+        ++j;
+      } else {
+        if (first_row < 0) {
+          first_row = i;
+          first_val = running;
+        } else {
+          y[row_s + i] = finish(alpha, running, beta, y + row_s + i);
+        }
+        running = T(0);
+        ++i;
+      }
+    }
+  }
+  const int lane = tid & 31, warp = tid >> 5;
+  int flag = first_row >= 0 ? 1 : 0;
+  T acc = running;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const T pv = __shfl_up_sync(0xffffffffu, acc, o);
+    const int pf = __shfl_up_sync(0xffffffffu, flag, o);
+    if (lane >= o) {
+      if (!flag) acc += pv;
+      flag |= pf;
+    }
+  }
+  if (lane == 31) {
+    s_wval[warp] = acc;
+    s_wflag[warp] = flag;
+  }
+  T ev = __shfl_up_sync(0xffffffffu, acc, 1);
+  int ef = __shfl_up_sync(0xffffffffu, flag, 1);
+  if (lane == 0) {
+    ev = T(0);
+    ef = 0;
+  }
+  __syncthreads();
+  T pv = T(0);
+  for (int w = 0; w < warp; ++w) pv = s_wflag[w] ? s_wval[w] : pv + s_wval[w];
+  const T carry_in = ef ? ev : pv + ev;
+  if (first_row >= 0) {
+    const int r = row_s + first_row;
+    y[r] = finish(alpha, carry_in + first_val, beta, y + r);
+  }
+  if (tid == kThreads - 1) carry[t] = flag ? acc : pv + acc;
 }
 
 // Adds the sums that left tiles to the rows they belong to.  Tile t's carry belongs to row
@@ -351,11 +646,11 @@ __global__ void __launch_bounds__(256) spmv_merge_fixup_kernel(const int32_t* __
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
-template <typename T, typename OffT, bool VL>
+template <typename T, typename OffT, bool VL, int U>
 alphasparseStatus_t launch_binned(alphasparseHandle_t h, const Plan* p, const BinnedArgs<T, OffT>& a0) {
   BinnedArgs<T, OffT> a = a0;
   const int g = p->group_lanes;
-  const int rows_per_cta = (kThreads / g) * kShortUnroll;
+  const int rows_per_cta = (kThreads / g) * U;
   const int64_t cs = (p->n_short + rows_per_cta - 1) / rows_per_cta;
   const int64_t cm = (p->n_medium + (kThreads / 32) - 1) / (kThreads / 32);
   const int64_t total = cs + cm + p->n_long;
@@ -365,11 +660,11 @@ alphasparseStatus_t launch_binned(alphasparseHandle_t h, const Plan* p, const Bi
   a.cta_medium = (int)cm;
   const dim3 grid((unsigned)total), block(kThreads);
   switch (g) {
-    case 2: spmv_binned_kernel<T, OffT, 2, VL><<<grid, block, 0, h->stream>>>(a); break;
-    case 4: spmv_binned_kernel<T, OffT, 4, VL><<<grid, block, 0, h->stream>>>(a); break;
-    case 8: spmv_binned_kernel<T, OffT, 8, VL><<<grid, block, 0, h->stream>>>(a); break;
-    case 16: spmv_binned_kernel<T, OffT, 16, VL><<<grid, block, 0, h->stream>>>(a); break;
-    default: spmv_binned_kernel<T, OffT, 32, VL><<<grid, block, 0, h->stream>>>(a); break;
+    case 2: spmv_binned_kernel<T, OffT, 2, VL, U><<<grid, block, 0, h->stream>>>(a); break;
+    case 4: spmv_binned_kernel<T, OffT, 4, VL, U><<<grid, block, 0, h->stream>>>(a); break;
+    case 8: spmv_binned_kernel<T, OffT, 8, VL, U><<<grid, block, 0, h->stream>>>(a); break;
+    case 16: spmv_binned_kernel<T, OffT, 16, VL, U><<<grid, block, 0, h->stream>>>(a); break;
+    default: spmv_binned_kernel<T, OffT, 32, VL, U><<<grid, block, 0, h->stream>>>(a); break;
   }
   impl(h)->launches++;
   return status_of(cudaGetLastError());
@@ -391,11 +686,21 @@ alphasparseStatus_t spmv_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, Pla
     a.rows_long = p->identity_short ? nullptr : p->bin_rows + p->n_short + p->n_medium;
     a.n_short = p->n_short; a.n_medium = p->n_medium; a.n_long = p->n_long; a.nnz = p->nnz;
     a.cta_short = a.cta_medium = 0;
-    return vl ? launch_binned<T, OffT, true>(h, p, a) : launch_binned<T, OffT, false>(h, p, a);
+    if (!vl) return launch_binned<T, OffT, false, 2>(h, p, a);
+    return env_int("ASP_SHORT_UNROLL", kShortUnroll) >= 4 ? launch_binned<T, OffT, true, 4>(h, p, a)
+                                                          : launch_binned<T, OffT, true, 2>(h, p, a);
   }
   T* carry = reinterpret_cast<T*>(ext ? ext : p->carry);
   if (p->merge_tiles > INT_MAX) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
-  const dim3 grid((unsigned)p->merge_tiles), block(kThreads);
+  const dim3 grid((unsigned)p->merge_tiles), block(kMergeThreads);
+  if (vl && env_int("ASP_MERGE_TMA", 1)) {
+    spmv_tile_kernel<T, OffT><<<grid, kThreads, 0, h->stream>>>(rp, col, val, x, y, alpha, beta, p->rows, p->nnz,
+                                                              p->merge_tile_row, carry, p->dev_err);
+    spmv_merge_fixup_kernel<T><<<(unsigned)((p->merge_tiles + 255) / 256), 256, 0, h->stream>>>(
+        p->merge_tile_row, carry, p->merge_tiles, p->rows, y, alpha);
+    impl(h)->launches += 2;
+    return status_of(cudaGetLastError());
+  }
   if (vl)
     spmv_merge_kernel<T, OffT, true><<<grid, block, 0, h->stream>>>(
         rp, col, val, x, y, alpha, beta, p->rows, p->nnz, p->merge_tile_row, carry);
@@ -565,9 +870,9 @@ alphasparseStatus_t spmv_noalloc_t(cudaStream_t st, int64_t rows, int64_t nnz, c
   noalloc_tile_search_kernel<OffT><<<(unsigned)((tiles + 1 + 255) / 256), 256, 0, st>>>(rp, rows, nnz, tiles, tile_row);
   const bool vl = aligned(val, 16) && aligned(col, 16);
   if (vl)
-    spmv_merge_kernel<T, OffT, true><<<(unsigned)tiles, kThreads, 0, st>>>(rp, col, val, x, y, alpha, beta, rows, nnz, tile_row, carry);
+    spmv_merge_kernel<T, OffT, true><<<(unsigned)tiles, kMergeThreads, 0, st>>>(rp, col, val, x, y, alpha, beta, rows, nnz, tile_row, carry);
   else
-    spmv_merge_kernel<T, OffT, false><<<(unsigned)tiles, kThreads, 0, st>>>(rp, col, val, x, y, alpha, beta, rows, nnz, tile_row, carry);
+    spmv_merge_kernel<T, OffT, false><<<(unsigned)tiles, kMergeThreads, 0, st>>>(rp, col, val, x, y, alpha, beta, rows, nnz, tile_row, carry);
   spmv_merge_fixup_kernel<T><<<(unsigned)((tiles + 255) / 256), 256, 0, st>>>(tile_row, carry, tiles, rows, y, alpha);
   return status_of(cudaGetLastError());
 }

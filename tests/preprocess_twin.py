@@ -52,5 +52,5 @@ def plan(row_ptr, val_bytes):
     variant = 1 if (max_len > 16.0 * mean_all + SHORT_MAX or empty * 4 > rows) else 0
     stats = dict(max_len=max_len, empty_rows=empty, num_short=n_short, num_medium=n_medium,
                  num_long=n_long, group_lanes=g, merge_items=MERGE_ITEMS, merge_tiles=tiles,
-                 variant=variant, identity_short=int(n_short == rows), nnz_short=nnz_short)
+                 variant=variant, identity_short=int(n_short == rows), nnz_short=nnz_short, device_error=0)
     return stats, bins, tile_row
