@@ -109,6 +109,25 @@ __global__ void __launch_bounds__(256) merge_tile_kernel(const OffT* __restrict_
 }
 
 template <typename OffT>
+__global__ void __launch_bounds__(256) block_nnz_max_kernel(const OffT* __restrict__ rp, int64_t rows,
+                                                            int64_t blocks,
+                                                            unsigned long long* __restrict__ out) {
+  unsigned long long m = 0;
+  for (int64_t b = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; b < blocks;
+       b += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r0 = b * kSpmmRowBlock;
+    const int64_t r1 = r0 + kSpmmRowBlock < rows ? r0 + kSpmmRowBlock : rows;
+    const unsigned long long n = (unsigned long long)((int64_t)rp[r1] - (int64_t)rp[r0]);
+    if (n > m) m = n;
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long w = __shfl_xor_sync(0xffffffffu, m, o);
+    if (w > m) m = w;
+  }
+  if ((threadIdx.x & 31) == 0 && m) atomicMax(out, m);
+}
+
+template <typename OffT>
 __global__ void partition_kernel(const OffT* __restrict__ rp, int64_t rows, int parts,
                                  int64_t* __restrict__ bounds) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -245,14 +264,29 @@ alphasparseStatus_t analyse_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, 
   ASP_CUDA(cudaGetLastError());
   ASP_CUDA(cudaStreamSynchronize(st));
 
-  // Variant choice: the binned kernel gives every row of a class the same lane count, so it
-  // loses when lengths inside the matrix differ by orders of magnitude or when many rows are
-  // empty (idle groups); merge-path gives every CTA the same number of items regardless.
+  // Variant choice.  The merge-path tile kernel streams A through the copy engine and gives every
+  // CTA the same number of items whatever the row lengths are; it wins on everything measured
+  // except problems so small that they are bound by launch latency, where the binned kernel's
+  // single launch (no carry fix-up kernel) is shorter.
+  p->variant_auto = (p->merge_tiles < kSmallProblemTiles) ? kVariantBinned : kVariantMerge;
+
+  // SpMM: the largest number of entries in an aligned block of kSpmmRowBlock rows decides whether
+  // a block's entries fit the staging buffer of the TMA-fed SpMM kernel.
   {
-    const double mean_all = p->rows > 0 ? (double)p->nnz / (double)p->rows : 0.0;
-    const bool skewed = (double)p->max_len > 16.0 * mean_all + kShortMax;
-    const bool sparse_rows = p->empty_rows * 4 > p->rows;
-    p->variant_auto = (skewed || sparse_rows) ? kVariantMerge : kVariantBinned;
+    unsigned long long* d_max = nullptr;
+    ASP_CUDA(cudaMalloc(&d_max, sizeof(unsigned long long)));
+    ASP_CUDA(cudaMemsetAsync(d_max, 0, sizeof(unsigned long long), st));
+    const int64_t blocks = (p->rows + kSpmmRowBlock - 1) / kSpmmRowBlock;
+    if (blocks > 0) {
+      block_nnz_max_kernel<OffT><<<grid_for(blocks, sms), 256, 0, st>>>(rp, p->rows, blocks, d_max);
+      impl(h)->launches++;
+    }
+    unsigned long long m = 0;
+    cudaError_t e = cudaMemcpyAsync(&m, d_max, sizeof m, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(d_max);
+    if (e != cudaSuccess) return status_of(e);
+    p->max_block_nnz = (int64_t)m;
   }
   return ALPHA_SPARSE_STATUS_SUCCESS;
 }

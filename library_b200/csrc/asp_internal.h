@@ -22,6 +22,13 @@ constexpr int kShortUnroll = 2;      // rows in flight per lane group
 constexpr int kMergeIpt = 8;
 constexpr int kMergeItems = kThreads * kMergeIpt;
 
+// Fewer merge tiles than this (about 2.5 M items): the matrix is L2-resident and launch-bound.
+constexpr int64_t kSmallProblemTiles = 1200;
+// SpMM: rows per CTA and entries of A a CTA can stage at once.
+constexpr int kSpmmRowBlock = 128;
+constexpr int kSpmmStageCap32 = 4096;  // 4-byte values
+constexpr int kSpmmStageCap64 = 3584;  // 8-byte values (48 KB of static shared memory)
+
 enum Variant { kVariantBinned = 0, kVariantMerge = 1 };
 
 struct HandleImpl {
@@ -49,6 +56,7 @@ struct Plan {
   int variant_auto = kVariantBinned;
   int last_variant = -1;
   // SpMM
+  int64_t max_block_nnz = 0;          // most entries in an aligned block of kSpmmRowBlock rows
   void* spmm_tc = nullptr;            // plan of the tcgen05 variant (spmm_tc.cu)
 };
 

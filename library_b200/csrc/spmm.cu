@@ -133,6 +133,172 @@ spmm_rowblock_kernel(const OffT* __restrict__ rp, const int* __restrict__ col,
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// TMA-staged row-block kernel (default when every 128-row block of A has at most kSpmmStageCap32/64
+// entries and the operands are 16-byte aligned).  A CTA owns kSpmmRowBlock consecutive rows and
+// one slab of LN*VN columns of C:
+//   (1) an elected thread asks the copy engine for the block's value and column slices (two 1-D
+//       bulk copies counted on an mbarrier; slices widened to groups of four entries, the few
+//       entries past the arrays' last full group fetched with plain loads) while all threads
+//       stage the block's row offsets;
+//   (2) LN lanes share a row and keep VN adjacent columns of C each.  A group reads four
+//       (column, value) pairs with two 16-byte shared-memory loads, issues the four matching row
+//       segments of B as 16-byte global loads and then does the sixteen FMAs; the groups of a
+//       warp work on neighbouring rows at the same time, so for banded matrices a warp's B loads
+//       fall into a few cache lines.
+// Arithmetic and order are those of spmm_rowblock_kernel: C row := beta*C row, then
+// fma(alpha*a, b, c) entry by entry.  The wait on the mbarrier is bounded.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ bool mbar_try_wait0(uint64_t* bar) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar))
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+template <typename T, typename OffT, int LN, int VN>
+__global__ void __launch_bounds__(kThreads)
+spmm_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const T* __restrict__ val,
+                 const T* __restrict__ B, int64_t ldb, T* __restrict__ C, int64_t ldc, T alpha, T beta,
+                 int64_t rows, int64_t n, int64_t nnz, int* __restrict__ err) {
+  constexpr int NG = kThreads / LN;
+  constexpr int RB = kSpmmRowBlock;
+  constexpr int RPG = RB >= NG ? RB / NG : 1;  // with one lane per row half the groups of a CTA idle
+  constexpr int CAP = sizeof(T) == 4 ? kSpmmStageCap32 : kSpmmStageCap64;
+  static_assert(RB % NG == 0 || NG > RB, "row block must be a multiple of the groups per CTA");
+  __shared__ __align__(128) T s_val[CAP + 8];
+  __shared__ __align__(128) int s_col[CAP + 8];
+  __shared__ int s_rp[RB + 1];
+  __shared__ __align__(8) uint64_t s_bar;
+
+  const int tid = threadIdx.x;
+  const int lane = tid % LN;
+  const int grp = tid / LN;
+  const int64_t r0 = (int64_t)blockIdx.x * RB;
+  const int nr = (int)(r0 + RB < rows ? RB : rows - r0);
+  const int64_t c0 = ((int64_t)blockIdx.y * LN + lane) * VN;
+  const bool col_ok = c0 < n;
+  const int64_t e0 = (int64_t)rp[r0], e1 = (int64_t)rp[r0 + nr];
+  const int64_t a0 = e0 & ~(int64_t)3;
+  const int lo = (int)(e0 - a0);
+
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s_bar)) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const int64_t nnz4 = nnz & ~(int64_t)3;
+    int64_t a1 = (e1 + 3) & ~(int64_t)3;
+    if (a1 > nnz4) a1 = nnz4;
+    if (a1 < a0) a1 = a0;
+    const uint32_t cnt = (uint32_t)(a1 - a0);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&s_bar)),
+                 "r"(cnt * (uint32_t)(sizeof(T) + sizeof(int)))
+                 : "memory");
+    if (cnt) {
+      bulk_g2s(s_val, val + a0, cnt * (uint32_t)sizeof(T), &s_bar);
+      bulk_g2s(s_col, col + a0, cnt * (uint32_t)sizeof(int), &s_bar);
+    }
+    for (int64_t e = a1 > e0 ? a1 : e0; e < e1; ++e) {
+      s_val[e - a0] = val[e];
+      s_col[e - a0] = col[e];
+    }
+  }
+  for (int i = tid; i <= nr; i += kThreads) s_rp[i] = (int)((int64_t)rp[r0 + i] - a0);  // index into s_val/s_col
+  __syncthreads();
+  bool failed = false;
+  {
+    uint32_t tries = 0;
+    while (!mbar_try_wait0(&s_bar)) {
+      if (++tries > (1u << 22)) {
+        failed = true;
+        break;
+      }
+    }
+  }
+  if (__syncthreads_or(failed ? 1 : 0)) {
+    if (tid == 0) atomicExch(err, 1);
+    __nanosleep(1000000);
+    return;
+  }
+  (void)lo;
+  if (!col_ok) return;
+
+#pragma unroll 1
+  for (int i = 0; i < RPG; ++i) {
+    const int lr = grp + i * NG;  // neighbouring groups take neighbouring rows
+    if (lr >= nr) break;
+    const int64_t r = r0 + lr;
+    int k = s_rp[lr];
+    const int e = s_rp[lr + 1];
+    T acc[VN];
+#pragma unroll
+    for (int v = 0; v < VN; ++v) acc[v] = T(0);
+    if (beta != T(0)) {
+      T c[VN];
+      load_pack<T, VN>(C + r * ldc + c0, c);
+#pragma unroll
+      for (int v = 0; v < VN; ++v) acc[v] = c[v] * beta;
+    }
+    const T* __restrict__ Bc = B + c0;
+    // entries up to the next group of four in shared memory
+    for (; (k & 3) && k < e; ++k) {
+      const T a = alpha * s_val[k];
+      T b[VN];
+      load_pack<T, VN>(Bc + (int64_t)s_col[k] * ldb, b);
+#pragma unroll
+      for (int v = 0; v < VN; ++v) acc[v] = fma(a, b[v], acc[v]);
+    }
+    for (; k + 4 <= e; k += 4) {
+      const int4 cc = *reinterpret_cast<const int4*>(s_col + k);
+      T a[4];
+      if constexpr (sizeof(T) == 4) {
+        const float4 vv = *reinterpret_cast<const float4*>(s_val + k);
+        a[0] = vv.x; a[1] = vv.y; a[2] = vv.z; a[3] = vv.w;
+      } else {
+        const double2 v0 = *reinterpret_cast<const double2*>(s_val + k);
+        const double2 v1 = *reinterpret_cast<const double2*>(s_val + k + 2);
+        a[0] = v0.x; a[1] = v0.y; a[2] = v1.x; a[3] = v1.y;
+      }
+      T b0[VN], b1[VN], b2[VN], b3[VN];
+      load_pack<T, VN>(Bc + (int64_t)cc.x * ldb, b0);
+      load_pack<T, VN>(Bc + (int64_t)cc.y * ldb, b1);
+      load_pack<T, VN>(Bc + (int64_t)cc.z * ldb, b2);
+      load_pack<T, VN>(Bc + (int64_t)cc.w * ldb, b3);
+      const T a0s = alpha * a[0], a1s = alpha * a[1], a2s = alpha * a[2], a3s = alpha * a[3];
+#pragma unroll
+      for (int v = 0; v < VN; ++v) acc[v] = fma(a0s, b0[v], acc[v]);
+#pragma unroll
+      for (int v = 0; v < VN; ++v) acc[v] = fma(a1s, b1[v], acc[v]);
+#pragma unroll
+      for (int v = 0; v < VN; ++v) acc[v] = fma(a2s, b2[v], acc[v]);
+#pragma unroll
+      for (int v = 0; v < VN; ++v) acc[v] = fma(a3s, b3[v], acc[v]);
+    }
+    for (; k < e; ++k) {
+      const T a = alpha * s_val[k];
+      T b[VN];
+      load_pack<T, VN>(Bc + (int64_t)s_col[k] * ldb, b);
+#pragma unroll
+      for (int v = 0; v < VN; ++v) acc[v] = fma(a, b[v], acc[v]);
+    }
+    store_pack<T, VN>(C + r * ldc + c0, acc);
+  }
+}
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 template <typename T, typename OffT, int LN, int VN>
@@ -150,6 +316,20 @@ alphasparseStatus_t launch_rb(alphasparseHandle_t h, alphasparseSpMatDescr_t A, 
   return status_of(cudaGetLastError());
 }
 
+template <typename T, typename OffT, int LN, int VN>
+alphasparseStatus_t launch_tile(alphasparseHandle_t h, alphasparseSpMatDescr_t A, const T* B,
+                                int64_t ldb, T* C, int64_t ldc, T alpha, T beta, int64_t n) {
+  const int64_t gx = (A->rows + kSpmmRowBlock - 1) / kSpmmRowBlock;
+  const int64_t gy = (n + (int64_t)LN * VN - 1) / ((int64_t)LN * VN);
+  if (gx > INT_MAX || gy > 65535) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  spmm_tile_kernel<T, OffT, LN, VN><<<dim3((unsigned)gx, (unsigned)gy), kThreads, 0, h->stream>>>(
+      reinterpret_cast<const OffT*>(A->row_offsets), A->const_col_data,
+      reinterpret_cast<const T*>(A->const_val_data), B, ldb, C, ldc, alpha, beta, A->rows, n, A->nnz,
+      plan_of(A)->dev_err);
+  impl(h)->launches++;
+  return status_of(cudaGetLastError());
+}
+
 template <typename T, typename OffT>
 alphasparseStatus_t spmm_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, const T* B, int64_t ldb,
                            T* C, int64_t ldc, T alpha, T beta, int64_t n) {
@@ -158,6 +338,16 @@ alphasparseStatus_t spmm_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, con
   const bool vec = (n % VN == 0) && (ldb % VN == 0) && (ldc % VN == 0) && aligned(B, 16) && aligned(C, 16);
   if (!vec) return launch_rb<T, OffT, 32, 1>(h, A, B, ldb, C, ldc, alpha, beta, n);
   const int64_t lanes = n / VN;
+  const bool tile_ok = plan_of(A)->max_block_nnz <= (sizeof(T) == 4 ? kSpmmStageCap32 : kSpmmStageCap64) && aligned(A->const_val_data, 16) &&
+                       aligned(A->const_col_data, 16) && env_int("ASP_SPMM_TMA", 1);
+  if (tile_ok) {
+    if (lanes <= 1) return launch_tile<T, OffT, 1, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
+    if (lanes <= 2) return launch_tile<T, OffT, 2, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
+    if (lanes <= 4) return launch_tile<T, OffT, 4, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
+    if (lanes <= 8) return launch_tile<T, OffT, 8, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
+    if (lanes <= 16) return launch_tile<T, OffT, 16, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
+    return launch_tile<T, OffT, 32, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
+  }
   if (lanes <= 1) return launch_rb<T, OffT, 1, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
   if (lanes <= 2) return launch_rb<T, OffT, 2, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
   if (lanes <= 4) return launch_rb<T, OffT, 4, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);

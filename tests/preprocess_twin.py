@@ -12,6 +12,7 @@ import numpy as np
 SHORT_MAX = 64
 MEDIUM_MAX = 4096
 MERGE_ITEMS = 2048
+SMALL_PROBLEM_TILES = 1200
 
 
 def merge_path_row(row_end, nnz, diag):
@@ -49,7 +50,7 @@ def plan(row_ptr, val_bytes):
                          for t in range(tiles + 1)], dtype=np.int32)
     max_len = int(lens.max()) if rows > 0 else 0
     mean_all = nnz / rows if rows > 0 else 0.0
-    variant = 1 if (max_len > 16.0 * mean_all + SHORT_MAX or empty * 4 > rows) else 0
+    variant = 0 if tiles < SMALL_PROBLEM_TILES else 1
     stats = dict(max_len=max_len, empty_rows=empty, num_short=n_short, num_medium=n_medium,
                  num_long=n_long, group_lanes=g, merge_items=MERGE_ITEMS, merge_tiles=tiles,
                  variant=variant, identity_short=int(n_short == rows), nnz_short=nnz_short, device_error=0)
