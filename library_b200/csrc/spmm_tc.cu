@@ -1,14 +1,476 @@
-// tcgen05 tensor-core SpMM variant (bf16 A and B, fp32 C).  Placeholder translation unit
-// until the kernel lands: reports the variant as not applicable.
+// Tensor-core SpMM for sm_100a:  C(fp32) = alpha * A(bf16, CSR) * B(bf16, row-major) + beta * C.
+//
+// The reference's CUDA backend has no tensor-core SpMM (its bf16 dispatch is commented out,
+// cuda/kernel/level3/alphasparse_spmm.cu:597-610).  The precedent is the HIP backend's
+// matrix-core algorithm ALG6 (hip/kernel/level3/alphasparse_spmm_tc4csr.h:43-255): a host pass
+// turns CSR into dense 16x4 blocks, one wavefront then multiplies a 16x16 tile of C.  This file
+// keeps the idea - treat the non-empty column blocks of a row block as small dense matrices -
+// and rebuilds it for tcgen05:
+//   * preprocessing (device): for every block of 128 rows, the ascending list of 64-column
+//     chunks that hold at least one entry (a bitmap per row block, a scan, a fill);
+//   * the kernel: one CTA per row block.  For each chunk, the 64 x N slice of B is fetched by
+//     TMA (cp.async.bulk.tensor, 128-byte swizzle, completion on an mbarrier) while the CTA's
+//     128 threads scatter their rows' entries of that chunk into a zeroed 128 x 64 bf16 tile in
+//     shared memory; one thread then issues four tcgen05.mma (M=128, N, K=16) that accumulate
+//     into tensor memory, and tcgen05.commit releases the stage.  Two stages overlap the next
+//     chunk's TMA and scatter with the current chunk's MMAs.  The epilogue reads the fp32
+//     accumulators with tcgen05.ld and writes alpha*acc + beta*C.
+// Every mbarrier wait is bounded; on expiry the CTA raises *err, frees its tensor memory and
+// leaves.  No TMA load here uses cluster multicast.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cub/device/device_scan.cuh>
+
+#include <new>
+
 #include "asp_internal.h"
 
 namespace asp {
-void free_spmm_tc_plan(void*) {}
-bool spmm_tc_applicable(alphasparseSpMatDescr_t, alphasparseDnMatDescr_t, alphasparseDnMatDescr_t) {
+
+namespace {
+
+constexpr int TC_M = 128;       // rows per CTA (the MMA's M)
+constexpr int TC_KC = 64;       // columns of A per chunk (four K=16 MMAs)
+constexpr int TC_THREADS = 128;
+constexpr int TC_SPAN_WORDS = 2048;  // bitmap words: a row block may span 65,536 chunks
+constexpr uint32_t TC_MAX_TRIES = 1u << 22;
+constexpr int TC_A_BYTES = TC_M * TC_KC * 2;  // 16 KB, K-major core matrices, no swizzle
+
+struct TcPlan {
+  int64_t blocks = 0, total_chunks = 0;
+  int max_chunks = 0;
+  bool usable = false;  // sorted columns, chunk span within the bitmap
+  int32_t* chunk_off = nullptr;   // device, blocks + 1
+  int32_t* chunk_list = nullptr;  // device, total_chunks
+};
+
+// ---- preprocessing -------------------------------------------------------------------------
+// One CTA per row block.  FILL = false: counts[b] = number of non-empty chunks, flags[0] |= 1 if
+// the block spans more chunks than the bitmap, flags[1] |= 1 if a row's columns are not
+// ascending.  FILL = true: writes the chunk ids, ascending, at chunk_off[b].
+template <bool FILL>
+__global__ void __launch_bounds__(256) tc_chunks_kernel(const int32_t* __restrict__ rp,
+                                                        const int32_t* __restrict__ col, int64_t rows,
+                                                        int32_t* __restrict__ counts,
+                                                        const int32_t* __restrict__ chunk_off,
+                                                        int32_t* __restrict__ chunk_list,
+                                                        int* __restrict__ flags) {
+  __shared__ unsigned bm[TC_SPAN_WORDS];
+  __shared__ int s_min;
+  __shared__ int s_scan[256];
+  const int tid = threadIdx.x;
+  const int64_t r0 = (int64_t)blockIdx.x * TC_M;
+  const int64_t r1 = r0 + TC_M < rows ? r0 + TC_M : rows;
+  const int e0 = rp[r0], e1 = rp[r1];
+  for (int i = tid; i < TC_SPAN_WORDS; i += 256) bm[i] = 0u;
+  if (tid == 0) s_min = INT_MAX;
+  __syncthreads();
+  int mn = INT_MAX;
+  for (int k = e0 + tid; k < e1; k += 256) mn = min(mn, col[k]);
+  for (int o = 16; o > 0; o >>= 1) mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+  if ((tid & 31) == 0 && mn != INT_MAX) atomicMin(&s_min, mn);
+  __syncthreads();
+  const int base = s_min == INT_MAX ? 0 : s_min / TC_KC;
+  bool over = false;
+  for (int k = e0 + tid; k < e1; k += 256) {
+    const int c = col[k] / TC_KC - base;
+    if (c >= TC_SPAN_WORDS * 32) over = true;
+    else atomicOr(&bm[c >> 5], 1u << (c & 31));
+  }
+  if (!FILL) {
+    bool unsorted = false;
+    if (tid < (int)(r1 - r0)) {
+      const int s = rp[r0 + tid], e = rp[r0 + tid + 1];
+      for (int k = s + 1; k < e; ++k) unsorted |= col[k] < col[k - 1];
+    }
+    if (over) atomicOr(&flags[0], 1);
+    if (unsorted) atomicOr(&flags[1], 1);
+  }
+  __syncthreads();
+  // 8 words per thread, block-wide exclusive scan of the popcounts
+  int cnt = 0;
+#pragma unroll
+  for (int w = 0; w < TC_SPAN_WORDS / 256; ++w) cnt += __popc(bm[tid * (TC_SPAN_WORDS / 256) + w]);
+  s_scan[tid] = cnt;
+  __syncthreads();
+  for (int o = 1; o < 256; o <<= 1) {
+    const int v = tid >= o ? s_scan[tid - o] : 0;
+    __syncthreads();
+    s_scan[tid] += v;
+    __syncthreads();
+  }
+  if (!FILL) {
+    if (tid == 255) counts[blockIdx.x] = s_scan[255];
+  } else {
+    int pos = chunk_off[blockIdx.x] + s_scan[tid] - cnt;
+    for (int w = 0; w < TC_SPAN_WORDS / 256; ++w) {
+      unsigned bits = bm[tid * (TC_SPAN_WORDS / 256) + w];
+      while (bits) {
+        const int b = __ffs(bits) - 1;
+        bits &= bits - 1;
+        chunk_list[pos++] = base + (tid * (TC_SPAN_WORDS / 256) + w) * 32 + b;
+      }
+    }
+  }
+}
+
+// ---- PTX helpers ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false if the phase did not complete within TC_MAX_TRIES polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < TC_MAX_TRIES; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
-alphasparseStatus_t spmm_tc_run(alphasparseHandle_t, alphasparseSpMatDescr_t, alphasparseDnMatDescr_t,
-                                alphasparseDnMatDescr_t, float, float, bool) {
-  return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
 }
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+  return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+// Byte offset of element (row r, column k) in the 128 x 64 bf16 A tile: K-major core matrices
+// of 8 rows x 8 columns (128 contiguous bytes), 16 of them down the rows (stride 128 B), 8
+// across the columns (stride 2,048 B).  This is the no-swizzle canonical layout of the MMA's
+// shared-memory descriptor with SBO = 128 and LBO = 2,048.
+__device__ __forceinline__ int a_tile_off(int r, int k) {
+  return (k >> 3) * 2048 + (r >> 3) * 128 + (r & 7) * 16 + (k & 7) * 2;
+}
+
+__global__ void __launch_bounds__(TC_THREADS)
+spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restrict__ rp,
+               const int32_t* __restrict__ col, const __nv_bfloat16* __restrict__ val,
+               float* __restrict__ C, int64_t ldc, float alpha, float beta, int64_t rows, int n,
+               const int32_t* __restrict__ chunk_off, const int32_t* __restrict__ chunk_list,
+               int* __restrict__ err) {
+  extern __shared__ unsigned char smem_raw[];
+  // the swizzled B boxes (and the descriptors' address arithmetic) need a 1,024-byte aligned base
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const int nblk = n / 64;                      // 64-column boxes of B per chunk
+  const int b_stage_bytes = nblk * 8192;        // 64 rows x 128 B per box
+  unsigned char* sA = smem;                     // 2 x 16 KB
+  unsigned char* sB = smem + 2 * TC_A_BYTES;    // 2 x b_stage_bytes, 1,024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sB + 2 * b_stage_bytes);
+  uint64_t* full = bars;          // [2] B slice landed
+  uint64_t* done = bars + 2;      // [2] MMAs that read the stage retired
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 4);
+  int* s_fail = reinterpret_cast<int*>(s_tmem + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int64_t r0 = (int64_t)blockIdx.x * TC_M;
+  const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
+  const int j0 = chunk_off[blockIdx.x], j1 = chunk_off[blockIdx.x + 1];
+  const int nchunks = j1 - j0;
+  const uint32_t tmem_cols = n <= 64 ? 64u : (n <= 128 ? 128u : 256u);
+
+  // zero both A tiles, set up barriers and tensor memory
+  for (int i = tid; i < 2 * TC_A_BYTES / 16; i += TC_THREADS) reinterpret_cast<uint4*>(sA)[i] = make_uint4(0, 0, 0, 0);
+  if (tid == 0) {
+    mbar_init(&full[0], 1);
+    mbar_init(&full[1], 1);
+    mbar_init(&done[0], 1);
+    mbar_init(&done[1], 1);
+    *s_fail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
+                 "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *s_tmem;
+
+  // instruction descriptor: D fp32, A and B bf16, A K-major, B MN-major, N = n, M = 128
+  const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(n >> 3) << 17) |
+                         ((uint32_t)(TC_M >> 4) << 24);
+
+  // this thread's row of A: entries are consumed in column order as the chunks advance
+  int k = 0, k_end = 0;
+  if (tid < nr) {
+    k = rp[r0 + tid];
+    k_end = rp[r0 + tid + 1];
+  }
+  int wb[2] = {0, 0}, we[2] = {0, 0}, wc[2] = {0, 0};  // what this thread wrote into each stage
+  bool ok = true;
+
+  for (int j = 0; j < nchunks; ++j) {
+    const int s = j & 1;
+    const int chunk = chunk_list[j0 + j];
+    if (j >= 2) {
+      // the MMAs of chunk j-2 must have finished reading this stage
+      if (ok && !mbar_wait(&done[s], (uint32_t)(((j >> 1) - 1) & 1))) ok = false;
+    }
+    if (tid == 0 && ok) {
+      mbar_expect_tx(&full[s], (uint32_t)b_stage_bytes);
+      for (int i = 0; i < nblk; ++i)
+        tma_load_2d(sB + s * b_stage_bytes + i * 8192, &tmB, i * 64, chunk * TC_KC, &full[s]);
+    }
+    // clear what this thread put into the stage two chunks ago, then scatter the new entries
+    unsigned char* tile = sA + s * TC_A_BYTES;
+    for (int q = wb[s]; q < we[s]; ++q)
+      *reinterpret_cast<unsigned short*>(tile + a_tile_off(tid, col[q] - wc[s])) = 0;
+    const int cbeg = chunk * TC_KC, cend = cbeg + TC_KC;
+    wb[s] = k;
+    wc[s] = cbeg;
+    while (k < k_end) {
+      const int c = col[k];
+      if (c >= cend) break;
+      *reinterpret_cast<__nv_bfloat16*>(tile + a_tile_off(tid, c - cbeg)) = val[k];
+      ++k;
+    }
+    we[s] = k;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // tile writes -> visible to the MMA
+    const int any_fail = __syncthreads_or(ok ? 0 : 1);
+    if (any_fail) {
+      ok = false;
+      break;
+    }
+    if (tid == 0) {
+      if (!mbar_wait(&full[s], (uint32_t)((j >> 1) & 1))) {
+        *s_fail = 1;
+      } else {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_base = smem_u32(tile);
+        const uint32_t b_base = smem_u32(sB + s * b_stage_bytes);
+#pragma unroll
+        for (int kk = 0; kk < TC_KC / 16; ++kk) {
+          const uint64_t ad = umma_desc(a_base + kk * 4096, 2048, 128, 0);   // no swizzle, K-major
+          const uint64_t bd = umma_desc(b_base + kk * 2048, 8192, 1024, 2);  // 128-byte swizzle, MN-major
+          umma_bf16(tmem, ad, bd, idesc, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&done[s]);
+      }
+    }
+  }
+
+  // wait for the last chunk's MMAs, then the epilogue
+  if (ok && nchunks > 0) {
+    const int jl = nchunks - 1;
+    if (!mbar_wait(&done[jl & 1], (uint32_t)((jl >> 1) & 1))) ok = false;
+  }
+  const int bad = __syncthreads_or((ok ? 0 : 1) | *s_fail);
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (!bad) {
+    const int row = tid;  // warp w reads tensor-memory lanes 32w .. 32w+31
+    float* crow = C + (r0 + row) * ldc;
+    for (int cb = 0; cb < n; cb += 32) {
+      uint32_t acc[32];
+      if (nchunks > 0) {
+        tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)cb, acc);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[i] = 0u;
+      }
+      if (row < nr) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          float4 o;
+          o.x = alpha * __uint_as_float(acc[i]);
+          o.y = alpha * __uint_as_float(acc[i + 1]);
+          o.z = alpha * __uint_as_float(acc[i + 2]);
+          o.w = alpha * __uint_as_float(acc[i + 3]);
+          if (beta != 0.f) {
+            const float4 c0 = *reinterpret_cast<const float4*>(crow + cb + i);
+            o.x = fmaf(beta, c0.x, o.x);
+            o.y = fmaf(beta, c0.y, o.y);
+            o.z = fmaf(beta, c0.z, o.z);
+            o.w = fmaf(beta, c0.w, o.w);
+          }
+          *reinterpret_cast<float4*>(crow + cb + i) = o;
+        }
+      }
+    }
+  } else {
+    if (tid == 0) atomicExch(err, 1);
+    __nanosleep(1000000);  // give copies and MMAs still in flight time to retire
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+alphasparseStatus_t build_plan(alphasparseHandle_t h, alphasparseSpMatDescr_t A, TcPlan* tp) {
+  cudaStream_t st = h->stream;
+  tp->blocks = (A->rows + TC_M - 1) / TC_M;
+  if (tp->blocks == 0 || tp->blocks > INT_MAX) return ALPHA_SPARSE_STATUS_SUCCESS;
+  int32_t* counts = nullptr;
+  int* flags = nullptr;
+  ASP_CUDA(cudaMalloc(&counts, sizeof(int32_t) * (tp->blocks + 1)));
+  ASP_CUDA(cudaMalloc(&flags, 2 * sizeof(int)));
+  ASP_CUDA(cudaMalloc(&tp->chunk_off, sizeof(int32_t) * (tp->blocks + 1)));
+  ASP_CUDA(cudaMemsetAsync(flags, 0, 2 * sizeof(int), st));
+  ASP_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t) * (tp->blocks + 1), st));
+  tc_chunks_kernel<false><<<(unsigned)tp->blocks, 256, 0, st>>>(A->const_row_data, A->const_col_data, A->rows,
+                                                               counts, nullptr, nullptr, flags);
+  size_t tmp_bytes = 0;
+  cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, counts, tp->chunk_off, (int)(tp->blocks + 1), st);
+  void* tmp = nullptr;
+  ASP_CUDA(cudaMalloc(&tmp, tmp_bytes ? tmp_bytes : 16));
+  cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, counts, tp->chunk_off, (int)(tp->blocks + 1), st);
+  int hflags[2] = {0, 0};
+  int32_t total = 0;
+  cudaError_t e = cudaMemcpyAsync(hflags, flags, sizeof hflags, cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess)
+    e = cudaMemcpyAsync(&total, tp->chunk_off + tp->blocks, sizeof total, cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  impl(h)->launches += 3;
+  cudaFree(tmp);
+  cudaFree(flags);
+  if (e != cudaSuccess) {
+    cudaFree(counts);
+    return status_of(e);
+  }
+  tp->total_chunks = total;
+  tp->usable = hflags[0] == 0 && hflags[1] == 0;
+  if (tp->usable && total > 0) {
+    if (cudaMalloc(&tp->chunk_list, sizeof(int32_t) * (size_t)total) != cudaSuccess) {
+      cudaFree(counts);
+      return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    tc_chunks_kernel<true><<<(unsigned)tp->blocks, 256, 0, st>>>(A->const_row_data, A->const_col_data, A->rows,
+                                                                nullptr, tp->chunk_off, tp->chunk_list, nullptr);
+    impl(h)->launches++;
+    e = cudaStreamSynchronize(st);
+  }
+  cudaFree(counts);
+  return status_of(e);
+}
+
+}  // namespace
+
+void free_spmm_tc_plan(void* p) {
+  TcPlan* tp = reinterpret_cast<TcPlan*>(p);
+  if (!tp) return;
+  cudaFree(tp->chunk_off);
+  cudaFree(tp->chunk_list);
+  delete tp;
+}
+
+// Shapes and types the kernel handles; the density test needs the plan and is done in spmm_tc_run.
+bool spmm_tc_applicable(alphasparseSpMatDescr_t A, alphasparseDnMatDescr_t B, alphasparseDnMatDescr_t C) {
+  const int64_t n = C->cols;
+  return A->data_type == ALPHA_R_16BF && B->data_type == ALPHA_R_16BF && C->data_type == ALPHA_R_32F &&
+         A->row_type == ALPHA_SPARSE_INDEXTYPE_I32 && n >= 64 && n <= 256 && n % 64 == 0 && B->ld % 8 == 0 &&
+         C->ld % 4 == 0 && aligned(B->values, 16) && aligned(C->values, 16) && A->cols < (int64_t(1) << 31);
+}
+
+alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A, alphasparseDnMatDescr_t B,
+                                alphasparseDnMatDescr_t C, float alpha, float beta, bool preprocess_only) {
+  Plan* p = plan_of(A);
+  if (!p) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+  if (!p->spmm_tc) {
+    TcPlan* tp = new (std::nothrow) TcPlan();
+    if (!tp) return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    alphasparseStatus_t s = build_plan(h, A, tp);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) {
+      free_spmm_tc_plan(tp);
+      return s;
+    }
+    p->spmm_tc = tp;
+  }
+  TcPlan* tp = reinterpret_cast<TcPlan*>(p->spmm_tc);
+  const int n = (int)C->cols;
+  // Dense enough: the MMA work over all non-empty chunks (at the sustained bf16 rate) must stay
+  // within three times the time HBM needs for the algorithmic bytes.
+  const double t_mma = (double)tp->total_chunks * TC_M * TC_KC * n * 2.0 / 1.39e15;
+  const double t_hbm = ((double)A->nnz * 6.0 + (double)A->cols * n * 2.0 + (double)A->rows * n * 4.0) / 6.55e12;
+  if (!tp->usable || t_mma > 3.0 * t_hbm) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (preprocess_only || A->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return ALPHA_SPARSE_STATUS_INTERNAL_ERROR;
+  CUtensorMap tm;
+  const cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)B->rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)B->ld * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)TC_KC};
+  const cuuint32_t estr[2] = {1, 1};
+  if (enc(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B->values, dims, strides, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+
+  const size_t smem = 2 * TC_A_BYTES + 2 * (size_t)(n / 64) * 8192 + 64 + 1024;
+  static size_t attr_bytes = 0;
+  if (smem > attr_bytes) {
+    ASP_CUDA(cudaFuncSetAttribute(spmm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_bytes = smem;
+  }
+  spmm_tc_kernel<<<(unsigned)tp->blocks, TC_THREADS, smem, h->stream>>>(
+      tm, A->const_row_data, A->const_col_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
+      reinterpret_cast<float*>(C->values), C->ld, alpha, beta, A->rows, n, tp->chunk_off, tp->chunk_list,
+      p->dev_err);
+  impl(h)->launches++;
+  return status_of(cudaGetLastError());
+}
+
 }  // namespace asp

@@ -1,0 +1,102 @@
+"""tcgen05 SpMM (bf16 A and B, fp32 accumulation and C) through the C ABI against the CPU oracle
+of the same arithmetic.  Tolerance: relative L2 1e-2 (the stated bound for bf16 operands); the
+products are exact in fp32 and only the summation order differs, so the observed error is
+orders of magnitude smaller and is also checked against 1e-5."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import rel_l2
+from library_b200 import api
+from library_b200 import generators as G
+
+pytestmark = pytest.mark.gpu
+
+
+def bits(t):
+    return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def run_tc(handle, A, X, Y0, alpha, beta, ldx=None, ldy=None):
+    dev = "cuda"
+    Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr.to(dev), A.col_idx.to(dev), A.val.to(dev))
+    n = X.shape[1]
+    Xd = X.to(dev)
+    Yd = Y0.clone().to(dev)
+    if ldx:
+        buf = torch.zeros(X.shape[0], ldx, dtype=X.dtype, device=dev)
+        buf[:, :n] = Xd
+        Xd = buf[:, :n]
+    if ldy:
+        buf2 = torch.full((Y0.shape[0], ldy), 3.0, dtype=Y0.dtype, device=dev)
+        buf2[:, :n] = Yd
+        Yd = buf2[:, :n]
+    handle.use_torch_stream()
+    B, C = api.DnMat(Xd), api.DnMat(Yd)
+    api.spmm_preprocess(handle, Am, B, C)
+    api.spmm(handle, Am, B, C, alpha, beta)
+    torch.cuda.synchronize()
+    stats, _, _ = Am.plan(handle)
+    assert stats["device_error"] == 0
+    if ldy:
+        assert bool((buf2[:, n:] == 3.0).all())
+    return Yd.cpu().numpy()
+
+
+@pytest.mark.parametrize("n", [64, 128, 256])
+@pytest.mark.parametrize("grid", [16, 10])
+def test_stencil_bf16(handle, n, grid):
+    A = G.stencil_3d_27pt(grid, seed=4)          # grid 10: 1000 rows, last row block partial
+    A.val = A.val.to(torch.bfloat16)
+    X = G.uniform((A.cols, n), -1, 1, dtype=torch.bfloat16, seed=70 + n)
+    Y0 = G.uniform((A.rows, n), -1, 1, seed=71 + n)
+    rp, ci = A.row_ptr.numpy(), A.col_idx.numpy()
+    for alpha, beta in ((1.0, 0.0), (0.5, -1.5)):
+        want = oracle.spmm(rp, ci, bits(A.val), bits(X), alpha, beta, Y0.numpy())
+        got = run_tc(handle, A, X, Y0, alpha, beta)
+        err = rel_l2(got, want)
+        assert err <= 1e-2 and err <= 1e-5, err
+
+
+def test_dense_blocks_and_empty_rows_bf16(handle):
+    """Block-dense matrix (every touched 64-column chunk well filled) with empty rows and an empty
+    row block in the middle."""
+    rng = np.random.default_rng(3)
+    rows, cols = 640, 512
+    dense = np.zeros((rows, cols), dtype=np.float32)
+    for rb in range(0, rows, 128):
+        if rb == 256:
+            continue                              # an entirely empty row block
+        for cb in rng.choice(cols // 64, size=3, replace=False):
+            blk = rng.standard_normal((128, 64)).astype(np.float32)
+            blk[rng.random((128, 64)) < 0.5] = 0
+            dense[rb:rb + 128, cb * 64:(cb + 1) * 64] = blk
+    dense[5] = 0
+    dense[130:140] = 0
+    rp = np.zeros(rows + 1, dtype=np.int32)
+    ci, v = [], []
+    for r in range(rows):
+        nz = np.nonzero(dense[r])[0]
+        ci.append(nz)
+        v.append(dense[r, nz])
+        rp[r + 1] = rp[r] + len(nz)
+    A = G.Csr(rows, cols, torch.from_numpy(rp), torch.from_numpy(np.concatenate(ci).astype(np.int32)),
+              torch.from_numpy(np.concatenate(v)).to(torch.bfloat16))
+    X = G.uniform((cols, 128), -1, 1, dtype=torch.bfloat16, seed=80)
+    Y0 = G.uniform((rows, 128), -1, 1, seed=81)
+    want = oracle.spmm(rp, A.col_idx.numpy(), bits(A.val), bits(X), 2.0, 1.0, Y0.numpy())
+    got = run_tc(handle, A, X, Y0, 2.0, 1.0, ldx=136, ldy=132)
+    assert rel_l2(got, want) <= 1e-5
+
+
+def test_sparse_random_matrix_is_refused(handle):
+    """Uniform random columns: almost every entry sits alone in its chunk, far from dense enough."""
+    A = G.poisson_random(1 << 16, 1 << 16, mean_len=16, seed=90).to("cuda")
+    A.val = A.val.to(torch.bfloat16)
+    Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr, A.col_idx, A.val)
+    B = api.DnMat(torch.zeros(A.cols, 128, dtype=torch.bfloat16, device="cuda"))
+    C = api.DnMat(torch.zeros(A.rows, 128, device="cuda"))
+    with pytest.raises(api.AlphaSparseError) as e:
+        api.spmm(handle, Am, B, C)
+    assert e.value.status == 6
