@@ -12,8 +12,8 @@
 //     TMA (cp.async.bulk.tensor, 128-byte swizzle, completion on an mbarrier) while the CTA's
 //     128 threads scatter their rows' entries of that chunk into a zeroed 128 x 64 bf16 tile in
 //     shared memory; one thread then issues four tcgen05.mma (M=128, N, K=16) that accumulate
-//     into tensor memory, and tcgen05.commit releases the stage.  Two stages overlap the next
-//     chunk's TMA and scatter with the current chunk's MMAs.  The epilogue reads the fp32
+//     into tensor memory, and tcgen05.commit releases the stage.  Three B stages keep the TMA a
+//     chunk ahead; two A tiles overlap the next chunk's scatter with the current chunk's MMAs.  The epilogue reads the fp32
 //     accumulators with tcgen05.ld and writes alpha*acc + beta*C.
 // Every mbarrier wait is bounded; on expiry the CTA raises *err, frees its tensor memory and
 // leaves.  No TMA load here uses cluster multicast.
@@ -35,6 +35,9 @@ constexpr int TC_THREADS = 128;
 constexpr int TC_SPAN_WORDS = 2048;  // bitmap words: a row block may span 65,536 chunks
 constexpr uint32_t TC_MAX_TRIES = 1u << 22;
 constexpr int TC_A_BYTES = TC_M * TC_KC * 2;  // 16 KB, K-major core matrices, no swizzle
+constexpr int TC_BSTAGES = 3;   // B slices in flight (two A tiles are enough: scatter is short)
+constexpr int TC_CAP = 4096;    // entries of a row block staged in shared memory
+constexpr int TC_MAXCH = 512;   // chunk ids of a row block staged in shared memory
 
 struct TcPlan {
   int64_t blocks = 0, total_chunks = 0;
@@ -147,6 +150,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
   return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
          ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
@@ -186,7 +196,7 @@ __device__ __forceinline__ int a_tile_off(int r, int k) {
 __global__ void __launch_bounds__(TC_THREADS)
 spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restrict__ rp,
                const int32_t* __restrict__ col, const __nv_bfloat16* __restrict__ val,
-               float* __restrict__ C, int64_t ldc, float alpha, float beta, int64_t rows, int n,
+               float* __restrict__ C, int64_t ldc, float alpha, float beta, int64_t rows, int64_t nnz, int n,
                const int32_t* __restrict__ chunk_off, const int32_t* __restrict__ chunk_list,
                int* __restrict__ err) {
   extern __shared__ unsigned char smem_raw[];
@@ -195,11 +205,15 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
   const int nblk = n / 64;                      // 64-column boxes of B per chunk
   const int b_stage_bytes = nblk * 8192;        // 64 rows x 128 B per box
   unsigned char* sA = smem;                     // 2 x 16 KB
-  unsigned char* sB = smem + 2 * TC_A_BYTES;    // 2 x b_stage_bytes, 1,024-byte aligned
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sB + 2 * b_stage_bytes);
-  uint64_t* full = bars;          // [2] B slice landed
-  uint64_t* done = bars + 2;      // [2] MMAs that read the stage retired
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 4);
+  unsigned char* sB = smem + 2 * TC_A_BYTES;    // TC_BSTAGES x b_stage_bytes, 1,024-byte aligned
+  int* s_col = reinterpret_cast<int*>(sB + TC_BSTAGES * b_stage_bytes);            // TC_CAP + 8
+  __nv_bfloat16* s_val = reinterpret_cast<__nv_bfloat16*>(s_col + TC_CAP + 8);      // TC_CAP + 8
+  int* s_chunks = reinterpret_cast<int*>(s_val + TC_CAP + 8);                       // TC_MAXCH
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_chunks + TC_MAXCH);
+  uint64_t* full = bars;               // [TC_BSTAGES] B slice landed
+  uint64_t* done = bars + TC_BSTAGES;  // [2] MMAs that read the A stage (and its B stage) retired
+  uint64_t* csr_full = bars + TC_BSTAGES + 2;  // the row block's entries landed
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + TC_BSTAGES + 3);
   int* s_fail = reinterpret_cast<int*>(s_tmem + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -212,10 +226,10 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
   // zero both A tiles, set up barriers and tensor memory
   for (int i = tid; i < 2 * TC_A_BYTES / 16; i += TC_THREADS) reinterpret_cast<uint4*>(sA)[i] = make_uint4(0, 0, 0, 0);
   if (tid == 0) {
-    mbar_init(&full[0], 1);
-    mbar_init(&full[1], 1);
+    for (int i = 0; i < TC_BSTAGES; ++i) mbar_init(&full[i], 1);
     mbar_init(&done[0], 1);
     mbar_init(&done[1], 1);
+    mbar_init(csr_full, 1);
     *s_fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -234,41 +248,82 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
   const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(n >> 3) << 17) |
                          ((uint32_t)(TC_M >> 4) << 24);
 
+  // The row block's entries go to shared memory with two bulk copies (slices widened to groups of
+  // eight entries, clipped to the arrays' last full group, the rest by plain loads); a block with
+  // more than TC_CAP entries is read from global memory instead.  Chunk ids likewise.
+  const int e0 = rp[r0], e1 = rp[r0 + nr];
+  const int a0 = e0 & ~7;
+  const bool staged = (e1 - a0) <= TC_CAP;
+  const bool chunks_staged = nchunks <= TC_MAXCH;
+  if (tid == 0 && staged) {
+    int a1 = (e1 + 7) & ~7;
+    const int nnz8 = (int)(nnz & ~(int64_t)7);
+    if (a1 > nnz8) a1 = nnz8;
+    if (a1 < a0) a1 = a0;
+    const uint32_t cnt = (uint32_t)(a1 - a0);
+    mbar_expect_tx(csr_full, cnt * 6u);
+    if (cnt) {
+      bulk_g2s(s_col, col + a0, cnt * 4u, csr_full);
+      bulk_g2s(s_val, val + a0, cnt * 2u, csr_full);
+    }
+    for (int e = a1 > e0 ? a1 : e0; e < e1; ++e) {
+      s_col[e - a0] = col[e];
+      s_val[e - a0] = val[e];
+    }
+  }
+  if (chunks_staged)
+    for (int i = tid; i < nchunks; i += TC_THREADS) s_chunks[i] = chunk_list[j0 + i];
+  const int* __restrict__ pc = staged ? s_col - a0 : col;               // indexed by the global entry number
+  const __nv_bfloat16* __restrict__ pv = staged ? s_val - a0 : val;
+  const int* __restrict__ pch = chunks_staged ? s_chunks : chunk_list + j0;
+
   // this thread's row of A: entries are consumed in column order as the chunks advance
   int k = 0, k_end = 0;
   if (tid < nr) {
     k = rp[r0 + tid];
     k_end = rp[r0 + tid + 1];
   }
-  int wb[2] = {0, 0}, we[2] = {0, 0}, wc[2] = {0, 0};  // what this thread wrote into each stage
   bool ok = true;
+  __syncthreads();  // s_chunks and the plain-load tail are visible
+  if (staged && !mbar_wait(csr_full, 0)) ok = false;
+
+  // B slices run one chunk ahead of the MMAs: chunks 0 and 1 are requested here, chunk j + 1 as
+  // soon as the MMAs of chunk j - 2 (which read the same B stage) have retired.
+  auto request_b = [&](int jj) {
+    const int bs = jj % TC_BSTAGES;
+    mbar_expect_tx(&full[bs], (uint32_t)b_stage_bytes);
+    for (int i = 0; i < nblk; ++i)
+      tma_load_2d(sB + bs * b_stage_bytes + i * 8192, &tmB, i * 64, pch[jj] * TC_KC, &full[bs]);
+  };
+  if (tid == 0) {
+    if (nchunks > 0) request_b(0);
+    if (nchunks > 1) request_b(1);
+  }
 
   for (int j = 0; j < nchunks; ++j) {
     const int s = j & 1;
-    const int chunk = chunk_list[j0 + j];
+    const int bs = j % TC_BSTAGES;
+    const int chunk = pch[j];
     if (j >= 2) {
-      // the MMAs of chunk j-2 must have finished reading this stage
+      // the MMAs of chunk j-2 must have finished reading this A stage and B stage (j-2) % 3
       if (ok && !mbar_wait(&done[s], (uint32_t)(((j >> 1) - 1) & 1))) ok = false;
     }
-    if (tid == 0 && ok) {
-      mbar_expect_tx(&full[s], (uint32_t)b_stage_bytes);
-      for (int i = 0; i < nblk; ++i)
-        tma_load_2d(sB + s * b_stage_bytes + i * 8192, &tmB, i * 64, chunk * TC_KC, &full[s]);
-    }
-    // clear what this thread put into the stage two chunks ago, then scatter the new entries
+    if (tid == 0 && ok && j >= 1 && j + 1 < nchunks) request_b(j + 1);
+    // re-zero this thread's row of the tile (eight 16-byte pieces, one per 8-column core matrix),
+    // then scatter the row's entries that fall into this chunk
     unsigned char* tile = sA + s * TC_A_BYTES;
-    for (int q = wb[s]; q < we[s]; ++q)
-      *reinterpret_cast<unsigned short*>(tile + a_tile_off(tid, col[q] - wc[s])) = 0;
+    if (j >= 2) {
+#pragma unroll
+      for (int q = 0; q < TC_KC / 8; ++q)
+        *reinterpret_cast<uint4*>(tile + q * 2048 + (tid >> 3) * 128 + (tid & 7) * 16) = make_uint4(0, 0, 0, 0);
+    }
     const int cbeg = chunk * TC_KC, cend = cbeg + TC_KC;
-    wb[s] = k;
-    wc[s] = cbeg;
     while (k < k_end) {
-      const int c = col[k];
+      const int c = pc[k];
       if (c >= cend) break;
-      *reinterpret_cast<__nv_bfloat16*>(tile + a_tile_off(tid, c - cbeg)) = val[k];
+      *reinterpret_cast<__nv_bfloat16*>(tile + a_tile_off(tid, c - cbeg)) = pv[k];
       ++k;
     }
-    we[s] = k;
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // tile writes -> visible to the MMA
     const int any_fail = __syncthreads_or(ok ? 0 : 1);
     if (any_fail) {
@@ -276,12 +331,12 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
       break;
     }
     if (tid == 0) {
-      if (!mbar_wait(&full[s], (uint32_t)((j >> 1) & 1))) {
+      if (!mbar_wait(&full[bs], (uint32_t)((j / TC_BSTAGES) & 1))) {
         *s_fail = 1;
       } else {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_base = smem_u32(tile);
-        const uint32_t b_base = smem_u32(sB + s * b_stage_bytes);
+        const uint32_t b_base = smem_u32(sB + bs * b_stage_bytes);
 #pragma unroll
         for (int kk = 0; kk < TC_KC / 16; ++kk) {
           const uint64_t ad = umma_desc(a_base + kk * 4096, 2048, 128, 0);   // no swizzle, K-major
@@ -421,7 +476,8 @@ bool spmm_tc_applicable(alphasparseSpMatDescr_t A, alphasparseDnMatDescr_t B, al
   const int64_t n = C->cols;
   return A->data_type == ALPHA_R_16BF && B->data_type == ALPHA_R_16BF && C->data_type == ALPHA_R_32F &&
          A->row_type == ALPHA_SPARSE_INDEXTYPE_I32 && n >= 64 && n <= 256 && n % 64 == 0 && B->ld % 8 == 0 &&
-         C->ld % 4 == 0 && aligned(B->values, 16) && aligned(C->values, 16) && A->cols < (int64_t(1) << 31);
+         C->ld % 4 == 0 && aligned(B->values, 16) && aligned(C->values, 16) && aligned(A->const_col_data, 16) &&
+         aligned(A->const_val_data, 16) && A->cols < (int64_t(1) << 31);
 }
 
 alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A, alphasparseDnMatDescr_t B,
@@ -459,7 +515,7 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return ALPHA_SPARSE_STATUS_INVALID_VALUE;
 
-  const size_t smem = 2 * TC_A_BYTES + 2 * (size_t)(n / 64) * 8192 + 64 + 1024;
+  const size_t smem = 2 * TC_A_BYTES + TC_BSTAGES * (size_t)(n / 64) * 8192 + (TC_CAP + 8) * 6 + TC_MAXCH * 4 + 128 + 1024;
   static size_t attr_bytes = 0;
   if (smem > attr_bytes) {
     ASP_CUDA(cudaFuncSetAttribute(spmm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -467,7 +523,7 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
   }
   spmm_tc_kernel<<<(unsigned)tp->blocks, TC_THREADS, smem, h->stream>>>(
       tm, A->const_row_data, A->const_col_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
-      reinterpret_cast<float*>(C->values), C->ld, alpha, beta, A->rows, n, tp->chunk_off, tp->chunk_list,
+      reinterpret_cast<float*>(C->values), C->ld, alpha, beta, A->rows, A->nnz, n, tp->chunk_off, tp->chunk_list,
       p->dev_err);
   impl(h)->launches++;
   return status_of(cudaGetLastError());
