@@ -142,8 +142,8 @@ spmm_rowblock_kernel(const OffT* __restrict__ rp, const int* __restrict__ col,
 //       entries past the arrays' last full group fetched with plain loads) while all threads
 //       stage the block's row offsets;
 //   (2) LN lanes share a row and keep VN adjacent columns of C each.  A group reads four
-//       (column, value) pairs with two 16-byte shared-memory loads, issues the four matching row
-//       segments of B as 16-byte global loads and then does the sixteen FMAs; the groups of a
+//       (column, value) pairs from shared memory, issues the four matching row segments of B
+//       as 16-byte global loads and then does the sixteen FMAs; the groups of a
 //       warp work on neighbouring rows at the same time, so for banded matrices a warp's B loads
 //       fall into a few cache lines.
 // Arithmetic and order are those of spmm_rowblock_kernel: C row := beta*C row, then
@@ -254,31 +254,17 @@ spmm_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
       for (int v = 0; v < VN; ++v) acc[v] = c[v] * beta;
     }
     const T* __restrict__ Bc = B + c0;
-    // entries up to the next group of four in shared memory
-    for (; (k & 3) && k < e; ++k) {
-      const T a = alpha * s_val[k];
-      T b[VN];
-      load_pack<T, VN>(Bc + (int64_t)s_col[k] * ldb, b);
-#pragma unroll
-      for (int v = 0; v < VN; ++v) acc[v] = fma(a, b[v], acc[v]);
-    }
+    // Four entries per step, counted from the row's first entry, so that the groups of a warp -
+    // which hold neighbouring rows - ask for neighbouring rows of B in the same instruction.
     for (; k + 4 <= e; k += 4) {
-      const int4 cc = *reinterpret_cast<const int4*>(s_col + k);
-      T a[4];
-      if constexpr (sizeof(T) == 4) {
-        const float4 vv = *reinterpret_cast<const float4*>(s_val + k);
-        a[0] = vv.x; a[1] = vv.y; a[2] = vv.z; a[3] = vv.w;
-      } else {
-        const double2 v0 = *reinterpret_cast<const double2*>(s_val + k);
-        const double2 v1 = *reinterpret_cast<const double2*>(s_val + k + 2);
-        a[0] = v0.x; a[1] = v0.y; a[2] = v1.x; a[3] = v1.y;
-      }
+      const int q0 = s_col[k], q1 = s_col[k + 1], q2 = s_col[k + 2], q3 = s_col[k + 3];
       T b0[VN], b1[VN], b2[VN], b3[VN];
-      load_pack<T, VN>(Bc + (int64_t)cc.x * ldb, b0);
-      load_pack<T, VN>(Bc + (int64_t)cc.y * ldb, b1);
-      load_pack<T, VN>(Bc + (int64_t)cc.z * ldb, b2);
-      load_pack<T, VN>(Bc + (int64_t)cc.w * ldb, b3);
-      const T a0s = alpha * a[0], a1s = alpha * a[1], a2s = alpha * a[2], a3s = alpha * a[3];
+      load_pack<T, VN>(Bc + (int64_t)q0 * ldb, b0);
+      load_pack<T, VN>(Bc + (int64_t)q1 * ldb, b1);
+      load_pack<T, VN>(Bc + (int64_t)q2 * ldb, b2);
+      load_pack<T, VN>(Bc + (int64_t)q3 * ldb, b3);
+      const T a0s = alpha * s_val[k], a1s = alpha * s_val[k + 1], a2s = alpha * s_val[k + 2],
+              a3s = alpha * s_val[k + 3];
 #pragma unroll
       for (int v = 0; v < VN; ++v) acc[v] = fma(a0s, b0[v], acc[v]);
 #pragma unroll
@@ -288,12 +274,27 @@ spmm_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
 #pragma unroll
       for (int v = 0; v < VN; ++v) acc[v] = fma(a3s, b3[v], acc[v]);
     }
-    for (; k < e; ++k) {
-      const T a = alpha * s_val[k];
-      T b[VN];
-      load_pack<T, VN>(Bc + (int64_t)s_col[k] * ldb, b);
+    if (k < e) {  // up to three entries left
+      const int q0 = s_col[k];
+      const int q1 = k + 1 < e ? s_col[k + 1] : q0;
+      const int q2 = k + 2 < e ? s_col[k + 2] : q0;
+      T b0[VN], b1[VN], b2[VN];
+      load_pack<T, VN>(Bc + (int64_t)q0 * ldb, b0);
+      load_pack<T, VN>(Bc + (int64_t)q1 * ldb, b1);
+      load_pack<T, VN>(Bc + (int64_t)q2 * ldb, b2);
+      const T a0s = alpha * s_val[k];
 #pragma unroll
-      for (int v = 0; v < VN; ++v) acc[v] = fma(a, b[v], acc[v]);
+      for (int v = 0; v < VN; ++v) acc[v] = fma(a0s, b0[v], acc[v]);
+      if (k + 1 < e) {
+        const T a1s = alpha * s_val[k + 1];
+#pragma unroll
+        for (int v = 0; v < VN; ++v) acc[v] = fma(a1s, b1[v], acc[v]);
+      }
+      if (k + 2 < e) {
+        const T a2s = alpha * s_val[k + 2];
+#pragma unroll
+        for (int v = 0; v < VN; ++v) acc[v] = fma(a2s, b2[v], acc[v]);
+      }
     }
     store_pack<T, VN>(C + r * ldc + c0, acc);
   }
