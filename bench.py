@@ -39,6 +39,20 @@ WORKLOADS = {
     "spmm_s27_128_f32_n32": "CSR SpMM fp32, 27-point stencil 128^3, N=32",
     "spmm_s27_128_f32_n128": "CSR SpMM fp32, 27-point stencil 128^3, N=128",
     "spmm_s27_128_bf16_n128": "CSR SpMM bf16 operands / fp32 accumulate (tcgen05), 27-point stencil 128^3, N=128",
+    "spmv_rmat26_f32_i64": "CSR SpMV fp32, R-MAT scale 26 edge factor 32, int64 offsets, alpha=1 beta=0",
+}
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel from the
+# ncu captures summarised under profiles/, as a ratio to the algorithmic bytes of the captured case.
+# The Laplacian was captured on a 256^3 grid (1/8 of the rows); its traffic grows with the rows, so the
+# ratio is applied to the full launch.
+TRAFFIC_RATIO = {
+    "spmv_poisson16_f32": 605.7e6 / 603.9e6,
+    "spmv_lap3d_f64_i64": 1804.2e6 / 1807.2e6,
+    "spmv_rmat22_f32": 584.1e6 / 572.0e6,
+    "spmm_s27_128_f32_n8": 580.7e6 / 588.5e6,
+    "spmm_s27_128_f32_n32": 969.5e6 / 991.2e6,
+    "spmm_s27_128_f32_n128": 2647.0e6 / 2601.8e6,
+    "spmm_s27_128_bf16_n128": 1903.6e6 / 1946.0e6,
 }
 DEFAULT_WORKLOAD = "spmv_poisson16_f32"
 
@@ -53,6 +67,9 @@ def parse_args():
     ap.add_argument("--variant", default="auto", choices=["auto", "binned", "merge"])
     ap.add_argument("--scale", type=float, default=1.0,
                     help="shrink the workload's row count by this factor (for profiler captures)")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every rank owns a workload-sized row shard; strong: one matrix is "
+                         "row-partitioned by balanced nnz across the ranks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -70,6 +87,10 @@ def make_workload(name, device, rank, scale):
     if name == "spmv_rmat22_f32":
         sc = 22 + int(round(__import__("math").log2(scale))) if scale != 1.0 else 22
         A = G.rmat(sc, 16, dtype=torch.float32, device=device, seed=3 + seed)
+        return dict(A=A, kind="spmv", n=1, alpha=1.0, beta=0.0, lo=0.0, dtype=torch.float32)
+    if name == "spmv_rmat26_f32_i64":
+        sc = 26 + int(round(__import__("math").log2(scale))) if scale != 1.0 else 26
+        A = G.rmat(sc, 32, dtype=torch.float32, device=device, seed=5 + seed, index64=True)
         return dict(A=A, kind="spmv", n=1, alpha=1.0, beta=0.0, lo=0.0, dtype=torch.float32)
     if name == "spmv_lap2d256_f64":
         A = G.laplacian_2d_5pt(256, dtype=torch.float64, device=device)
@@ -268,12 +289,26 @@ def run_ours(args):
     if args.variant != "auto":
         os.environ["ASP_SPMV_VARIANT"] = args.variant
 
-    w = make_workload(args.workload, dev, rank, args.scale)
-    A = w["A"]
-    nbytes = algorithmic_bytes(w)
+    strong = args.scaling == "strong" and world > 1
     h = api.Handle()
     stream = torch.cuda.Stream()
     h.set_stream(stream.cuda_stream)
+    if strong:
+        # every rank builds the same matrix (same seed), takes its nnz-balanced row range and drops the rest
+        from library_b200.generators import Csr
+        from library_b200.sharding import shard_csr
+        w = make_workload(args.workload, dev, 0, args.scale)
+        full = w["A"]
+        with torch.cuda.stream(stream):
+            Aloc, (r0, r1) = shard_csr(h, full.rows, full.cols, full.row_ptr, full.col_idx, full.val, rank, world)
+            w["A"] = Csr(r1 - r0, full.cols, Aloc.row_ptr, Aloc.col_idx.clone(), Aloc.val.clone())
+        torch.cuda.synchronize()
+        del Aloc, full
+        torch.cuda.empty_cache()
+    else:
+        w = make_workload(args.workload, dev, rank, args.scale)
+    A = w["A"]
+    nbytes = algorithmic_bytes(w)
     Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr, A.col_idx, A.val)
     ydt = torch.float32 if w["dtype"] == torch.bfloat16 else w["dtype"]
 
@@ -398,7 +433,8 @@ def run_ours(args):
         line = {
             "metric": "effective HBM GB/s on algorithmic bytes (CSR SpMV/SpMM)",
             "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak",
+            "vs_baseline": None,
             "dtype": {torch.float32: "f32", torch.float64: "f64", torch.bfloat16: "bf16"}[w["dtype"]],
             "data": "synthetic", "gflops": total_flops / (ms_step * 1e-3) / 1e9,
             "frac_of_nominal_8TBs": value / world / 8000.0,
@@ -407,9 +443,13 @@ def run_ours(args):
                        "alpha": w["alpha"], "beta": w["beta"], "variant": variant,
                        "algorithmic_bytes_per_gpu": nbytes, "l2": "inputs larger than L2 (126 MB), no flush"
                        if nbytes > 126e6 else "L2-resident workload, no flush (the configuration is smaller than L2)",
-                       "sharding": "rows, nnz-balanced shards, x replicated by NCCL broadcast, y sharded"},
+                       "sharding": ("one matrix row-partitioned by balanced nnz" if strong else
+                                    "every rank owns a workload-sized row shard")
+                       + ", x replicated by NCCL broadcast, y sharded"},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                         "peak_source": peak_src, "traffic": None},
+                         "peak_source": peak_src,
+                         "traffic": (TRAFFIC_RATIO[args.workload] * nbytes) if args.workload in TRAFFIC_RATIO else None,
+                         "traffic_source": "ncu dram__bytes_read+write of the dominant kernel, see profiles/"},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk.summary(),
         }
         print(json.dumps(line), flush=True)

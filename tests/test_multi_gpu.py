@@ -3,8 +3,8 @@
 CPU part (gloo, world_size 2, runs anywhere): the host-side planning - bounds, rebased offsets,
 replication of x with a broadcast, sharded y - assembled from per-rank oracle results equals the
 single-process oracle bit for bit.  GPU part (needs two CUDA devices; skipped otherwise): the
-same through the C ABI with NCCL, every rank's y shard bit-equal to the one-GPU result of the
-same kernel on the same rows.
+same through the C ABI with NCCL, the concatenated y shards equal to the one-GPU result within
+fp32 rounding.
 """
 import os
 import socket
@@ -94,7 +94,7 @@ def _gpu_worker(rank, world, port, out_dir):
     h = api.Handle()
     Aloc, (r0, r1) = shard_csr(h, A.rows, A.cols, A.row_ptr, A.col_idx, A.val, rank, world)
     y = torch.zeros(r1 - r0, device="cuda")
-    os.environ["ASP_SPMV_VARIANT"] = "binned"   # per-row sums do not depend on the shard's tiling
+    os.environ["ASP_SPMV_VARIANT"] = "binned"
     api.spmv(h, Aloc, api.DnVec(x), api.DnVec(y), 1.0, 0.0)
     torch.cuda.synchronize()
     np.save(os.path.join(out_dir, f"y{rank}.npy"), y.cpu().numpy())
@@ -117,4 +117,7 @@ def test_row_sharding_on_two_gpus(tmp_path):
     mp.spawn(_gpu_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     full = np.load(tmp_path / "full.npy")
     got = np.concatenate([np.load(tmp_path / f"y{r}.npy") for r in range(world)])
-    assert np.array_equal(got, full)
+    # A shard's entry arrays start at another offset than the full matrix's, so 16-byte chunks fall
+    # differently onto a row and lanes add in another order: equal within fp32 rounding, not bit-equal.
+    from conftest import rel_l2
+    assert got.shape == full.shape and rel_l2(got, full) <= 1e-6
