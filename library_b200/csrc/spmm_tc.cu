@@ -19,6 +19,7 @@
 // leaves.  No TMA load here uses cluster multicast.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cub/device/device_reduce.cuh>
 #include <cub/device/device_scan.cuh>
 
 #include <new>
@@ -43,8 +44,9 @@ struct TcPlan {
   int64_t blocks = 0, total_chunks = 0;
   int max_chunks = 0;
   bool usable = false;  // sorted columns, chunk span within the bitmap
-  int32_t* chunk_off = nullptr;   // device, blocks + 1
-  int32_t* chunk_list = nullptr;  // device, total_chunks
+  int32_t* chunk_off = nullptr;   // device, blocks + 1; every block's list starts on a multiple of four
+  int32_t* chunk_cnt = nullptr;   // device, blocks: number of chunks of the block
+  int32_t* chunk_list = nullptr;  // device, chunk_off[blocks] entries
 };
 
 // ---- preprocessing -------------------------------------------------------------------------
@@ -55,6 +57,7 @@ template <bool FILL>
 __global__ void __launch_bounds__(256) tc_chunks_kernel(const int32_t* __restrict__ rp,
                                                         const int32_t* __restrict__ col, int64_t rows,
                                                         int32_t* __restrict__ counts,
+                                                        int32_t* __restrict__ padded,
                                                         const int32_t* __restrict__ chunk_off,
                                                         int32_t* __restrict__ chunk_list,
                                                         int* __restrict__ flags) {
@@ -103,7 +106,10 @@ __global__ void __launch_bounds__(256) tc_chunks_kernel(const int32_t* __restric
     __syncthreads();
   }
   if (!FILL) {
-    if (tid == 255) counts[blockIdx.x] = s_scan[255];
+    if (tid == 255) {
+      counts[blockIdx.x] = s_scan[255];
+      padded[blockIdx.x] = (s_scan[255] + 3) & ~3;
+    }
   } else {
     int pos = chunk_off[blockIdx.x] + s_scan[tid] - cnt;
     for (int w = 0; w < TC_SPAN_WORDS / 256; ++w) {
@@ -197,8 +203,8 @@ __global__ void __launch_bounds__(TC_THREADS)
 spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restrict__ rp,
                const int32_t* __restrict__ col, const __nv_bfloat16* __restrict__ val,
                float* __restrict__ C, int64_t ldc, float alpha, float beta, int64_t rows, int64_t nnz, int n,
-               const int32_t* __restrict__ chunk_off, const int32_t* __restrict__ chunk_list,
-               int* __restrict__ err) {
+               const int32_t* __restrict__ chunk_off, const int32_t* __restrict__ chunk_cnt,
+               const int32_t* __restrict__ chunk_list, int* __restrict__ err) {
   extern __shared__ unsigned char smem_raw[];
   // the swizzled B boxes (and the descriptors' address arithmetic) need a 1,024-byte aligned base
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -219,8 +225,8 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
   const int tid = threadIdx.x, warp = tid >> 5;
   const int64_t r0 = (int64_t)blockIdx.x * TC_M;
   const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
-  const int j0 = chunk_off[blockIdx.x], j1 = chunk_off[blockIdx.x + 1];
-  const int nchunks = j1 - j0;
+  const int j0 = chunk_off[blockIdx.x];
+  const int nchunks = chunk_cnt[blockIdx.x];
   const uint32_t tmem_cols = n <= 64 ? 64u : (n <= 128 ? 128u : 256u);
 
   // zero both A tiles, set up barriers and tensor memory
@@ -396,6 +402,351 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
 }
 
+// ------------------------------------------------------------------------------------------
+// Persistent, warp-specialised form: one CTA per SM walks row blocks blockIdx.x, +gridDim.x, ...
+// and splits the work of spmm_tc_kernel over four roles that only meet through mbarriers, so the
+// copy engine runs many chunks (and one row block) ahead of the tensor core and the epilogue of a
+// row block overlaps the MMAs of the next one:
+//   warps 0-3  builders : thread = row of the block; zero + scatter the row's entries of a chunk
+//                         into the A tile of the chunk's ring stage      (st_empty -> a_full)
+//   warps 4-7  epilogue : tcgen05.ld of one of two accumulators, alpha/beta, store C
+//                                                                       (acc_full -> acc_empty)
+//   warp 8     producer : bulk copies of the next block's CSR slice and chunk ids (csr_empty ->
+//                         csr_full), TMA of every chunk's B slice into the same ring of `sb`
+//                         stages                                        (st_empty -> b_full)
+//   warp 9     MMA      : waits a_full + b_full, issues the four tcgen05.mma of the chunk, commits
+//                         once to st_empty, and to acc_full after the block's last chunk;
+//                         owns the tensor-memory allocation (two accumulators)
+// A barrier of the "empty" kind is waited on with the inverted parity, so its first use passes.
+// Every wait is bounded; a role whose wait expires raises the CTA's fail flag and leaves its loop,
+// the other roles then run into their own limits, and all meet at the final __syncthreads.
+// ------------------------------------------------------------------------------------------
+constexpr int TCP_THREADS = 320;
+
+// Bounded spin on the non-blocking test: lowest wake-up latency, for the waits that sit on the
+// per-chunk critical path (try_wait may park the thread for a scheduler time slice).
+__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (TC_MAX_TRIES << 4); ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(TCP_THREADS, 1)
+spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restrict__ rp,
+                          const int32_t* __restrict__ col, const __nv_bfloat16* __restrict__ val,
+                          float* __restrict__ C, int64_t ldc, float alpha, float beta, int64_t rows,
+                          int64_t nnz, int n, int nblocks, int sb,
+                          const int32_t* __restrict__ chunk_off, const int32_t* __restrict__ chunk_cnt,
+                          const int32_t* __restrict__ chunk_list, int* __restrict__ err) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const int nblk = n / 64;
+  const int b_stage_bytes = nblk * 8192;
+  unsigned char* sA = smem;                               // sb x 16 KB (A tiles and B slices share one ring)
+  unsigned char* sB = sA + (size_t)sb * TC_A_BYTES;       // sb x b_stage_bytes
+  unsigned char* p = sB + (size_t)sb * b_stage_bytes;
+  int* s_col = reinterpret_cast<int*>(p);                 // 2 x (TC_CAP + 8)
+  __nv_bfloat16* s_val = reinterpret_cast<__nv_bfloat16*>(s_col + 2 * (TC_CAP + 8));  // 2 x (TC_CAP + 8)
+  int* s_chunks = reinterpret_cast<int*>(s_val + 2 * (TC_CAP + 8));                   // 2 x TC_MAXCH
+  float* s_tr = reinterpret_cast<float*>(s_chunks + 2 * TC_MAXCH);  // 4 epilogue warps x 32 x 33
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_tr + 4 * 32 * 33 + 2);
+  uint64_t* csr_full = bars;            // [2]
+  uint64_t* csr_empty = bars + 2;       // [2]
+  uint64_t* acc_full = bars + 4;        // [2]
+  uint64_t* acc_empty = bars + 6;       // [2]
+  uint64_t* a_full = bars + 8;          // [sb] the chunk's A tile is built
+  uint64_t* b_full = a_full + sb;       // [sb] the chunk's B slice landed
+  uint64_t* st_empty = b_full + sb;     // [sb] the chunk's MMAs retired: tile and slice are free
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(st_empty + sb);
+  volatile int* s_fail = reinterpret_cast<volatile int*>(s_tmem + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t acc_cols = n <= 64 ? 64u : (n <= 128 ? 128u : 256u);
+
+  for (int i = tid; i < sb * TC_A_BYTES / 16; i += TCP_THREADS)
+    reinterpret_cast<uint4*>(sA)[i] = make_uint4(0, 0, 0, 0);
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&csr_full[i], 1);
+      mbar_init(&csr_empty[i], 4);   // one arrival per builder warp: 128 arrivals on one barrier
+      mbar_init(&acc_full[i], 1);    // serialise in the barrier unit and cost ~500 cycles per use
+      mbar_init(&acc_empty[i], 4);
+    }
+    for (int i = 0; i < sb; ++i) {
+      mbar_init(&a_full[i], 4);
+      mbar_init(&b_full[i], 1);
+      mbar_init(&st_empty[i], 1);
+    }
+    *s_fail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 9) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
+                 "r"(2u * acc_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *s_tmem;
+
+  const int first = blockIdx.x, stride = gridDim.x;
+  const int n_my = first < nblocks ? (nblocks - first + stride - 1) / stride : 0;
+
+  if (warp == 8) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      int nch_of[2] = {0, 0};
+      auto stage_csr = [&](int i) -> bool {
+        const int cs = i & 1;
+        if (!mbar_wait(&csr_empty[cs], (uint32_t)(((i >> 1) & 1) ^ 1))) return false;
+        const int b = first + i * stride;
+        const int64_t r0 = (int64_t)b * TC_M;
+        const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
+        const int e0 = rp[r0], e1 = rp[r0 + nr];
+        const int a0 = e0 & ~7;
+        const bool staged = (e1 - a0) <= TC_CAP;
+        const int j0 = chunk_off[b], nch = chunk_cnt[b];
+        nch_of[cs] = nch;
+        int* dc = s_col + cs * (TC_CAP + 8);
+        __nv_bfloat16* dv = s_val + cs * (TC_CAP + 8);
+        uint32_t cnt = 0;
+        if (staged) {
+          int a1 = (e1 + 7) & ~7;
+          const int nnz8 = (int)(nnz & ~(int64_t)7);
+          if (a1 > nnz8) a1 = nnz8;
+          if (a1 < a0) a1 = a0;
+          cnt = (uint32_t)(a1 - a0);
+          for (int e = a1 > e0 ? a1 : e0; e < e1; ++e) {  // past the arrays' last full group of eight
+            dc[e - a0] = col[e];
+            dv[e - a0] = val[e];
+          }
+        }
+        const uint32_t nch4 = (uint32_t)((nch + 3) & ~3);
+        mbar_expect_tx(&csr_full[cs], cnt * 6u + nch4 * 4u);
+        if (cnt) {
+          bulk_g2s(dc, col + a0, cnt * 4u, &csr_full[cs]);
+          bulk_g2s(dv, val + a0, cnt * 2u, &csr_full[cs]);
+        }
+        if (nch4) bulk_g2s(s_chunks + cs * TC_MAXCH, chunk_list + j0, nch4 * 4u, &csr_full[cs]);
+        return true;
+      };
+      bool ok = n_my > 0 ? stage_csr(0) : true;
+      int st = 0;           // ring stage and its use parity, advanced without divisions
+      uint32_t ph = 0;
+      for (int i = 0; i < n_my && ok; ++i) {
+        const int cs = i & 1;
+        const int nch = nch_of[cs];
+        if (i + 1 < n_my) ok = stage_csr(i + 1);
+        if (ok && !mbar_wait(&csr_full[cs], (uint32_t)((i >> 1) & 1))) ok = false;
+        const int* pch = s_chunks + cs * TC_MAXCH;
+        for (int j = 0; j < nch && ok; ++j) {
+          if (!mbar_spin(&st_empty[st], ph ^ 1u)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&b_full[st], (uint32_t)b_stage_bytes);
+          for (int q = 0; q < nblk; ++q)
+            tma_load_2d(sB + (size_t)st * b_stage_bytes + q * 8192, &tmB, q * 64, pch[j] * TC_KC, &b_full[st]);
+          if (++st == sb) {
+            st = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+      if (!ok) *s_fail = 1;
+    }
+  } else if (warp == 9) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(n >> 3) << 17) |
+                             ((uint32_t)(TC_M >> 4) << 24);
+      bool ok = true;
+      int st = 0;
+      uint32_t ph = 0;
+      const uint32_t a_base0 = smem_u32(sA), b_base0 = smem_u32(sB);
+      int nch_next = n_my > 0 ? chunk_cnt[first] : 0;
+      for (int i = 0; i < n_my && ok; ++i) {
+        const int acc = i & 1;
+        const int nch = nch_next;  // fetched one block ahead: no global latency between blocks
+        if (i + 1 < n_my) nch_next = chunk_cnt[first + (i + 1) * stride];
+        if (!mbar_wait(&acc_empty[acc], (uint32_t)(((i >> 1) & 1) ^ 1))) {
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t d = tmem + (uint32_t)acc * acc_cols;
+        for (int j = 0; j < nch; ++j) {
+          if (!mbar_spin(&a_full[st], ph) || !mbar_spin(&b_full[st], ph)) {
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          // descriptors differ from the stage's first one only in the 14-bit address field
+          const uint64_t ad0 = umma_desc(a_base0 + (uint32_t)st * TC_A_BYTES, 2048, 128, 0);
+          const uint64_t bd0 = umma_desc(b_base0 + (uint32_t)st * (uint32_t)b_stage_bytes, 8192, 1024, 2);
+#pragma unroll
+          for (int kk = 0; kk < TC_KC / 16; ++kk)
+            umma_bf16(d, ad0 + (uint64_t)(kk * (4096 >> 4)), bd0 + (uint64_t)(kk * (2048 >> 4)), idesc,
+                      (j > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(&st_empty[st]);
+          if (++st == sb) {
+            st = 0;
+            ph ^= 1u;
+          }
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+      }
+      if (!ok) *s_fail = 1;
+    }
+  } else if (warp < 4) {
+    // ---------------- builders: thread = row ----------------
+    bool ok = true;
+    int sa = 0;
+    uint32_t ph = 0;
+    unsigned long long wrote[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // per ring stage (sb <= 8)
+    // per-block scalars are fetched one block ahead
+    int n_e0 = 0, n_e1 = 0, n_nch = 0, n_k = 0, n_kend = 0;
+    auto fetch = [&](int i) {
+      const int b = first + i * stride;
+      const int64_t r0 = (int64_t)b * TC_M;
+      const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
+      n_e0 = rp[r0];
+      n_e1 = rp[r0 + nr];
+      n_nch = chunk_cnt[b];
+      n_k = n_kend = 0;
+      if (tid < nr) {
+        n_k = rp[r0 + tid];
+        n_kend = rp[r0 + tid + 1];
+      }
+    };
+    if (n_my > 0) fetch(0);
+    for (int i = 0; i < n_my && ok; ++i) {
+      const int cs = i & 1;
+      const int e0 = n_e0, e1 = n_e1, nch = n_nch;
+      int k = n_k;
+      const int k_end = n_kend;
+      const int a0 = e0 & ~7;
+      const bool staged = (e1 - a0) <= TC_CAP;
+      if (i + 1 < n_my) fetch(i + 1);
+      if (!mbar_wait(&csr_full[cs], (uint32_t)((i >> 1) & 1))) {
+        ok = false;
+        break;
+      }
+      const int* __restrict__ pc = staged ? s_col + cs * (TC_CAP + 8) - a0 : col;
+      const __nv_bfloat16* __restrict__ pv = staged ? s_val + cs * (TC_CAP + 8) - a0 : val;
+      const int* pch = s_chunks + cs * TC_MAXCH;
+      for (int j = 0; j < nch; ++j) {
+        if (!mbar_spin(&st_empty[sa], ph ^ 1u)) {
+          ok = false;
+          break;
+        }
+        unsigned char* tile = sA + sa * TC_A_BYTES;
+        // clear the (few) positions this thread wrote when the stage was last used: their 6-bit
+        // in-chunk columns are remembered in a 64-bit mask per ring stage
+        unsigned long long m = wrote[sa];
+        while (m) {
+          const int c = __ffsll((long long)m) - 1;
+          m &= m - 1;
+          *reinterpret_cast<unsigned short*>(tile + a_tile_off(tid, c)) = 0;
+        }
+        const int cbeg = pch[j] * TC_KC, cend = cbeg + TC_KC;
+        unsigned long long w = 0;
+        while (k < k_end) {
+          const int c = pc[k];
+          if (c >= cend) break;
+          *reinterpret_cast<__nv_bfloat16*>(tile + a_tile_off(tid, c - cbeg)) = pv[k];
+          w |= 1ull << (c - cbeg);
+          ++k;
+        }
+        wrote[sa] = w;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&a_full[sa]);
+        if (++sa == sb) {
+          sa = 0;
+          ph ^= 1u;
+        }
+      }
+      __syncwarp();
+      if (ok && lane == 0) mbar_arrive(&csr_empty[cs]);
+    }
+    if (!ok) *s_fail = 1;
+  } else {
+    // ---------------- epilogue: warps 4-7 read tensor-memory lanes 32*(warp-4) .. ----------------
+    bool ok = true;
+    const int row = tid - 128;
+    int nch_next = n_my > 0 ? chunk_cnt[first] : 0;
+    for (int i = 0; i < n_my && ok; ++i) {
+      const int acc = i & 1;
+      const int b = first + i * stride;
+      const int64_t r0 = (int64_t)b * TC_M;
+      const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
+      const int nch = nch_next;
+      if (i + 1 < n_my) nch_next = chunk_cnt[first + (i + 1) * stride];
+      if (!mbar_wait(&acc_full[acc], (uint32_t)((i >> 1) & 1))) {
+        ok = false;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // tcgen05.ld hands lane l the 32 columns of row l; a per-warp 32 x 33 shared-memory tile turns
+      // that around so that a store instruction writes 32 consecutive floats of one row (one line)
+      // instead of 16 bytes of 32 different rows.
+      float* tr = s_tr + (warp - 4) * (32 * 33);
+      const int wrow0 = (warp - 4) * 32;
+      (void)row;
+      for (int cb = 0; cb < n; cb += 32) {
+        uint32_t a[32];
+        if (nch > 0) {
+          tmem_ld32(tmem + ((uint32_t)wrow0 << 16) + (uint32_t)acc * acc_cols + (uint32_t)cb, a);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
+#pragma unroll
+          for (int q = 0; q < 32; ++q) a[q] = 0u;
+        }
+#pragma unroll
+        for (int q = 0; q < 32; ++q) tr[lane * 33 + q] = alpha * __uint_as_float(a[q]);
+        __syncwarp();
+        const int rmax = nr - wrow0 < 32 ? nr - wrow0 : 32;
+        for (int rr = 0; rr < rmax; ++rr) {
+          float* cp = C + (r0 + wrow0 + rr) * ldc + cb + lane;
+          float o = tr[rr * 33 + lane];
+          if (beta != 0.f) o = fmaf(beta, *cp, o);
+          *cp = o;
+        }
+        __syncwarp();
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+    if (!ok) *s_fail = 1;
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*s_fail) {
+    if (tid == 0) atomicExch(err, 1);
+    __nanosleep(1000000);  // let copies and MMAs still in flight retire before the memory goes away
+  }
+  if (warp == 9)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2u * acc_cols) : "memory");
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -418,46 +769,74 @@ alphasparseStatus_t build_plan(alphasparseHandle_t h, alphasparseSpMatDescr_t A,
   cudaStream_t st = h->stream;
   tp->blocks = (A->rows + TC_M - 1) / TC_M;
   if (tp->blocks == 0 || tp->blocks > INT_MAX) return ALPHA_SPARSE_STATUS_SUCCESS;
-  int32_t* counts = nullptr;
+  const int nb = (int)tp->blocks;
+  int32_t *padded = nullptr, *cnt_scan = nullptr;
   int* flags = nullptr;
-  ASP_CUDA(cudaMalloc(&counts, sizeof(int32_t) * (tp->blocks + 1)));
-  ASP_CUDA(cudaMalloc(&flags, 2 * sizeof(int)));
-  ASP_CUDA(cudaMalloc(&tp->chunk_off, sizeof(int32_t) * (tp->blocks + 1)));
-  ASP_CUDA(cudaMemsetAsync(flags, 0, 2 * sizeof(int), st));
-  ASP_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t) * (tp->blocks + 1), st));
-  tc_chunks_kernel<false><<<(unsigned)tp->blocks, 256, 0, st>>>(A->const_row_data, A->const_col_data, A->rows,
-                                                               counts, nullptr, nullptr, flags);
-  size_t tmp_bytes = 0;
-  cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, counts, tp->chunk_off, (int)(tp->blocks + 1), st);
   void* tmp = nullptr;
-  ASP_CUDA(cudaMalloc(&tmp, tmp_bytes ? tmp_bytes : 16));
-  cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, counts, tp->chunk_off, (int)(tp->blocks + 1), st);
+  auto cleanup = [&]() {
+    cudaFree(padded);
+    cudaFree(cnt_scan);
+    cudaFree(flags);
+    cudaFree(tmp);
+  };
+  ASP_CUDA(cudaMalloc(&tp->chunk_cnt, sizeof(int32_t) * (nb + 1)));
+  ASP_CUDA(cudaMalloc(&tp->chunk_off, sizeof(int32_t) * (nb + 1)));
+  if (cudaMalloc(&padded, sizeof(int32_t) * (nb + 1)) != cudaSuccess ||
+      cudaMalloc(&cnt_scan, sizeof(int32_t) * (nb + 1)) != cudaSuccess ||
+      cudaMalloc(&flags, 2 * sizeof(int)) != cudaSuccess) {
+    cleanup();
+    return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+  }
+  cudaMemsetAsync(flags, 0, 2 * sizeof(int), st);
+  cudaMemsetAsync(tp->chunk_cnt, 0, sizeof(int32_t) * (nb + 1), st);
+  cudaMemsetAsync(padded, 0, sizeof(int32_t) * (nb + 1), st);
+  tc_chunks_kernel<false><<<(unsigned)nb, 256, 0, st>>>(A->const_row_data, A->const_col_data, A->rows,
+                                                       tp->chunk_cnt, padded, nullptr, nullptr, flags);
+  size_t tmp_bytes = 0;
+  cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, padded, tp->chunk_off, nb + 1, st);
+  if (cudaMalloc(&tmp, tmp_bytes ? tmp_bytes : 16) != cudaSuccess) {
+    cleanup();
+    return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+  }
+  cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, padded, tp->chunk_off, nb + 1, st);
+  cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, tp->chunk_cnt, cnt_scan, nb + 1, st);
   int hflags[2] = {0, 0};
-  int32_t total = 0;
+  int32_t total_padded = 0, total = 0;
   cudaError_t e = cudaMemcpyAsync(hflags, flags, sizeof hflags, cudaMemcpyDeviceToHost, st);
-  if (e == cudaSuccess)
-    e = cudaMemcpyAsync(&total, tp->chunk_off + tp->blocks, sizeof total, cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(&total_padded, tp->chunk_off + nb, sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(&total, cnt_scan + nb, sizeof(int32_t), cudaMemcpyDeviceToHost, st);
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   impl(h)->launches += 3;
-  cudaFree(tmp);
-  cudaFree(flags);
   if (e != cudaSuccess) {
-    cudaFree(counts);
+    cleanup();
     return status_of(e);
   }
   tp->total_chunks = total;
   tp->usable = hflags[0] == 0 && hflags[1] == 0;
-  if (tp->usable && total > 0) {
-    if (cudaMalloc(&tp->chunk_list, sizeof(int32_t) * (size_t)total) != cudaSuccess) {
-      cudaFree(counts);
+  if (tp->usable && total_padded > 0) {
+    if (cudaMalloc(&tp->chunk_list, sizeof(int32_t) * (size_t)total_padded) != cudaSuccess) {
+      cleanup();
       return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
     }
-    tc_chunks_kernel<true><<<(unsigned)tp->blocks, 256, 0, st>>>(A->const_row_data, A->const_col_data, A->rows,
-                                                                nullptr, tp->chunk_off, tp->chunk_list, nullptr);
+    cudaMemsetAsync(tp->chunk_list, 0, sizeof(int32_t) * (size_t)total_padded, st);
+    tc_chunks_kernel<true><<<(unsigned)nb, 256, 0, st>>>(A->const_row_data, A->const_col_data, A->rows, nullptr,
+                                                        nullptr, tp->chunk_off, tp->chunk_list, nullptr);
     impl(h)->launches++;
     e = cudaStreamSynchronize(st);
   }
-  cudaFree(counts);
+  // the largest chunk count of a block decides whether chunk ids fit the persistent kernel's staging
+  if (e == cudaSuccess && tp->usable) {
+    size_t rb = 0;
+    cub::DeviceReduce::Max(nullptr, rb, tp->chunk_cnt, cnt_scan, nb, st);
+    if (rb <= tmp_bytes || (cudaFree(tmp), tmp = nullptr, cudaMalloc(&tmp, rb) == cudaSuccess)) {
+      cub::DeviceReduce::Max(tmp, rb, tp->chunk_cnt, cnt_scan, nb, st);
+      int32_t m = 0;
+      e = cudaMemcpyAsync(&m, cnt_scan, sizeof m, cudaMemcpyDeviceToHost, st);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+      tp->max_chunks = m;
+    }
+  }
+  cleanup();
   return status_of(e);
 }
 
@@ -467,6 +846,7 @@ void free_spmm_tc_plan(void* p) {
   TcPlan* tp = reinterpret_cast<TcPlan*>(p);
   if (!tp) return;
   cudaFree(tp->chunk_off);
+  cudaFree(tp->chunk_cnt);
   cudaFree(tp->chunk_list);
   delete tp;
 }
@@ -515,7 +895,32 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return ALPHA_SPARSE_STATUS_INVALID_VALUE;
 
-  const size_t smem = 2 * TC_A_BYTES + TC_BSTAGES * (size_t)(n / 64) * 8192 + (TC_CAP + 8) * 6 + TC_MAXCH * 4 + 128 + 1024;
+  const size_t b_stage = (size_t)(n / 64) * 8192;
+  if (env_int("ASP_TC_PERSISTENT", 1) && tp->max_chunks <= TC_MAXCH) {
+    // one CTA per SM; whatever shared memory the fixed parts leave goes to B stages
+    const size_t fixed = 2 * (size_t)(TC_CAP + 8) * 6 + 2 * TC_MAXCH * 4 + 4 * 32 * 33 * 4 + 16 + 1024 + 1024;
+    const size_t budget = impl(h)->smem_optin ? impl(h)->smem_optin : 232448;
+    int sb = (int)((budget - fixed) / (b_stage + TC_A_BYTES));
+    const int cap = env_int("ASP_TC_STAGES", 4);  // more stages measured no faster (1.17 ms at 5, 1.12 ms at 3)
+    if (sb > cap) sb = cap;
+    if (sb >= 2) {
+      const size_t smem = fixed + (size_t)sb * (b_stage + TC_A_BYTES);
+      static size_t attr_p = 0;
+      if (smem > attr_p) {
+        ASP_CUDA(cudaFuncSetAttribute(spmm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_p = smem;
+      }
+      int64_t g = impl(h)->sm_count;
+      if (g > tp->blocks) g = tp->blocks;
+      spmm_tc_persistent_kernel<<<(unsigned)g, TCP_THREADS, smem, h->stream>>>(
+          tm, A->const_row_data, A->const_col_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
+          reinterpret_cast<float*>(C->values), C->ld, alpha, beta, A->rows, A->nnz, n, (int)tp->blocks, sb,
+          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, p->dev_err);
+      impl(h)->launches++;
+      return status_of(cudaGetLastError());
+    }
+  }
+  const size_t smem = 2 * TC_A_BYTES + TC_BSTAGES * b_stage + (TC_CAP + 8) * 6 + TC_MAXCH * 4 + 128 + 1024;
   static size_t attr_bytes = 0;
   if (smem > attr_bytes) {
     ASP_CUDA(cudaFuncSetAttribute(spmm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -523,8 +928,8 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
   }
   spmm_tc_kernel<<<(unsigned)tp->blocks, TC_THREADS, smem, h->stream>>>(
       tm, A->const_row_data, A->const_col_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
-      reinterpret_cast<float*>(C->values), C->ld, alpha, beta, A->rows, A->nnz, n, tp->chunk_off, tp->chunk_list,
-      p->dev_err);
+      reinterpret_cast<float*>(C->values), C->ld, alpha, beta, A->rows, A->nnz, n, tp->chunk_off, tp->chunk_cnt,
+      tp->chunk_list, p->dev_err);
   impl(h)->launches++;
   return status_of(cudaGetLastError());
 }
