@@ -422,6 +422,20 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
 // the other roles then run into their own limits, and all meet at the final __syncthreads.
 // ------------------------------------------------------------------------------------------
 constexpr int TCP_THREADS = 320;
+#ifndef ASP_TC_BACKOFF_NS
+#define ASP_TC_BACKOFF_NS 64
+#endif
+
+// Bounded wait with back-off for the roles whose waits are long (builders at a block boundary,
+// epilogue): a warp that spins flat out takes issue slots from the single-thread producer and
+// MMA roles that share its scheduler.
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < TC_MAX_TRIES; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(ASP_TC_BACKOFF_NS);
+  }
+  return false;
+}
 
 // Bounded spin on the non-blocking test: lowest wake-up latency, for the waits that sit on the
 // per-chunk critical path (try_wait may park the thread for a scheduler time slice).
@@ -643,7 +657,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       const int a0 = e0 & ~7;
       const bool staged = (e1 - a0) <= TC_CAP;
       if (i + 1 < n_my) fetch(i + 1);
-      if (!mbar_wait(&csr_full[cs], (uint32_t)((i >> 1) & 1))) {
+      if (!mbar_wait_backoff(&csr_full[cs], (uint32_t)((i >> 1) & 1))) {
         ok = false;
         break;
       }
@@ -651,7 +665,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       const __nv_bfloat16* __restrict__ pv = staged ? s_val + cs * (TC_CAP + 8) - a0 : val;
       const int* pch = s_chunks + cs * TC_MAXCH;
       for (int j = 0; j < nch; ++j) {
-        if (!mbar_spin(&st_empty[sa], ph ^ 1u)) {
+        if (!mbar_wait_backoff(&st_empty[sa], ph ^ 1u)) {
           ok = false;
           break;
         }
@@ -698,7 +712,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
       const int nch = nch_next;
       if (i + 1 < n_my) nch_next = chunk_cnt[first + (i + 1) * stride];
-      if (!mbar_wait(&acc_full[acc], (uint32_t)((i >> 1) & 1))) {
+      if (!mbar_wait_backoff(&acc_full[acc], (uint32_t)((i >> 1) & 1))) {
         ok = false;
         break;
       }
