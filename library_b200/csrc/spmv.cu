@@ -446,10 +446,12 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   constexpr int IPT = kMergeIpt;
   __shared__ __align__(128) T s_val[kTileSlot];
   __shared__ __align__(128) int s_col[kTileSlot];
-  __shared__ int s_rowend[ITEMS + 1];
+  __shared__ __align__(8) unsigned char s_flags[ITEMS];  // 1 where an item of the merge list is a row end
   __shared__ __align__(8) uint64_t s_bar;
   __shared__ T s_wval[kThreads / 32];
   __shared__ int s_wflag[kThreads / 32];
+  __shared__ int s_wcnt[kThreads / 32];
+  static_assert(IPT == 8, "a thread's row-end bytes are read as one 8-byte word");
 
   const int tid = threadIdx.x;
   const int64_t t = blockIdx.x;
@@ -550,35 +552,45 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
     return;
   }
 
-  // (3b) products in place, then the serial walk
+  // (3b) products in place, then the serial walk.  Row end i is item (row_end_i + i) of the tile's
+  // merge list, so the rows mark their end items in a byte map and a thread learns from its eight
+  // bytes which of its items are row ends; the number of row ends before its first item (a block
+  // scan of the byte counts) is the row it starts in.  No search, no per-item offset reads.
   T* sp = s_val + lo;
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
     const int e = i * kThreads + tid;
     if (e < tile_nnz) sp[e] = sp[e] * __ldg(x + sc[e]);
   }
-  for (int i = tid; i < tile_rows; i += kThreads) s_rowend[i] = (int)((int64_t)rp[row_s + i + 1] - nz_s);
-  if (tid == 0) s_rowend[tile_rows] = INT_MAX;
+  *reinterpret_cast<uint2*>(s_flags + IPT * tid) = make_uint2(0u, 0u);
   __syncthreads();
-  const int tile_items = tile_rows + tile_nnz;
-  int d = tid * IPT;
-  if (d > tile_items) d = tile_items;
-  int d_end = d + IPT;
-  if (d_end > tile_items) d_end = tile_items;
-  int wl = d > tile_nnz ? d - tile_nnz : 0;
-  int wh = d < tile_rows ? d : tile_rows;
-  while (wl < wh) {
-    const int mid = (wl + wh) >> 1;
-    if (s_rowend[mid] <= d - mid - 1) wl = mid + 1;
-    else wh = mid;
+  for (int i = tid; i < tile_rows; i += kThreads) {
+    const int e = i == tid ? seg_e : (int)((int64_t)rp[row_s + i + 1] - nz_s);
+    s_flags[e + i] = 1;
   }
-  int i = wl, j = d - wl;
+  __syncthreads();
+  const int lane = tid & 31, warp = tid >> 5;
+  const uint2 fl = *reinterpret_cast<const uint2*>(s_flags + IPT * tid);
+  const unsigned long long ends = ((unsigned long long)fl.y << 32) | fl.x;
+  const int cnt = __popc(fl.x) + __popc(fl.y);
+  int inc = cnt;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += v;
+  }
+  if (lane == 31) s_wcnt[warp] = inc;
+  __syncthreads();
+  int i = inc - cnt;  // row ends before this thread's first item: the (tile-relative) row it starts in
+  for (int w = 0; w < warp; ++w) i += s_wcnt[w];
+  int j = IPT * tid - i;
+  const int tile_items = tile_rows + tile_nnz;
   T running = T(0), first_val = T(0);
   int first_row = -1;
 #pragma unroll
   for (int it = 0; it < IPT; ++it) {
-    if (d + it < d_end) {
-      if (j < s_rowend[i]) {
+    if (IPT * tid + it < tile_items) {
+      if (!((ends >> (8 * it)) & 1ull)) {
         running += sp[j];
         ++j;
       } else {
@@ -593,7 +605,6 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
       }
     }
   }
-  const int lane = tid & 31, warp = tid >> 5;
   int flag = first_row >= 0 ? 1 : 0;
   T acc = running;
 #pragma unroll
