@@ -344,6 +344,14 @@ alphasparseStatus_t alphasparseCsrRebaseRowOffsets(alphasparseHandle_t handle,
                                                    void* local_offsets,
                                                    alphasparseIndexType_t outType);
 
+/* ---- the step before the path: COO -> CSR row offsets -------------------------------- */
+/* cuda/format/coo2csr.h:82-92 (template alphasparseXcoo2csr<T>(row_data, nnz, m, csrRowPtr), default
+ * stream).  cooRowInd: DEVICE array of nnz ascending, zero-based row indices; csrRowPtr: DEVICE array
+ * of m+1 offsets (I32 or I64).  Stream-ordered on `stream`, no allocation. */
+alphasparseStatus_t alphasparseXcoo2csr(cudaStream_t stream, const int32_t* cooRowInd, int64_t nnz,
+                                        int64_t m, void* csrRowPtr,
+                                        alphasparseIndexType_t rowOffsetsType);
+
 /* ---- introspection (extension) ------------------------------------------------------ */
 /* Copies the analysed plan to host arrays for bit-exact comparison with a CPU twin.
  * Any output pointer may be NULL.  stats[16]: see ASP_STAT_* below. */
@@ -383,6 +391,13 @@ inline alphasparseStatus_t alphasparseCreateCsr(alphasparseSpMatDescr_t* spMatDe
   return alphasparseCreateCsr(spMatDescr, (int64_t)rows, (int64_t)cols, (int64_t)nnz,
                               (void*)csrRowOffsets, (void*)col_data, (void*)val_data,
                               csrRowOffsetsType, csrColIndType, idxBase, valueType);
+}
+/* Source compatibility with cuda/format/coo2csr.h:82-92 (default stream, as there). */
+template <typename T>
+inline alphasparseStatus_t alphasparseXcoo2csr(const int* row_data, int nnz, int m, T* csrRowPtr) {
+  static_assert(sizeof(T) == 4 || sizeof(T) == 8, "row offsets are 32- or 64-bit integers");
+  return alphasparseXcoo2csr((cudaStream_t)0, row_data, (int64_t)nnz, (int64_t)m, (void*)csrRowPtr,
+                             sizeof(T) == 8 ? ALPHA_SPARSE_INDEXTYPE_I64 : ALPHA_SPARSE_INDEXTYPE_I32);
 }
 #endif
 #endif /* ALPHASPARSE_B200_H */

@@ -42,7 +42,7 @@ EXPORTS = [
     "alphasparseSpMM_bufferSize", "alphasparseSpMM_preprocess",
     "alphasparseCsrPartitionRowsByNnz", "alphasparseCsrRebaseRowOffsets", "alphasparseCsrPlanGet",
     "alphasparseCsrLastVariant", "alphasparseGetLaunchCount", "get_time_us", "get_avg_time_n",
-    "alphasparseSpMVCsrNoAlloc",
+    "alphasparseSpMVCsrNoAlloc", "alphasparseXcoo2csr",
 ]
 
 
@@ -271,3 +271,14 @@ def spmv_csr_noalloc(row_ptr: torch.Tensor, col_idx: torch.Tensor, val: torch.Te
         C.c_int64(col_idx.numel()), C.c_void_p(row_ptr.data_ptr()), rt, C.c_void_p(col_idx.data_ptr()),
         C.c_void_p(val.data_ptr()), code, C.byref(a), C.c_void_p(x.data_ptr()), C.byref(b),
         C.c_void_p(y.data_ptr())))
+
+
+def coo2csr(coo_row: torch.Tensor, rows: int, out_dtype=torch.int32, stream=None) -> torch.Tensor:
+    """Row offsets (rows+1) from ascending int32 COO row indices on the device."""
+    assert coo_row.is_cuda and coo_row.dtype == torch.int32
+    out = torch.empty(rows + 1, dtype=out_dtype, device=coo_row.device)
+    st = torch.cuda.current_stream().cuda_stream if stream is None else stream
+    _check(load().alphasparseXcoo2csr(C.c_void_p(st), C.c_void_p(coo_row.data_ptr()), C.c_int64(coo_row.numel()),
+                                      C.c_int64(rows), C.c_void_p(out.data_ptr()),
+                                      INDEX_I64 if out_dtype == torch.int64 else INDEX_I32), "alphasparseXcoo2csr")
+    return out

@@ -161,6 +161,22 @@ __global__ void __launch_bounds__(256) rebase_kernel(const InT* __restrict__ rp,
     out[i] = (OutT)((int64_t)rp[row_begin + i] - base);
 }
 
+// csrRowPtr[r] = number of COO entries whose (ascending) row index is below r.
+template <typename OutT>
+__global__ void __launch_bounds__(256) coo2csr_kernel(const int32_t* __restrict__ coo_row, int64_t nnz,
+                                                      int64_t m, OutT* __restrict__ row_ptr) {
+  for (int64_t r = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; r <= m;
+       r += (int64_t)gridDim.x * blockDim.x) {
+    int64_t lo = 0, hi = nnz;
+    while (lo < hi) {
+      const int64_t mid = lo + ((hi - lo) >> 1);
+      if ((int64_t)coo_row[mid] < r) lo = mid + 1;
+      else hi = mid;
+    }
+    row_ptr[r] = (OutT)lo;
+  }
+}
+
 inline int grid_for(int64_t n, int sm_count) {
   int64_t g = (n + 255) / 256;
   const int64_t cap = (int64_t)sm_count * 8;
@@ -462,3 +478,22 @@ alphasparseStatus_t alphasparseCsrRebaseRowOffsets(alphasparseHandle_t h, const 
 }
 
 }  // extern "C"
+
+// The step before the path: CSR row offsets from the ascending row indices of a COO matrix.
+// Replaces cuda/format/coo2csr.h:82-92 of the reference (zero + atomicAdd histogram + thrust scan
+// on the default stream, with a printf) by one stream-ordered kernel: row r's offset is the
+// position of the first entry whose row index is >= r.
+extern "C" alphasparseStatus_t alphasparseXcoo2csr(cudaStream_t stream, const int32_t* cooRowInd,
+                                                   int64_t nnz, int64_t m, void* csrRowPtr,
+                                                   alphasparseIndexType_t rowOffsetsType) {
+  if (!csrRowPtr || (nnz > 0 && !cooRowInd)) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  if (nnz < 0 || m < 0) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  const bool o64 = rowOffsetsType == ALPHA_SPARSE_INDEXTYPE_I64;
+  if (!o64 && rowOffsetsType != ALPHA_SPARSE_INDEXTYPE_I32) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (!o64 && nnz >= (int64_t(1) << 31)) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  int64_t g = (m + 1 + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  if (o64) asp::coo2csr_kernel<int64_t><<<(unsigned)g, 256, 0, stream>>>(cooRowInd, nnz, m, (int64_t*)csrRowPtr);
+  else asp::coo2csr_kernel<int32_t><<<(unsigned)g, 256, 0, stream>>>(cooRowInd, nnz, m, (int32_t*)csrRowPtr);
+  return asp::status_of(cudaGetLastError());
+}

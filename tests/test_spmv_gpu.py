@@ -273,3 +273,19 @@ def test_partition_and_rebase_match_oracle(handle):
         loc = api.rebase_row_offsets(handle, rpd, int(b[1]), int(b[2]), torch.int32)
         torch.cuda.synchronize()
         assert np.array_equal(loc.cpu().numpy(), rp[b[1]:b[2] + 1] - rp[b[1]])
+
+
+def test_coo2csr_matches_row_offsets(handle):
+    """alphasparseXcoo2csr: offsets rebuilt from the expanded (ascending) row indices of a CSR matrix,
+    empty rows at both ends included."""
+    A = _mk("rmat", np.float32)
+    rp, _, _ = A.numpy()
+    rp = np.concatenate([[0, 0], rp, [rp[-1], rp[-1]]]).astype(np.int32)    # leading / trailing empty rows
+    rows = len(rp) - 1
+    coo = np.repeat(np.arange(rows, dtype=np.int32), np.diff(rp))
+    d = torch.from_numpy(coo).to("cuda")
+    for dt in (torch.int32, torch.int64):
+        got = api.coo2csr(d, rows, dt)
+        torch.cuda.synchronize()
+        assert np.array_equal(got.cpu().numpy(), rp)
+    assert np.array_equal(api.coo2csr(d[:0], 5).cpu().numpy(), np.zeros(6, np.int32))
