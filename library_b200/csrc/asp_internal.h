@@ -25,7 +25,10 @@ constexpr int kMergeItems = kThreads * kMergeIpt;
 // Fewer merge tiles than this (about 2.5 M items): the matrix is L2-resident and launch-bound.
 constexpr int64_t kSmallProblemTiles = 1200;
 // SpMM: rows per CTA and entries of A a CTA can stage at once.
-constexpr int kSpmmRowBlock = 128;
+#ifndef ASP_SPMM_ROW_BLOCK
+#define ASP_SPMM_ROW_BLOCK 128
+#endif
+constexpr int kSpmmRowBlock = ASP_SPMM_ROW_BLOCK;
 constexpr int kSpmmStageCap32 = 4096;  // 4-byte values
 constexpr int kSpmmStageCap64 = 3584;  // 8-byte values (48 KB of static shared memory)
 

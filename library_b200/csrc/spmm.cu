@@ -171,8 +171,11 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
       : "memory");
 }
 
+#ifndef ASP_SPMM_MIN_CTAS
+#define ASP_SPMM_MIN_CTAS 6
+#endif
 template <typename T, typename OffT, int LN, int VN>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, ASP_SPMM_MIN_CTAS)
 spmm_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const T* __restrict__ val,
                  const T* __restrict__ B, int64_t ldb, T* __restrict__ C, int64_t ldc, T alpha, T beta,
                  int64_t rows, int64_t n, int64_t nnz, int* __restrict__ err) {

@@ -175,6 +175,19 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
       : "memory");
 }
+// Same with the descriptors given as (low, high) words: a stage's or K step's descriptor differs
+// from a base descriptor only in the address field of the low word.
+__device__ __forceinline__ void umma_bf16_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(acc)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
@@ -408,13 +421,13 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
 // copy engine runs many chunks (and one row block) ahead of the tensor core and the epilogue of a
 // row block overlaps the MMAs of the next one:
 //   warps 0-3  builders : thread = row of the block; zero + scatter the row's entries of a chunk
-//                         into the A tile of the chunk's ring stage      (st_empty -> a_full)
+//                         into the A tile of the chunk's ring stage      (st_empty -> st_full)
 //   warps 4-7  epilogue : tcgen05.ld of one of two accumulators, alpha/beta, store C
 //                                                                       (acc_full -> acc_empty)
 //   warp 8     producer : bulk copies of the next block's CSR slice and chunk ids (csr_empty ->
 //                         csr_full), TMA of every chunk's B slice into the same ring of `sb`
-//                         stages                                        (st_empty -> b_full)
-//   warp 9     MMA      : waits a_full + b_full, issues the four tcgen05.mma of the chunk, commits
+//                         stages                                        (st_empty -> st_full)
+//   warp 9     MMA      : waits st_full (tile built + slice landed), issues the chunk's four tcgen05.mma, commits
 //                         once to st_empty, and to acc_full after the block's last chunk;
 //                         owns the tensor-memory allocation (two accumulators)
 // A barrier of the "empty" kind is waited on with the inverted parity, so its first use passes.
@@ -422,6 +435,7 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
 // the other roles then run into their own limits, and all meet at the final __syncthreads.
 // ------------------------------------------------------------------------------------------
 constexpr int TCP_THREADS = 320;
+constexpr int TCP_CSR = 3;  // row-block CSR buffers: staging block i+1 never waits for the builders of block i-1
 #ifndef ASP_TC_BACKOFF_NS
 #define ASP_TC_BACKOFF_NS 64
 #endif
@@ -472,18 +486,17 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
   unsigned char* sA = smem;                               // sb x 16 KB (A tiles and B slices share one ring)
   unsigned char* sB = sA + (size_t)sb * TC_A_BYTES;       // sb x b_stage_bytes
   unsigned char* p = sB + (size_t)sb * b_stage_bytes;
-  int* s_col = reinterpret_cast<int*>(p);                 // 2 x (TC_CAP + 8)
-  __nv_bfloat16* s_val = reinterpret_cast<__nv_bfloat16*>(s_col + 2 * (TC_CAP + 8));  // 2 x (TC_CAP + 8)
-  int* s_chunks = reinterpret_cast<int*>(s_val + 2 * (TC_CAP + 8));                   // 2 x TC_MAXCH
-  float* s_tr = reinterpret_cast<float*>(s_chunks + 2 * TC_MAXCH);  // 4 epilogue warps x 32 x 33
+  int* s_col = reinterpret_cast<int*>(p);                 // TCP_CSR x (TC_CAP + 8)
+  __nv_bfloat16* s_val = reinterpret_cast<__nv_bfloat16*>(s_col + TCP_CSR * (TC_CAP + 8));  // TCP_CSR x (TC_CAP + 8)
+  int* s_chunks = reinterpret_cast<int*>(s_val + TCP_CSR * (TC_CAP + 8));                   // TCP_CSR x TC_MAXCH
+  float* s_tr = reinterpret_cast<float*>(s_chunks + TCP_CSR * TC_MAXCH);  // 4 epilogue warps x 32 x 33
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_tr + 4 * 32 * 33 + 2);
-  uint64_t* csr_full = bars;            // [2]
-  uint64_t* csr_empty = bars + 2;       // [2]
-  uint64_t* acc_full = bars + 4;        // [2]
-  uint64_t* acc_empty = bars + 6;       // [2]
-  uint64_t* a_full = bars + 8;          // [sb] the chunk's A tile is built
-  uint64_t* b_full = a_full + sb;       // [sb] the chunk's B slice landed
-  uint64_t* st_empty = b_full + sb;     // [sb] the chunk's MMAs retired: tile and slice are free
+  uint64_t* csr_full = bars;            // [TCP_CSR]
+  uint64_t* csr_empty = bars + 4;       // [TCP_CSR]
+  uint64_t* acc_full = bars + 8;        // [2]
+  uint64_t* acc_empty = bars + 10;      // [2]
+  uint64_t* st_full = bars + 12;        // [sb] A tile built (4 builder warps) and B slice landed (producer + bytes)
+  uint64_t* st_empty = st_full + sb;    // [sb] the chunk's MMAs retired: tile and slice are free
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(st_empty + sb);
   volatile int* s_fail = reinterpret_cast<volatile int*>(s_tmem + 1);
 
@@ -493,15 +506,16 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
   for (int i = tid; i < sb * TC_A_BYTES / 16; i += TCP_THREADS)
     reinterpret_cast<uint4*>(sA)[i] = make_uint4(0, 0, 0, 0);
   if (tid == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < TCP_CSR; ++i) {
       mbar_init(&csr_full[i], 1);
-      mbar_init(&csr_empty[i], 4);   // one arrival per builder warp: 128 arrivals on one barrier
-      mbar_init(&acc_full[i], 1);    // serialise in the barrier unit and cost ~500 cycles per use
+      mbar_init(&csr_empty[i], 4);   // one arrival per builder warp
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], 4);
     }
     for (int i = 0; i < sb; ++i) {
-      mbar_init(&a_full[i], 4);
-      mbar_init(&b_full[i], 1);
+      mbar_init(&st_full[i], 5);
       mbar_init(&st_empty[i], 1);
     }
     *s_fail = 0;
@@ -524,10 +538,10 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
   if (warp == 8) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      int nch_of[2] = {0, 0};
+      int nch_of[TCP_CSR] = {0, 0, 0};
       auto stage_csr = [&](int i) -> bool {
-        const int cs = i & 1;
-        if (!mbar_wait(&csr_empty[cs], (uint32_t)(((i >> 1) & 1) ^ 1))) return false;
+        const int cs = i % TCP_CSR;
+        if (!mbar_wait(&csr_empty[cs], (uint32_t)(((i / TCP_CSR) & 1) ^ 1))) return false;
         const int b = first + i * stride;
         const int64_t r0 = (int64_t)b * TC_M;
         const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
@@ -563,19 +577,19 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       int st = 0;           // ring stage and its use parity, advanced without divisions
       uint32_t ph = 0;
       for (int i = 0; i < n_my && ok; ++i) {
-        const int cs = i & 1;
+        const int cs = i % TCP_CSR;
         const int nch = nch_of[cs];
         if (i + 1 < n_my) ok = stage_csr(i + 1);
-        if (ok && !mbar_wait(&csr_full[cs], (uint32_t)((i >> 1) & 1))) ok = false;
+        if (ok && !mbar_wait(&csr_full[cs], (uint32_t)((i / TCP_CSR) & 1))) ok = false;
         const int* pch = s_chunks + cs * TC_MAXCH;
         for (int j = 0; j < nch && ok; ++j) {
           if (!mbar_spin(&st_empty[st], ph ^ 1u)) {
             ok = false;
             break;
           }
-          mbar_expect_tx(&b_full[st], (uint32_t)b_stage_bytes);
+          mbar_expect_tx(&st_full[st], (uint32_t)b_stage_bytes);
           for (int q = 0; q < nblk; ++q)
-            tma_load_2d(sB + (size_t)st * b_stage_bytes + q * 8192, &tmB, q * 64, pch[j] * TC_KC, &b_full[st]);
+            tma_load_2d(sB + (size_t)st * b_stage_bytes + q * 8192, &tmB, q * 64, pch[j] * TC_KC, &st_full[st]);
           if (++st == sb) {
             st = 0;
             ph ^= 1u;
@@ -592,7 +606,14 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       bool ok = true;
       int st = 0;
       uint32_t ph = 0;
-      const uint32_t a_base0 = smem_u32(sA), b_base0 = smem_u32(sB);
+      // The issuing thread's instruction stream is the pipeline's clock: keep it short.  A stage's
+      // descriptors differ from stage 0's only in the low word (the 14-bit address field), so the
+      // loop adds small constants instead of rebuilding 64-bit descriptors.
+      const uint64_t ad0 = umma_desc(smem_u32(sA), 2048, 128, 0);
+      const uint64_t bd0 = umma_desc(smem_u32(sB), 8192, 1024, 2);
+      const uint32_t a_hi = (uint32_t)(ad0 >> 32), b_hi = (uint32_t)(bd0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)ad0, b_lo0 = (uint32_t)bd0;
+      const uint32_t a_step = TC_A_BYTES >> 4, b_step = (uint32_t)b_stage_bytes >> 4;
       int nch_next = n_my > 0 ? chunk_cnt[first] : 0;
       for (int i = 0; i < n_my && ok; ++i) {
         const int acc = i & 1;
@@ -604,19 +625,19 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d = tmem + (uint32_t)acc * acc_cols;
+        uint32_t first_acc = 0u;  // the block's very first MMA overwrites the accumulator
         for (int j = 0; j < nch; ++j) {
-          if (!mbar_spin(&a_full[st], ph) || !mbar_spin(&b_full[st], ph)) {
+          if (!mbar_spin(&st_full[st], ph)) {
             ok = false;
             break;
           }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          // descriptors differ from the stage's first one only in the 14-bit address field
-          const uint64_t ad0 = umma_desc(a_base0 + (uint32_t)st * TC_A_BYTES, 2048, 128, 0);
-          const uint64_t bd0 = umma_desc(b_base0 + (uint32_t)st * (uint32_t)b_stage_bytes, 8192, 1024, 2);
-#pragma unroll
-          for (int kk = 0; kk < TC_KC / 16; ++kk)
-            umma_bf16(d, ad0 + (uint64_t)(kk * (4096 >> 4)), bd0 + (uint64_t)(kk * (2048 >> 4)), idesc,
-                      (j > 0 || kk > 0) ? 1u : 0u);
+          const uint32_t a_lo = a_lo0 + (uint32_t)st * a_step, b_lo = b_lo0 + (uint32_t)st * b_step;
+          umma_bf16_lohi(d, a_lo, a_hi, b_lo, b_hi, idesc, first_acc);
+          umma_bf16_lohi(d, a_lo + 256u, a_hi, b_lo + 128u, b_hi, idesc, 1u);
+          umma_bf16_lohi(d, a_lo + 512u, a_hi, b_lo + 256u, b_hi, idesc, 1u);
+          umma_bf16_lohi(d, a_lo + 768u, a_hi, b_lo + 384u, b_hi, idesc, 1u);
+          first_acc = 1u;
           umma_commit(&st_empty[st]);
           if (++st == sb) {
             st = 0;
@@ -650,14 +671,14 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
     };
     if (n_my > 0) fetch(0);
     for (int i = 0; i < n_my && ok; ++i) {
-      const int cs = i & 1;
+      const int cs = i % TCP_CSR;
       const int e0 = n_e0, e1 = n_e1, nch = n_nch;
       int k = n_k;
       const int k_end = n_kend;
       const int a0 = e0 & ~7;
       const bool staged = (e1 - a0) <= TC_CAP;
       if (i + 1 < n_my) fetch(i + 1);
-      if (!mbar_wait_backoff(&csr_full[cs], (uint32_t)((i >> 1) & 1))) {
+      if (!mbar_wait_backoff(&csr_full[cs], (uint32_t)((i / TCP_CSR) & 1))) {
         ok = false;
         break;
       }
@@ -690,7 +711,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
         wrote[sa] = w;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(&a_full[sa]);
+        if (lane == 0) mbar_arrive(&st_full[sa]);
         if (++sa == sb) {
           sa = 0;
           ph ^= 1u;
@@ -912,10 +933,10 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
   const size_t b_stage = (size_t)(n / 64) * 8192;
   if (env_int("ASP_TC_PERSISTENT", 1) && tp->max_chunks <= TC_MAXCH) {
     // one CTA per SM; whatever shared memory the fixed parts leave goes to B stages
-    const size_t fixed = 2 * (size_t)(TC_CAP + 8) * 6 + 2 * TC_MAXCH * 4 + 4 * 32 * 33 * 4 + 16 + 1024 + 1024;
+    const size_t fixed = TCP_CSR * (size_t)(TC_CAP + 8) * 6 + TCP_CSR * TC_MAXCH * 4 + 4 * 32 * 33 * 4 + 16 + 1024 + 1024;
     const size_t budget = impl(h)->smem_optin ? impl(h)->smem_optin : 232448;
     int sb = (int)((budget - fixed) / (b_stage + TC_A_BYTES));
-    const int cap = env_int("ASP_TC_STAGES", 4);  // more stages measured no faster (1.17 ms at 5, 1.12 ms at 3)
+    const int cap = env_int("ASP_TC_STAGES", 3);  // more stages measured no faster (1.17 ms at 5, 1.12 ms at 3)
     if (sb > cap) sb = cap;
     if (sb >= 2) {
       const size_t smem = fixed + (size_t)sb * (b_stage + TC_A_BYTES);
