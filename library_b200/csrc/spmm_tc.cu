@@ -420,21 +420,24 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
 // and splits the work of spmm_tc_kernel over four roles that only meet through mbarriers, so the
 // copy engine runs many chunks (and one row block) ahead of the tensor core and the epilogue of a
 // row block overlaps the MMAs of the next one:
-//   warps 0-3  builders : thread = row of the block; zero + scatter the row's entries of a chunk
-//                         into the A tile of the chunk's ring stage      (st_empty -> st_full)
-//   warps 4-7  epilogue : tcgen05.ld of one of two accumulators, alpha/beta, store C
+//   warps 0-15 builders : four groups of 128 threads (thread = row of the block) take chunks in
+//                         turn; a group clears what it last wrote in the chunk's ring stage and
+//                         scatters its rows' entries of the chunk into the A tile
+//                                                                       (st_empty -> st_full)
+//   warps 16-19 epilogue: tcgen05.ld of one of two accumulators, alpha/beta, store C
 //                                                                       (acc_full -> acc_empty)
-//   warp 8     producer : bulk copies of the next block's CSR slice and chunk ids (csr_empty ->
+//   warp 20    producer : bulk copies of the next block's CSR slice and chunk ids (csr_empty ->
 //                         csr_full), TMA of every chunk's B slice into the same ring of `sb`
 //                         stages                                        (st_empty -> st_full)
-//   warp 9     MMA      : waits st_full (tile built + slice landed), issues the chunk's four tcgen05.mma, commits
+//   warp 21    MMA      : waits st_full (tile built + slice landed), issues the chunk's four tcgen05.mma, commits
 //                         once to st_empty, and to acc_full after the block's last chunk;
 //                         owns the tensor-memory allocation (two accumulators)
 // A barrier of the "empty" kind is waited on with the inverted parity, so its first use passes.
 // Every wait is bounded; a role whose wait expires raises the CTA's fail flag and leaves its loop,
 // the other roles then run into their own limits, and all meet at the final __syncthreads.
 // ------------------------------------------------------------------------------------------
-constexpr int TCP_THREADS = 320;
+constexpr int TCP_GROUPS = 4;                 // builder groups of 128 threads; the ring depth is a multiple of it
+constexpr int TCP_THREADS = (TCP_GROUPS * 4 + 6) * 32;
 constexpr int TCP_CSR = 3;  // row-block CSR buffers: staging block i+1 never waits for the builders of block i-1
 #ifndef ASP_TC_BACKOFF_NS
 #define ASP_TC_BACKOFF_NS 64
@@ -508,7 +511,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
   if (tid == 0) {
     for (int i = 0; i < TCP_CSR; ++i) {
       mbar_init(&csr_full[i], 1);
-      mbar_init(&csr_empty[i], 4);   // one arrival per builder warp
+      mbar_init(&csr_empty[i], TCP_GROUPS * 4);   // one arrival per builder warp
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], 1);
@@ -521,7 +524,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
     *s_fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 9) {
+  if (warp == TCP_GROUPS * 4 + 5) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
                  "r"(2u * acc_cols)
                  : "memory");
@@ -535,61 +538,80 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
   const int first = blockIdx.x, stride = gridDim.x;
   const int n_my = first < nblocks ? (nblocks - first + stride - 1) / stride : 0;
 
-  if (warp == 8) {
+  if (warp == TCP_GROUPS * 4 + 4) {
     // ---------------- producer ----------------
-    if (lane == 0) {
+    // The whole warp runs the loop (waits are warp-uniform): lane 0 stages the CSR slices and arms
+    // the barriers, lanes 0..nblk-1 each issue one 64-column box of a chunk's B slice.  The scalars
+    // a block's staging needs are loaded from global memory a block ahead of their use.
+    {
       int nch_of[TCP_CSR] = {0, 0, 0};
-      auto stage_csr = [&](int i) -> bool {
-        const int cs = i % TCP_CSR;
-        if (!mbar_wait(&csr_empty[cs], (uint32_t)(((i / TCP_CSR) & 1) ^ 1))) return false;
+      int p_e0 = 0, p_e1 = 0, p_j0 = 0, p_nch = 0;  // prefetched for the next block to stage
+      auto prefetch = [&](int i) {
         const int b = first + i * stride;
         const int64_t r0 = (int64_t)b * TC_M;
         const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
-        const int e0 = rp[r0], e1 = rp[r0 + nr];
-        const int a0 = e0 & ~7;
-        const bool staged = (e1 - a0) <= TC_CAP;
-        const int j0 = chunk_off[b], nch = chunk_cnt[b];
+        p_e0 = rp[r0];
+        p_e1 = rp[r0 + nr];
+        p_j0 = chunk_off[b];
+        p_nch = chunk_cnt[b];
+      };
+      auto stage_csr = [&](int i) -> bool {
+        const int cs = i % TCP_CSR;
+        if (!mbar_wait(&csr_empty[cs], (uint32_t)(((i / TCP_CSR) & 1) ^ 1))) return false;
+        const int e0 = p_e0, e1 = p_e1, j0 = p_j0, nch = p_nch;
+        if (i + 1 < n_my) prefetch(i + 1);
         nch_of[cs] = nch;
-        int* dc = s_col + cs * (TC_CAP + 8);
-        __nv_bfloat16* dv = s_val + cs * (TC_CAP + 8);
-        uint32_t cnt = 0;
-        if (staged) {
-          int a1 = (e1 + 7) & ~7;
-          const int nnz8 = (int)(nnz & ~(int64_t)7);
-          if (a1 > nnz8) a1 = nnz8;
-          if (a1 < a0) a1 = a0;
-          cnt = (uint32_t)(a1 - a0);
-          for (int e = a1 > e0 ? a1 : e0; e < e1; ++e) {  // past the arrays' last full group of eight
-            dc[e - a0] = col[e];
-            dv[e - a0] = val[e];
+        if (lane == 0) {
+          const int a0 = e0 & ~7;
+          const bool staged = (e1 - a0) <= TC_CAP;
+          int* dc = s_col + cs * (TC_CAP + 8);
+          __nv_bfloat16* dv = s_val + cs * (TC_CAP + 8);
+          uint32_t cnt = 0;
+          if (staged) {
+            int a1 = (e1 + 7) & ~7;
+            const int nnz8 = (int)(nnz & ~(int64_t)7);
+            if (a1 > nnz8) a1 = nnz8;
+            if (a1 < a0) a1 = a0;
+            cnt = (uint32_t)(a1 - a0);
+            for (int e = a1 > e0 ? a1 : e0; e < e1; ++e) {  // past the arrays' last full group of eight
+              dc[e - a0] = col[e];
+              dv[e - a0] = val[e];
+            }
           }
+          const uint32_t nch4 = (uint32_t)((nch + 3) & ~3);
+          mbar_expect_tx(&csr_full[cs], cnt * 6u + nch4 * 4u);
+          if (cnt) {
+            bulk_g2s(dc, col + a0, cnt * 4u, &csr_full[cs]);
+            bulk_g2s(dv, val + a0, cnt * 2u, &csr_full[cs]);
+          }
+          if (nch4) bulk_g2s(s_chunks + cs * TC_MAXCH, chunk_list + j0, nch4 * 4u, &csr_full[cs]);
         }
-        const uint32_t nch4 = (uint32_t)((nch + 3) & ~3);
-        mbar_expect_tx(&csr_full[cs], cnt * 6u + nch4 * 4u);
-        if (cnt) {
-          bulk_g2s(dc, col + a0, cnt * 4u, &csr_full[cs]);
-          bulk_g2s(dv, val + a0, cnt * 2u, &csr_full[cs]);
-        }
-        if (nch4) bulk_g2s(s_chunks + cs * TC_MAXCH, chunk_list + j0, nch4 * 4u, &csr_full[cs]);
         return true;
       };
-      bool ok = n_my > 0 ? stage_csr(0) : true;
+      bool ok = true;
+      if (n_my > 0) {
+        prefetch(0);
+        ok = stage_csr(0);
+      }
       int st = 0;           // ring stage and its use parity, advanced without divisions
       uint32_t ph = 0;
+      unsigned char* my_box = sB + lane * 8192;
       for (int i = 0; i < n_my && ok; ++i) {
         const int cs = i % TCP_CSR;
         const int nch = nch_of[cs];
         if (i + 1 < n_my) ok = stage_csr(i + 1);
         if (ok && !mbar_wait(&csr_full[cs], (uint32_t)((i / TCP_CSR) & 1))) ok = false;
         const int* pch = s_chunks + cs * TC_MAXCH;
+        int next_row = nch > 0 ? pch[0] * TC_KC : 0;
         for (int j = 0; j < nch && ok; ++j) {
+          const int brow = next_row;
+          if (j + 1 < nch) next_row = pch[j + 1] * TC_KC;
           if (!mbar_spin(&st_empty[st], ph ^ 1u)) {
             ok = false;
             break;
           }
-          mbar_expect_tx(&st_full[st], (uint32_t)b_stage_bytes);
-          for (int q = 0; q < nblk; ++q)
-            tma_load_2d(sB + (size_t)st * b_stage_bytes + q * 8192, &tmB, q * 64, pch[j] * TC_KC, &st_full[st]);
+          if (lane == 0) mbar_expect_tx(&st_full[st], (uint32_t)b_stage_bytes);
+          if (lane < nblk) tma_load_2d(my_box + (size_t)st * b_stage_bytes, &tmB, lane * 64, brow, &st_full[st]);
           if (++st == sb) {
             st = 0;
             ph ^= 1u;
@@ -598,7 +620,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       }
       if (!ok) *s_fail = 1;
     }
-  } else if (warp == 9) {
+  } else if (warp == TCP_GROUPS * 4 + 5) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(n >> 3) << 17) |
@@ -631,7 +653,9 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
             ok = false;
             break;
           }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          // no tcgen05.fence here: the mbarrier wait orders the MMAs after the TMA bytes and after
+          // the builders' stores (made visible to the async proxy by their fence.proxy.async); a
+          // fence in this loop would make the issuing thread wait for the previous chunk's MMAs
           const uint32_t a_lo = a_lo0 + (uint32_t)st * a_step, b_lo = b_lo0 + (uint32_t)st * b_step;
           umma_bf16_lohi(d, a_lo, a_hi, b_lo, b_hi, idesc, first_acc);
           umma_bf16_lohi(d, a_lo + 256u, a_hi, b_lo + 128u, b_hi, idesc, 1u);
@@ -648,12 +672,15 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       }
       if (!ok) *s_fail = 1;
     }
-  } else if (warp < 4) {
-    // ---------------- builders: thread = row ----------------
+  } else if (warp < TCP_GROUPS * 4) {
+    // ---------------- builders: TCP_GROUPS groups, thread = row ----------------
     bool ok = true;
-    int sa = 0;
+    const int grp = warp >> 2;    // builder group: takes the chunks whose running number is = grp (mod TCP_GROUPS)
+    const int row = tid & 127;
+    int sa = 0;                   // ring stage / parity of the running chunk number (all chunks, both groups)
     uint32_t ph = 0;
-    unsigned long long wrote[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // per ring stage (sb <= 8)
+    uint32_t cnum = 0;
+    const int row_off = (row >> 3) * 128 + (row & 7) * 16;  // this row inside an 8-column core-matrix column
     // per-block scalars are fetched one block ahead
     int n_e0 = 0, n_e1 = 0, n_nch = 0, n_k = 0, n_kend = 0;
     auto fetch = [&](int i) {
@@ -664,9 +691,9 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       n_e1 = rp[r0 + nr];
       n_nch = chunk_cnt[b];
       n_k = n_kend = 0;
-      if (tid < nr) {
-        n_k = rp[r0 + tid];
-        n_kend = rp[r0 + tid + 1];
+      if (row < nr) {
+        n_k = rp[r0 + row];
+        n_kend = rp[r0 + row + 1];
       }
     };
     if (n_my > 0) fetch(0);
@@ -685,33 +712,47 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       const int* __restrict__ pc = staged ? s_col + cs * (TC_CAP + 8) - a0 : col;
       const __nv_bfloat16* __restrict__ pv = staged ? s_val + cs * (TC_CAP + 8) - a0 : val;
       const int* pch = s_chunks + cs * TC_MAXCH;
-      for (int j = 0; j < nch; ++j) {
-        if (!mbar_wait_backoff(&st_empty[sa], ph ^ 1u)) {
-          ok = false;
-          break;
+      for (int j = 0; j < nch; ++j, ++cnum) {
+        if ((int)(cnum % TCP_GROUPS) == grp) {
+          if (!mbar_wait_backoff(&st_empty[sa], ph ^ 1u)) {
+            ok = false;
+            break;
+          }
+          // A serial thread pays 4-6 cycles per dependent instruction, so the chunk's work is kept
+          // short and wide: the row is re-zeroed with eight independent 16-byte stores (one per
+          // 8-column core matrix) and entries are handled four at a time without a dependency
+          // between them (columns ascend, so "below cend" is monotone within the four).
+          unsigned char* trow = sA + sa * TC_A_BYTES + row_off;
+          if (cnum >= (uint32_t)sb) {
+#pragma unroll
+            for (int q = 0; q < TC_KC / 8; ++q) *reinterpret_cast<uint4*>(trow + q * 2048) = make_uint4(0, 0, 0, 0);
+          }
+          const int cbeg = pch[j] * TC_KC, cend = cbeg + TC_KC;
+          bool more = k < k_end;
+          while (more) {
+            int c[4];
+            __nv_bfloat16 v[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int kk = k + q < k_end ? k + q : k_end - 1;
+              c[q] = pc[kk];
+              v[q] = pv[kk];
+            }
+            int used = 0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const bool live = (k + q < k_end) && (c[q] < cend);  // entries below cbeg belong to the other group
+              const int x = c[q] - cbeg;
+              if (live && x >= 0) *reinterpret_cast<__nv_bfloat16*>(trow + (x >> 3) * 2048 + (x & 7) * 2) = v[q];
+              used += live ? 1 : 0;
+            }
+            k += used;
+            more = (used == 4) && (k < k_end);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&st_full[sa]);
         }
-        unsigned char* tile = sA + sa * TC_A_BYTES;
-        // clear the (few) positions this thread wrote when the stage was last used: their 6-bit
-        // in-chunk columns are remembered in a 64-bit mask per ring stage
-        unsigned long long m = wrote[sa];
-        while (m) {
-          const int c = __ffsll((long long)m) - 1;
-          m &= m - 1;
-          *reinterpret_cast<unsigned short*>(tile + a_tile_off(tid, c)) = 0;
-        }
-        const int cbeg = pch[j] * TC_KC, cend = cbeg + TC_KC;
-        unsigned long long w = 0;
-        while (k < k_end) {
-          const int c = pc[k];
-          if (c >= cend) break;
-          *reinterpret_cast<__nv_bfloat16*>(tile + a_tile_off(tid, c - cbeg)) = pv[k];
-          w |= 1ull << (c - cbeg);
-          ++k;
-        }
-        wrote[sa] = w;
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&st_full[sa]);
         if (++sa == sb) {
           sa = 0;
           ph ^= 1u;
@@ -722,9 +763,9 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
     }
     if (!ok) *s_fail = 1;
   } else {
-    // ---------------- epilogue: warps 4-7 read tensor-memory lanes 32*(warp-4) .. ----------------
+    // ---------------- epilogue: four warps (ids = 0..3 mod 4) read tensor-memory lanes 32*(id mod 4) .. ----------------
     bool ok = true;
-    const int row = tid - 128;
+    const int row = tid - TCP_GROUPS * 128;
     int nch_next = n_my > 0 ? chunk_cnt[first] : 0;
     for (int i = 0; i < n_my && ok; ++i) {
       const int acc = i & 1;
@@ -741,8 +782,8 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       // tcgen05.ld hands lane l the 32 columns of row l; a per-warp 32 x 33 shared-memory tile turns
       // that around so that a store instruction writes 32 consecutive floats of one row (one line)
       // instead of 16 bytes of 32 different rows.
-      float* tr = s_tr + (warp - 4) * (32 * 33);
-      const int wrow0 = (warp - 4) * 32;
+      float* tr = s_tr + (warp - TCP_GROUPS * 4) * (32 * 33);
+      const int wrow0 = (warp - TCP_GROUPS * 4) * 32;
       (void)row;
       for (int cb = 0; cb < n; cb += 32) {
         uint32_t a[32];
@@ -778,7 +819,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
     if (tid == 0) atomicExch(err, 1);
     __nanosleep(1000000);  // let copies and MMAs still in flight retire before the memory goes away
   }
-  if (warp == 9)
+  if (warp == TCP_GROUPS * 4 + 5)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2u * acc_cols) : "memory");
 }
 
@@ -936,9 +977,10 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
     const size_t fixed = TCP_CSR * (size_t)(TC_CAP + 8) * 6 + TCP_CSR * TC_MAXCH * 4 + 4 * 32 * 33 * 4 + 16 + 1024 + 1024;
     const size_t budget = impl(h)->smem_optin ? impl(h)->smem_optin : 232448;
     int sb = (int)((budget - fixed) / (b_stage + TC_A_BYTES));
-    const int cap = env_int("ASP_TC_STAGES", 3);  // more stages measured no faster (1.17 ms at 5, 1.12 ms at 3)
+    const int cap = env_int("ASP_TC_STAGES", 4);  // more stages measured no faster (1.17 ms at 5, 1.12 ms at 3)
     if (sb > cap) sb = cap;
-    if (sb >= 2) {
+    sb -= sb % TCP_GROUPS;  // a ring stage always returns to the same builder group
+    if (sb >= TCP_GROUPS) {
       const size_t smem = fixed + (size_t)sb * (b_stage + TC_A_BYTES);
       static size_t attr_p = 0;
       if (smem > attr_p) {
