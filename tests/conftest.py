@@ -13,6 +13,16 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 
 
+def pytest_sessionstart(session):
+    """A fresh checkout has no built libraries (they are not in the history): compile the CUDA library
+    and the C oracle once when nvcc / gcc are there.  A prebuilt library is used as it is."""
+    from library_b200 import build as lib_build
+    if not os.path.exists(lib_build.LIB):
+        lib_build.build()
+    import oracle
+    oracle.lib()
+
+
 def load_golden():
     """tests/golden/csr_golden.npz -> {case: {field: array}} (made by tests/golden/make_golden.py
     from the reference's own CPU code)."""
