@@ -70,6 +70,9 @@ def parse_args():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every rank owns a workload-sized row shard; strong: one matrix is "
                          "row-partitioned by balanced nnz across the ranks")
+    ap.add_argument("--x-exchange", default="broadcast", choices=["broadcast", "window"],
+                    help="N > 1: how x reaches the ranks.  broadcast: whole x from rank 0.  window (strong scaling, "
+                         "SpMV): x is sharded like y and a rank receives only the column window of its rows")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -302,6 +305,9 @@ def run_ours(args):
         os.environ["ASP_SPMV_VARIANT"] = args.variant
 
     strong = args.scaling == "strong" and world > 1
+    window = args.x_exchange == "window" and strong
+    if args.x_exchange == "window" and not window:
+        raise SystemExit("--x-exchange window needs --scaling strong and more than one rank")
     h = api.Handle()
     stream = torch.cuda.Stream()
     h.set_stream(stream.cuda_stream)
@@ -312,6 +318,7 @@ def run_ours(args):
         w = make_workload(args.workload, dev, 0, args.scale)
         full = w["A"]
         with torch.cuda.stream(stream):
+            bounds = api.partition_rows_by_nnz(h, full.row_ptr, world)
             Aloc, (r0, r1) = shard_csr(h, full.rows, full.cols, full.row_ptr, full.col_idx, full.val, rank, world)
             w["A"] = Csr(r1 - r0, full.cols, Aloc.row_ptr, Aloc.col_idx.clone(), Aloc.val.clone())
         torch.cuda.synchronize()
@@ -331,12 +338,27 @@ def run_ours(args):
     else:
         x = G.uniform((A.cols, w["n"]), w["lo"], 1.0, dtype=w["dtype"], device=dev, seed=11)
         y = torch.zeros((A.rows, w["n"]), dtype=ydt, device=dev)
-    if world > 1:
+    ex = x_own = None
+    if window:
+        if w["kind"] != "spmv":
+            raise SystemExit("--x-exchange window covers SpMV")
+        from library_b200.sharding import XWindowExchange
+        # x is sharded like y: this rank keeps x[r0, r1) and receives the rest of its column window
+        with torch.cuda.stream(stream):
+            cmin, cmax = api.column_range(h, A.col_idx)
+            ex = XWindowExchange(bounds, cmin, cmax, rank, world, w["dtype"], dev)
+            x_own = x[r0:r1].clone()
+            x_win = ex.run(x_own)
+        torch.cuda.synchronize()
+        del x
+        x = x_own
+        torch.cuda.empty_cache()
+    elif world > 1:
         dist.broadcast(x, src=0)
     torch.cuda.synchronize()
 
     if w["kind"] == "spmv":
-        xd, yd = api.DnVec(x), api.DnVec(y)
+        xd, yd = (api.DnVecWindow(x_win, A.cols, ex.lo) if window else api.DnVec(x)), api.DnVec(y)
         buf = torch.empty(api.spmv_buffer_size(h, Am, xd, yd, w["alpha"], w["beta"]), dtype=torch.uint8, device=dev)
         with torch.cuda.stream(stream):
             Am.analyse(h)
@@ -397,9 +419,11 @@ def run_ours(args):
 
         def e2e_step():
             with torch.cuda.stream(stream):
-                if rank == 0 or world == 1:
+                if window or rank == 0 or world == 1:
                     x.copy_(hx, non_blocking=True)
-                if world > 1:
+                if window:
+                    ex.run(x)
+                elif world > 1:
                     dist.broadcast(x, src=0)
                 if reads_y:
                     y.copy_(hy_in, non_blocking=True)
@@ -419,9 +443,30 @@ def run_ours(args):
         if world > 1:
             dist.all_reduce(et, op=dist.ReduceOp.MAX)
         e_ms = float(et.item()) / e_steps
+        # the exchange step alone (whole-x broadcast, or the window exchange)
+        x_ms = None
+        if world > 1:
+            def xchg():
+                with torch.cuda.stream(stream):
+                    ex.run(x) if window else dist.broadcast(x, src=0)
+            for _ in range(3):
+                xchg()
+            barrier()
+            x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            x0.record(stream)
+            for _ in range(10):
+                xchg()
+            x1.record(stream)
+            barrier()
+            xt = torch.tensor([x0.elapsed_time(x1) / 10], dtype=torch.float64, device=dev)
+            dist.all_reduce(xt, op=dist.ReduceOp.MAX)
+            x_ms = float(xt.item())
         h2d = x.numel() * x.element_size() + (y.numel() * y.element_size() if reads_y else 0)
         e2e = {"value": total_bytes / (e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e_ms,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": y.numel() * y.element_size(),
+               "x_exchange": args.x_exchange if world > 1 else None, "x_exchange_ms": x_ms,
+               "x_bytes_received_per_rank": (ex.bytes_received if window else
+                                             (x.numel() * x.element_size() if world > 1 else 0)),
                "note": "A resident in HBM (like the reference's created matrix handle); x (+y when beta!=0) from "
                        "pinned host memory each step, y back to the host each step"}
 
@@ -458,7 +503,8 @@ def run_ours(args):
                        if nbytes > 126e6 else "L2-resident workload, no flush (the configuration is smaller than L2)",
                        "sharding": ("one matrix row-partitioned by balanced nnz" if strong else
                                     "every rank owns a workload-sized row shard")
-                       + ", x replicated by NCCL broadcast, y sharded"},
+                       + (", x sharded like y and exchanged by column window (point-to-point over NVLink), y sharded"
+                          if window else ", x replicated by NCCL broadcast, y sharded")},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                          "peak_source": peak_src,
                          "traffic": (TRAFFIC_RATIO[args.workload] * nbytes) if args.workload in TRAFFIC_RATIO else None,

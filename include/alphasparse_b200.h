@@ -344,6 +344,22 @@ alphasparseStatus_t alphasparseCsrRebaseRowOffsets(alphasparseHandle_t handle,
                                                    void* local_offsets,
                                                    alphasparseIndexType_t outType);
 
+/* Smallest and largest column index in col_idx[0, nnz) (DEVICE pointer, I32), written to HOST
+ * integers; nnz = 0 gives {0, -1}.  A rank of a row-sharded matrix needs only
+ * x[min_col, max_col]: for a banded matrix that is its own rows plus a halo.  Allocates 16 bytes
+ * and synchronises handle->stream (a set-up call, not part of the SpMV path). */
+alphasparseStatus_t alphasparseCsrColumnRange(alphasparseHandle_t handle, int64_t nnz,
+                                              const void* col_idx, alphasparseIndexType_t colType,
+                                              int64_t* min_col, int64_t* max_col);
+/* A dense vector of logical length size of which only elements [first, first+count) exist, stored
+ * at window_values[0, count).  alphasparseSpMV with such an x is valid when every column index of
+ * A lies inside the window (alphasparseCsrColumnRange); nothing outside it is read.  As y it is
+ * valid only for a matrix whose rows are the window.  No counterpart in the reference (its
+ * vectors are always whole, handle.h:478-485). */
+alphasparseStatus_t alphasparseCreateDnVecWindow(alphasparseDnVecDescr_t* descr, int64_t size,
+                                                 int64_t first, int64_t count,
+                                                 void* window_values, alphasparseDataType data_type);
+
 /* ---- the step before the path: COO -> CSR row offsets -------------------------------- */
 /* cuda/format/coo2csr.h:82-92 (template alphasparseXcoo2csr<T>(row_data, nnz, m, csrRowPtr), default
  * stream).  cooRowInd: DEVICE array of nnz ascending, zero-based row indices; csrRowPtr: DEVICE array

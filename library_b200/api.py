@@ -42,7 +42,8 @@ EXPORTS = [
     "alphasparseSpMM_bufferSize", "alphasparseSpMM_preprocess",
     "alphasparseCsrPartitionRowsByNnz", "alphasparseCsrRebaseRowOffsets", "alphasparseCsrPlanGet",
     "alphasparseCsrLastVariant", "alphasparseGetLaunchCount", "get_time_us", "get_avg_time_n",
-    "alphasparseSpMVCsrNoAlloc", "alphasparseXcoo2csr",
+    "alphasparseSpMVCsrNoAlloc", "alphasparseXcoo2csr", "alphasparseCsrColumnRange",
+    "alphasparseCreateDnVecWindow",
 ]
 
 
@@ -131,6 +132,19 @@ class DnVec:
     def __del__(self):
         if getattr(self, "d", None):
             load().alphasparseDestroyDnVec(self.d)
+
+
+class DnVecWindow(DnVec):
+    """A vector of logical length ``size`` of which only [first, first + t.numel()) exists, in t."""
+
+    def __init__(self, t: torch.Tensor, size: int, first: int):
+        assert t.is_cuda and t.is_contiguous()
+        self.t = t
+        self.size, self.first = size, first
+        self.d = C.c_void_p()
+        _check(load().alphasparseCreateDnVecWindow(C.byref(self.d), C.c_int64(size), C.c_int64(first),
+                                                   C.c_int64(t.numel()), C.c_void_p(t.data_ptr()),
+                                                   _dtype_code(t.dtype)), "alphasparseCreateDnVecWindow")
 
 
 class DnMat:
@@ -242,6 +256,15 @@ def partition_rows_by_nnz(handle: Handle, row_ptr: torch.Tensor, parts: int):
                                                    out.ctypes.data_as(C.c_void_p)),
            "alphasparseCsrPartitionRowsByNnz")
     return out
+
+
+def column_range(handle: Handle, col_idx: torch.Tensor):
+    """(min, max) column index of a device col_idx slice; (0, -1) when it is empty."""
+    lo, hi = C.c_int64(0), C.c_int64(-1)
+    _check(load().alphasparseCsrColumnRange(handle.h, C.c_int64(col_idx.numel()),
+                                            C.c_void_p(col_idx.data_ptr()), INDEX_I32, C.byref(lo),
+                                            C.byref(hi)), "alphasparseCsrColumnRange")
+    return int(lo.value), int(hi.value)
 
 
 def rebase_row_offsets(handle: Handle, row_ptr: torch.Tensor, row_begin: int, row_end: int,

@@ -161,6 +161,27 @@ __global__ void __launch_bounds__(256) rebase_kernel(const InT* __restrict__ rp,
     out[i] = (OutT)((int64_t)rp[row_begin + i] - base);
 }
 
+// Smallest and largest column index of a slice of col_idx: out[0] = min, out[1] = max
+// (out starts as {INT64_MAX, -1}).
+__global__ void __launch_bounds__(256) col_range_kernel(const int32_t* __restrict__ col, int64_t nnz,
+                                                        long long* __restrict__ out) {
+  int32_t lo = INT32_MAX, hi = -1;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nnz;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t c = __ldg(col + i);
+    lo = min(lo, c);
+    hi = max(hi, c);
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+    hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+  }
+  if ((threadIdx.x & 31) == 0 && hi >= 0) {
+    atomicMin(out, (long long)lo);
+    atomicMax(out + 1, (long long)hi);
+  }
+}
+
 // csrRowPtr[r] = number of COO entries whose (ascending) row index is below r.
 template <typename OutT>
 __global__ void __launch_bounds__(256) coo2csr_kernel(const int32_t* __restrict__ coo_row, int64_t nnz,
@@ -475,6 +496,35 @@ alphasparseStatus_t alphasparseCsrRebaseRowOffsets(alphasparseHandle_t h, const 
   else rebase_kernel<<<g, 256, 0, st>>>((const int32_t*)row_offsets, row_begin, n, (int32_t*)local);
   impl(h)->launches++;
   return status_of(cudaGetLastError());
+}
+
+alphasparseStatus_t alphasparseCsrColumnRange(alphasparseHandle_t h, int64_t nnz, const void* col_idx,
+                                              alphasparseIndexType_t colT, int64_t* min_col,
+                                              int64_t* max_col) {
+  if (!h || !h->impl) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+  if (!min_col || !max_col || (nnz > 0 && !col_idx)) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  if (nnz < 0) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  if (colT != ALPHA_SPARSE_INDEXTYPE_I32) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  *min_col = 0;
+  *max_col = -1;
+  if (nnz == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+  long long* d = nullptr;
+  ASP_CUDA(cudaMalloc(&d, 2 * sizeof(long long)));
+  const long long init[2] = {INT64_MAX, -1};
+  cudaError_t e = cudaMemcpyAsync(d, init, sizeof(init), cudaMemcpyHostToDevice, h->stream);
+  long long out[2] = {0, -1};
+  if (e == cudaSuccess) {
+    col_range_kernel<<<grid_for(nnz, impl(h)->sm_count), 256, 0, h->stream>>>((const int32_t*)col_idx, nnz, d);
+    impl(h)->launches++;
+    e = cudaMemcpyAsync(out, d, sizeof(out), cudaMemcpyDeviceToHost, h->stream);
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+  cudaFree(d);
+  if (e == cudaSuccess) {
+    *min_col = out[0];
+    *max_col = out[1];
+  }
+  return status_of(e);
 }
 
 }  // extern "C"

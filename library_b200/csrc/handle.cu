@@ -167,6 +167,21 @@ alphasparseStatus_t alphasparseCreateDnVec(alphasparseDnVecDescr_t* descr, int64
   return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
+alphasparseStatus_t alphasparseCreateDnVecWindow(alphasparseDnVecDescr_t* descr, int64_t size,
+                                                 int64_t first, int64_t count, void* window_values,
+                                                 alphasparseDataType data_type) {
+  if (!descr) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  if (size < 0 || first < 0 || count < 0 || first + count > size) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  if (count > 0 && !window_values) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  const size_t es = asp::elem_size(data_type);
+  if (es == 0) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  // Element i of the logical vector lives at window_values[i - first]: the descriptor carries the
+  // address element 0 would have.  Only elements inside the window may be touched by a kernel.
+  const uintptr_t base = reinterpret_cast<uintptr_t>(window_values) - (uintptr_t)first * es;
+  return alphasparseCreateDnVec(descr, size, size > 0 ? reinterpret_cast<void*>(base) : window_values,
+                                data_type);
+}
+
 alphasparseStatus_t alphasparseCreateDnMat(alphasparseDnMatDescr_t* descr, int64_t rows,
                                            int64_t cols, int64_t ld, void* values,
                                            alphasparseDataType valueType,

@@ -4,7 +4,10 @@ Rows are split into contiguous ranges of near-equal nnz by the C ABI call
 alphasparseCsrPartitionRowsByNnz (the rule of the reference's CPU partitioner,
 hygon/util/partition.cpp:83-96, in 64-bit).  A shard keeps global column indices, its own
 rebased row offsets (32-bit when the shard's nnz allows) and the matching slices of the column
-and value arrays; x is replicated to every rank, y stays sharded by rows.
+and value arrays; y stays sharded by rows.  x is either replicated to every rank (broadcast /
+all-gather of the whole vector) or, when it is sharded like y, exchanged by column window: a rank
+receives only x[min_col, max_col] of its shard (XWindowExchange), which for a banded matrix is its
+own rows plus a halo.
 """
 from __future__ import annotations
 
@@ -42,3 +45,74 @@ def shard_csr(handle: api.Handle, rows: int, cols: int, row_ptr: torch.Tensor, c
     local_rp = api.rebase_row_offsets(handle, row_ptr, r0, r1, out_dtype)
     A = api.CsrMatrix(r1 - r0, cols, local_rp, col_idx[k0:k1], val[k0:k1])
     return A, (r0, r1)
+
+
+WINDOW_ALIGN = 32  # the window starts on a multiple of this many elements (keeps 128-byte alignment)
+
+
+def exchange_plan(own_bounds, windows, rank: int):
+    """Who sends what for the column-window exchange.  ``own_bounds`` (world + 1 ascending integers):
+    rank p owns x[own_bounds[p], own_bounds[p+1]).  ``windows`` (world pairs): rank p needs
+    x[lo_p, hi_p) (hi_p <= lo_p: nothing).  Returns (sends, recvs) for ``rank``:
+    sends = [(peer, a, b)]: x[a, b) of this rank's own part goes to peer;
+    recvs = [(peer, a, b)]: x[a, b) arrives from peer.  Global element indices, peers ascending,
+    the rank's own overlap listed as a copy to itself (peer == rank)."""
+    world = len(windows)
+    my_lo, my_hi = int(own_bounds[rank]), int(own_bounds[rank + 1])
+    w_lo, w_hi = int(windows[rank][0]), int(windows[rank][1])
+    sends, recvs = [], []
+    for p in range(world):
+        a, b = max(my_lo, int(windows[p][0])), min(my_hi, int(windows[p][1]))
+        if b > a:
+            sends.append((p, a, b))
+        a, b = max(w_lo, int(own_bounds[p])), min(w_hi, int(own_bounds[p + 1]))
+        if b > a:
+            recvs.append((p, a, b))
+    return sends, recvs
+
+
+class XWindowExchange:
+    """x sharded like y (rank p owns x[own_bounds[p], own_bounds[p+1])); before each SpMV a rank
+    fills a buffer holding x[lo, hi), the column window of its shard, from the owners.  Peers
+    exchange with point-to-point sends (NCCL over NVLink on GPUs, gloo on CPU), the own part is a
+    local copy.  For a banded matrix the traffic is the halo, not the vector."""
+
+    def __init__(self, own_bounds, col_min: int, col_max: int, rank: int, world: int, dtype, device,
+                 group=None):
+        import torch.distributed as dist
+        self.rank, self.world, self.group = rank, world, group
+        self.own_bounds = [int(b) for b in own_bounds]
+        lo = (col_min // WINDOW_ALIGN) * WINDOW_ALIGN if col_max >= col_min else 0
+        hi = col_max + 1 if col_max >= col_min else 0
+        self.lo, self.hi = lo, hi
+        mine = torch.tensor([lo, hi], dtype=torch.int64)
+        if world > 1:
+            # windows of all ranks (two integers each); NCCL needs device tensors
+            t = mine.to(device) if dist.get_backend(group) == "nccl" else mine
+            allw = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(allw, t, group=group)
+            self.windows = [(int(w[0]), int(w[1])) for w in allw]
+        else:
+            self.windows = [(lo, hi)]
+        self.sends, self.recvs = exchange_plan(self.own_bounds, self.windows, rank)
+        self.window = torch.empty(max(hi - lo, 0), dtype=dtype, device=device)
+        self.bytes_received = sum(b - a for p, a, b in self.recvs if p != rank) * self.window.element_size()
+
+    def run(self, x_own: torch.Tensor) -> torch.Tensor:
+        """x_own = this rank's part of x.  Returns the window buffer (element i is x[lo + i]).
+        Ordered on the current stream."""
+        import torch.distributed as dist
+        o0 = self.own_bounds[self.rank]
+        ops = []
+        for p, a, b in self.recvs:
+            if p == self.rank:
+                self.window[a - self.lo:b - self.lo].copy_(x_own[a - o0:b - o0])
+            else:
+                ops.append(dist.P2POp(dist.irecv, self.window[a - self.lo:b - self.lo], p, group=self.group))
+        for p, a, b in self.sends:
+            if p != self.rank:
+                ops.append(dist.P2POp(dist.isend, x_own[a - o0:b - o0], p, group=self.group))
+        if ops:
+            for r in dist.batch_isend_irecv(ops):
+                r.wait()
+        return self.window

@@ -1,0 +1,176 @@
+"""Column-window exchange of x for a row-sharded matrix (x sharded like y).
+
+CPU part: the exchange plan (who sends which range to whom) against a brute-force statement, and
+the exchange itself on gloo ranks (world 2 and 3): every rank's window equals the same slice of
+the whole x, and a banded matrix moves only its halo.  GPU part: a windowed x descriptor through
+the C ABI gives the same y as the whole x on one device; on two devices the exchange runs over
+NCCL and the y shards equal the oracle.
+"""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def test_exchange_plan_brute_force():
+    from library_b200.sharding import exchange_plan
+    rng = np.random.default_rng(3)
+    for world in (1, 2, 3, 5):
+        n = 1000
+        cuts = np.sort(rng.integers(0, n + 1, size=world - 1))
+        own = np.concatenate([[0], cuts, [n]])
+        windows = []
+        for _ in range(world):
+            a, b = sorted(rng.integers(0, n + 1, size=2))
+            windows.append((int(a), int(b)) if rng.random() > 0.2 else (0, 0))
+        owner = np.searchsorted(own[1:], np.arange(n), side="right")
+        for r in range(world):
+            sends, recvs = exchange_plan(own, windows, r)
+            got = np.full(n, -1)
+            for p, a, b in recvs:
+                assert np.all(owner[a:b] == p) and np.all(got[a:b] == -1)
+                got[a:b] = p
+            lo, hi = windows[r]
+            want = np.full(n, -1)
+            want[lo:hi] = owner[lo:hi]
+            assert np.array_equal(got, want)
+            # what r sends to p is what p expects from r
+            for p, a, b in sends:
+                assert (r, a, b) in exchange_plan(own, windows, p)[1]
+
+
+def _cpu_worker(rank, world, port, out_dir, kind):
+    sys.path.insert(0, ROOT)
+    import oracle
+    from library_b200 import generators as G
+    from library_b200.sharding import partition_bounds_host, XWindowExchange
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    A = G.laplacian_2d_5pt(48) if kind == "banded" else G.rmat(11, 8, seed=5, dtype=torch.float64)
+    rp, ci, v = A.numpy()
+    x = G.uniform((A.cols,), -1, 1, dtype=torch.float64, seed=6).numpy()
+    b = partition_bounds_host(rp, world)
+    r0, r1 = int(b[rank]), int(b[rank + 1])
+    k0, k1 = int(rp[r0]), int(rp[r1])
+    cols = ci[k0:k1]
+    cmin, cmax = (int(cols.min()), int(cols.max())) if len(cols) else (0, -1)
+    ex = XWindowExchange(b, cmin, cmax, rank, world, torch.float64, "cpu")
+    win = ex.run(torch.from_numpy(x[r0:r1].copy()))          # this rank holds only its own part of x
+    assert np.array_equal(win.numpy(), x[ex.lo:ex.hi])
+    # the oracle indexes x from 0: place the window in a vector of NaN so that any read outside it shows
+    xw = np.full(A.cols, np.nan)
+    xw[ex.lo:ex.hi] = win.numpy()
+    local_rp = (rp[r0:r1 + 1] - rp[r0]).astype(np.int32)
+    y = oracle.spmv(local_rp, cols, v[k0:k1], xw, 1.5, 0.0)
+    np.save(os.path.join(out_dir, f"y{rank}.npy"), y)
+    np.save(os.path.join(out_dir, f"recv{rank}.npy"), np.array([ex.bytes_received]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,kind", [(2, "banded"), (3, "banded"), (3, "rmat")])
+def test_window_exchange_on_cpu_ranks(tmp_path, world, kind):
+    import oracle
+    from library_b200 import generators as G
+    mp.spawn(_cpu_worker, args=(world, _free_port(), str(tmp_path), kind), nprocs=world, join=True)
+    A = G.laplacian_2d_5pt(48) if kind == "banded" else G.rmat(11, 8, seed=5, dtype=torch.float64)
+    rp, ci, v = A.numpy()
+    x = G.uniform((A.cols,), -1, 1, dtype=torch.float64, seed=6).numpy()
+    want = oracle.spmv(rp, ci, v, x, 1.5, 0.0)
+    got = np.concatenate([np.load(tmp_path / f"y{r}.npy") for r in range(world)])
+    assert np.array_equal(got, want)
+    recv = [int(np.load(tmp_path / f"recv{r}.npy")[0]) for r in range(world)]
+    if kind == "banded":
+        # a rank of the 48-wide grid needs at most one grid line (plus alignment slack) per neighbour
+        assert max(recv) <= 2 * (48 + 32) * 8
+
+
+@pytest.mark.gpu
+def test_windowed_x_equals_whole_x(handle):
+    from library_b200 import api
+    from library_b200 import generators as G
+    A = G.laplacian_3d_7pt(40, dtype=torch.float32, index64=False).to("cuda")
+    x = G.uniform((A.cols,), -1, 1, device="cuda", seed=3)
+    r0, r1 = 20000, 41000
+    k0, k1 = int(A.row_ptr[r0]), int(A.row_ptr[r1])
+    rp = api.rebase_row_offsets(handle, A.row_ptr, r0, r1)
+    col = A.col_idx[k0:k1].clone()
+    val = A.val[k0:k1].clone()
+    lo, hi = api.column_range(handle, col)
+    assert (lo, hi) == (int(col.min()), int(col.max()))
+    assert api.column_range(handle, col[:0]) == (0, -1)
+    Am = api.CsrMatrix(r1 - r0, A.cols, rp, col, val)
+    y_full = torch.zeros(r1 - r0, device="cuda")
+    api.spmv(handle, Am, api.DnVec(x), api.DnVec(y_full), 1.0, 0.0)
+    lo_al = lo // 32 * 32
+    win = x[lo_al:hi + 1].clone()
+    for variant in ("binned", "merge"):
+        os.environ["ASP_SPMV_VARIANT"] = variant
+        try:
+            y_win = torch.full((r1 - r0,), 7.0, device="cuda")
+            api.spmv(handle, Am, api.DnVecWindow(win, A.cols, lo_al), api.DnVec(y_win), 1.0, 0.0)
+            torch.cuda.synchronize()
+        finally:
+            del os.environ["ASP_SPMV_VARIANT"]
+        assert torch.allclose(y_win, y_full, rtol=1e-6, atol=1e-6)
+    with pytest.raises(api.AlphaSparseError):
+        api.DnVecWindow(win, A.cols, A.cols - 1)          # window runs past the logical end
+
+
+def _gpu_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    from library_b200 import api
+    from library_b200 import generators as G
+    from library_b200.sharding import shard_csr, XWindowExchange
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    A = G.laplacian_3d_7pt(64, dtype=torch.float64).to("cuda")
+    x = G.uniform((A.cols,), -1, 1, dtype=torch.float64, seed=8).to("cuda")   # the host generator's stream
+    h = api.Handle()
+    bounds = api.partition_rows_by_nnz(h, A.row_ptr, world)
+    Aloc, (r0, r1) = shard_csr(h, A.rows, A.cols, A.row_ptr, A.col_idx, A.val, rank, world)
+    cmin, cmax = api.column_range(h, Aloc.col_idx)
+    ex = XWindowExchange(bounds, cmin, cmax, rank, world, torch.float64, torch.device("cuda", rank))
+    win = ex.run(x[r0:r1].clone())
+    y = torch.zeros(r1 - r0, dtype=torch.float64, device="cuda")
+    api.spmv(h, Aloc, api.DnVecWindow(win, A.cols, ex.lo), api.DnVec(y), 1.0, 0.0)
+    torch.cuda.synchronize()
+    np.save(os.path.join(out_dir, f"y{rank}.npy"), y.cpu().numpy())
+    np.save(os.path.join(out_dir, f"recv{rank}.npy"), np.array([ex.bytes_received]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_window_exchange_on_two_gpus(tmp_path):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    import oracle
+    from conftest import rel_l2
+    from library_b200 import generators as G
+    world = 2
+    mp.spawn(_gpu_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    A = G.laplacian_3d_7pt(64, dtype=torch.float64)
+    rp, ci, v = A.numpy()
+    x = G.uniform((A.cols,), -1, 1, dtype=torch.float64, seed=8).numpy()
+    want = oracle.spmv(rp, ci, v, x, 1.0, 0.0)
+    got = np.concatenate([np.load(tmp_path / f"y{r}.npy") for r in range(world)])
+    assert rel_l2(got, want) <= 1e-12
+    recv = [int(np.load(tmp_path / f"recv{r}.npy")[0]) for r in range(world)]
+    assert max(recv) <= (64 * 64 + 32) * 8            # one grid plane (plus alignment slack)
