@@ -38,7 +38,8 @@ constexpr uint32_t TC_MAX_TRIES = 1u << 22;
 constexpr int TC_A_BYTES = TC_M * TC_KC * 2;  // 16 KB, K-major core matrices, no swizzle
 constexpr int TC_BSTAGES = 3;   // B slices in flight (two A tiles are enough: scatter is short)
 constexpr int TC_CAP = 4096;    // entries of a row block staged in shared memory
-constexpr int TC_MAXCH = 512;   // chunk ids of a row block staged in shared memory
+constexpr int TC_MAXCH = 256;   // chunks of a row block whose ids and entry offsets are staged in shared memory
+constexpr int TC_SRC_SHIFT = 13; // a scatter word = (entry's offset in the block's slice << 13) | element offset in the tile
 
 struct TcPlan {
   int64_t blocks = 0, total_chunks = 0;
@@ -47,6 +48,10 @@ struct TcPlan {
   int32_t* chunk_off = nullptr;   // device, blocks + 1; every block's list starts on a multiple of four
   int32_t* chunk_cnt = nullptr;   // device, blocks: number of chunks of the block
   int32_t* chunk_list = nullptr;  // device, chunk_off[blocks] entries
+  // The entries of A regrouped by chunk (within a row block; inside a chunk in row, then column
+  // order), so that a tile is filled by independent threads instead of one serial walk per row:
+  int32_t* chunk_ent = nullptr;   // device, parallel to chunk_list: first position in `scatter` of the chunk's entries
+  uint32_t* scatter = nullptr;    // device, nnz words: where the entry comes from and where it goes
 };
 
 // ---- preprocessing -------------------------------------------------------------------------
@@ -120,6 +125,61 @@ __global__ void __launch_bounds__(256) tc_chunks_kernel(const int32_t* __restric
         chunk_list[pos++] = base + (tid * (TC_SPAN_WORDS / 256) + w) * 32 + b;
       }
     }
+  }
+}
+
+// One CTA per row block, one thread per chunk of the block.  A chunk's entries are, row by row,
+// the run of the row's (ascending) columns inside [64 c, 64 c + 64): two binary searches per row.
+// FILL = false: counts[g] = entries of chunk g.  FILL = true: writes the chunk's scatter words at
+// chunk_ent[g]; a word holds the entry's offset from the block's first entry rounded down to a
+// multiple of eight (the staging kernel copies from there) and the bf16 element offset in the
+// 128 x 64 tile.  An exclusive scan of the counts over all chunk slots (padding slots count zero)
+// is the chunk's position: the chunks of earlier blocks hold exactly the entries before the block.
+__device__ __forceinline__ int lower_bound_col(const int32_t* __restrict__ col, int lo, int hi, int key) {
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (col[mid] < key) lo = mid + 1;
+    else hi = mid;
+  }
+  return lo;
+}
+template <bool FILL>
+__global__ void __launch_bounds__(128) tc_scatter_kernel(const int32_t* __restrict__ rp,
+                                                         const int32_t* __restrict__ col, int64_t rows,
+                                                         const int32_t* __restrict__ chunk_off,
+                                                         const int32_t* __restrict__ chunk_cnt,
+                                                         const int32_t* __restrict__ chunk_list,
+                                                         int32_t* __restrict__ counts,
+                                                         const int32_t* __restrict__ chunk_ent,
+                                                         uint32_t* __restrict__ scatter, int* __restrict__ flags) {
+  __shared__ int s_rp[TC_M + 1];
+  const int64_t r0 = (int64_t)blockIdx.x * TC_M;
+  const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
+  for (int i = threadIdx.x; i <= nr; i += 128) s_rp[i] = rp[r0 + i];
+  __syncthreads();
+  const int j0 = chunk_off[blockIdx.x], nch = chunk_cnt[blockIdx.x];
+  const int a0 = s_rp[0] & ~7;
+  for (int j = threadIdx.x; j < nch; j += 128) {
+    const int cbeg = chunk_list[j0 + j] * TC_KC, cend = cbeg + TC_KC;
+    int n = 0;
+    int out = FILL ? chunk_ent[j0 + j] : 0;
+    for (int r = 0; r < nr; ++r) {
+      const int lo = lower_bound_col(col, s_rp[r], s_rp[r + 1], cbeg);
+      const int hi = lower_bound_col(col, lo, s_rp[r + 1], cend);
+      if (FILL) {
+        for (int e = lo; e < hi; ++e) {
+          const int x = col[e] - cbeg;
+          scatter[out++] = ((uint32_t)(e - a0) << TC_SRC_SHIFT) |
+                           (uint32_t)((x >> 3) * 1024 + (r >> 3) * 64 + (r & 7) * 8 + (x & 7));
+        }
+      } else {
+        n += hi - lo;
+        // two entries of a row in one column would land on one tile element
+        for (int e = lo + 1; e < hi; ++e)
+          if (col[e] == col[e - 1]) atomicOr(&flags[1], 1);
+      }
+    }
+    if (!FILL) counts[j0 + j] = n;
   }
 }
 
@@ -437,7 +497,7 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
 // the other roles then run into their own limits, and all meet at the final __syncthreads.
 // ------------------------------------------------------------------------------------------
 constexpr int TCP_GROUPS = 4;                 // builder groups of 128 threads; the ring depth is a multiple of it
-constexpr int TCP_THREADS = (TCP_GROUPS * 4 + 6) * 32;
+constexpr int TCP_THREADS = (TCP_GROUPS * 4 + 7) * 32;  // builders, 4 epilogue warps, producer, 2 MMA warps
 constexpr int TCP_CSR = 3;  // row-block CSR buffers: staging block i+1 never waits for the builders of block i-1
 #ifndef ASP_TC_BACKOFF_NS
 #define ASP_TC_BACKOFF_NS 64
@@ -481,7 +541,8 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
                           float* __restrict__ C, int64_t ldc, float alpha, float beta, int64_t rows,
                           int64_t nnz, int n, int nblocks, int sb,
                           const int32_t* __restrict__ chunk_off, const int32_t* __restrict__ chunk_cnt,
-                          const int32_t* __restrict__ chunk_list, int* __restrict__ err) {
+                          const int32_t* __restrict__ chunk_list, const int32_t* __restrict__ chunk_ent,
+                          const uint32_t* __restrict__ scatter, int* __restrict__ err) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int nblk = n / 64;
@@ -489,10 +550,11 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
   unsigned char* sA = smem;                               // sb x 16 KB (A tiles and B slices share one ring)
   unsigned char* sB = sA + (size_t)sb * TC_A_BYTES;       // sb x b_stage_bytes
   unsigned char* p = sB + (size_t)sb * b_stage_bytes;
-  int* s_col = reinterpret_cast<int*>(p);                 // TCP_CSR x (TC_CAP + 8)
-  __nv_bfloat16* s_val = reinterpret_cast<__nv_bfloat16*>(s_col + TCP_CSR * (TC_CAP + 8));  // TCP_CSR x (TC_CAP + 8)
-  int* s_chunks = reinterpret_cast<int*>(s_val + TCP_CSR * (TC_CAP + 8));                   // TCP_CSR x TC_MAXCH
-  float* s_tr = reinterpret_cast<float*>(s_chunks + TCP_CSR * TC_MAXCH);  // 4 epilogue warps x 32 x 33
+  uint32_t* s_sc = reinterpret_cast<uint32_t*>(p);        // TCP_CSR x (TC_CAP + 8) scatter words
+  __nv_bfloat16* s_val = reinterpret_cast<__nv_bfloat16*>(s_sc + TCP_CSR * (TC_CAP + 8));   // TCP_CSR x (TC_CAP + 8)
+  int* s_chunks = reinterpret_cast<int*>(s_val + TCP_CSR * (TC_CAP + 8));                   // TCP_CSR x TC_MAXCH chunk ids
+  int* s_ent = s_chunks + TCP_CSR * TC_MAXCH;                                               // TCP_CSR x TC_MAXCH entry offsets
+  float* s_tr = reinterpret_cast<float*>(s_ent + TCP_CSR * TC_MAXCH);  // 4 epilogue warps x 32 x 33
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_tr + 4 * 32 * 33 + 2);
   uint64_t* csr_full = bars;            // [TCP_CSR]
   uint64_t* csr_empty = bars + 4;       // [TCP_CSR]
@@ -505,6 +567,11 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t acc_cols = n <= 64 ? 64u : (n <= 128 ? 128u : 256u);
+  // Two threads issue MMAs when tensor memory holds four accumulators (N <= 128): chunks with an
+  // even running number go to one, odd ones to the other, each into an accumulator of its own
+  // (the epilogue adds them).  One thread's stream of wait / 4 x tcgen05.mma / commit costs about
+  // twice the 256 cycles the tensor core needs for a chunk, so a single issuer halves its rate.
+  const int issuers = acc_cols <= 128u ? 2 : 1;
 
   for (int i = tid; i < sb * TC_A_BYTES / 16; i += TCP_THREADS)
     reinterpret_cast<uint4*>(sA)[i] = make_uint4(0, 0, 0, 0);
@@ -514,7 +581,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       mbar_init(&csr_empty[i], TCP_GROUPS * 4);   // one arrival per builder warp
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_full[i], (uint32_t)issuers);
       mbar_init(&acc_empty[i], 4);
     }
     for (int i = 0; i < sb; ++i) {
@@ -526,7 +593,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
   }
   if (warp == TCP_GROUPS * 4 + 5) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
-                 "r"(2u * acc_cols)
+                 "r"(2u * (uint32_t)issuers * acc_cols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -544,7 +611,6 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
     // the barriers, lanes 0..nblk-1 each issue one 64-column box of a chunk's B slice.  The scalars
     // a block's staging needs are loaded from global memory a block ahead of their use.
     {
-      int nch_of[TCP_CSR] = {0, 0, 0};
       int p_e0 = 0, p_e1 = 0, p_j0 = 0, p_nch = 0;  // prefetched for the next block to stage
       auto prefetch = [&](int i) {
         const int b = first + i * stride;
@@ -560,11 +626,10 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
         if (!mbar_wait(&csr_empty[cs], (uint32_t)(((i / TCP_CSR) & 1) ^ 1))) return false;
         const int e0 = p_e0, e1 = p_e1, j0 = p_j0, nch = p_nch;
         if (i + 1 < n_my) prefetch(i + 1);
-        nch_of[cs] = nch;
         if (lane == 0) {
           const int a0 = e0 & ~7;
           const bool staged = (e1 - a0) <= TC_CAP;
-          int* dc = s_col + cs * (TC_CAP + 8);
+          uint32_t* dc = s_sc + cs * (TC_CAP + 8);
           __nv_bfloat16* dv = s_val + cs * (TC_CAP + 8);
           uint32_t cnt = 0;
           if (staged) {
@@ -574,17 +639,20 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
             if (a1 < a0) a1 = a0;
             cnt = (uint32_t)(a1 - a0);
             for (int e = a1 > e0 ? a1 : e0; e < e1; ++e) {  // past the arrays' last full group of eight
-              dc[e - a0] = col[e];
+              dc[e - a0] = scatter[e];
               dv[e - a0] = val[e];
             }
           }
           const uint32_t nch4 = (uint32_t)((nch + 3) & ~3);
-          mbar_expect_tx(&csr_full[cs], cnt * 6u + nch4 * 4u);
+          mbar_expect_tx(&csr_full[cs], cnt * 6u + nch4 * 8u);
           if (cnt) {
-            bulk_g2s(dc, col + a0, cnt * 4u, &csr_full[cs]);
+            bulk_g2s(dc, scatter + a0, cnt * 4u, &csr_full[cs]);
             bulk_g2s(dv, val + a0, cnt * 2u, &csr_full[cs]);
           }
-          if (nch4) bulk_g2s(s_chunks + cs * TC_MAXCH, chunk_list + j0, nch4 * 4u, &csr_full[cs]);
+          if (nch4) {
+            bulk_g2s(s_chunks + cs * TC_MAXCH, chunk_list + j0, nch4 * 4u, &csr_full[cs]);
+            bulk_g2s(s_ent + cs * TC_MAXCH, chunk_ent + j0, nch4 * 4u, &csr_full[cs]);
+          }
         }
         return true;
       };
@@ -593,41 +661,26 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
         prefetch(0);
         ok = stage_csr(0);
       }
-      int st = 0;           // ring stage and its use parity, advanced without divisions
-      uint32_t ph = 0;
-      unsigned char* my_box = sB + lane * 8192;
-      for (int i = 0; i < n_my && ok; ++i) {
-        const int cs = i % TCP_CSR;
-        const int nch = nch_of[cs];
+      // The chunks' B slices are requested by the builder groups: this warp only keeps the row
+      // blocks' slices of the scatter list, the values and the chunk tables a block ahead.
+      for (int i = 0; i < n_my && ok; ++i)
         if (i + 1 < n_my) ok = stage_csr(i + 1);
-        if (ok && !mbar_wait(&csr_full[cs], (uint32_t)((i / TCP_CSR) & 1))) ok = false;
-        const int* pch = s_chunks + cs * TC_MAXCH;
-        int next_row = nch > 0 ? pch[0] * TC_KC : 0;
-        for (int j = 0; j < nch && ok; ++j) {
-          const int brow = next_row;
-          if (j + 1 < nch) next_row = pch[j + 1] * TC_KC;
-          if (!mbar_spin(&st_empty[st], ph ^ 1u)) {
-            ok = false;
-            break;
-          }
-          if (lane == 0) mbar_expect_tx(&st_full[st], (uint32_t)b_stage_bytes);
-          if (lane < nblk) tma_load_2d(my_box + (size_t)st * b_stage_bytes, &tmB, lane * 64, brow, &st_full[st]);
-          if (++st == sb) {
-            st = 0;
-            ph ^= 1u;
-          }
-        }
-      }
       if (!ok) *s_fail = 1;
     }
-  } else if (warp == TCP_GROUPS * 4 + 5) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+  } else if (warp >= TCP_GROUPS * 4 + 5) {
+    // ---------------- MMA issuers ----------------
+    const int w = warp - (TCP_GROUPS * 4 + 5);
+    if (lane == 0 && w < issuers) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(n >> 3) << 17) |
                              ((uint32_t)(TC_M >> 4) << 24);
       bool ok = true;
-      int st = 0;
+      int st = w;               // ring stage and parity of this issuer's next chunk
       uint32_t ph = 0;
+      while (st >= sb) {
+        st -= sb;
+        ph ^= 1u;
+      }
+      uint32_t cnum0 = 0, mine = (uint32_t)w;  // running numbers: the block's first chunk, this issuer's next chunk
       // The issuing thread's instruction stream is the pipeline's clock: keep it short.  A stage's
       // descriptors differ from stage 0's only in the low word (the 14-bit address field), so the
       // loop adds small constants instead of rebuilding 64-bit descriptors.
@@ -638,17 +691,17 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       const uint32_t a_step = TC_A_BYTES >> 4, b_step = (uint32_t)b_stage_bytes >> 4;
       int nch_next = n_my > 0 ? chunk_cnt[first] : 0;
       for (int i = 0; i < n_my && ok; ++i) {
-        const int acc = i & 1;
+        const int acc = (i & 1) * issuers + w;
         const int nch = nch_next;  // fetched one block ahead: no global latency between blocks
         if (i + 1 < n_my) nch_next = chunk_cnt[first + (i + 1) * stride];
-        if (!mbar_wait(&acc_empty[acc], (uint32_t)(((i >> 1) & 1) ^ 1))) {
+        if (!mbar_wait(&acc_empty[i & 1], (uint32_t)(((i >> 1) & 1) ^ 1))) {
           ok = false;
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d = tmem + (uint32_t)acc * acc_cols;
-        uint32_t first_acc = 0u;  // the block's very first MMA overwrites the accumulator
-        for (int j = 0; j < nch; ++j) {
+        uint32_t first_acc = 0u;  // the issuer's first MMA of the block overwrites its accumulator
+        for (int j = (int)(mine - cnum0); j < nch; j += issuers, mine += (uint32_t)issuers) {
           if (!mbar_spin(&st_full[st], ph)) {
             ok = false;
             break;
@@ -663,26 +716,37 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
           umma_bf16_lohi(d, a_lo + 768u, a_hi, b_lo + 384u, b_hi, idesc, 1u);
           first_acc = 1u;
           umma_commit(&st_empty[st]);
-          if (++st == sb) {
-            st = 0;
+          st += issuers;
+          while (st >= sb) {
+            st -= sb;
             ph ^= 1u;
           }
         }
-        if (ok) umma_commit(&acc_full[acc]);
+        cnum0 += (uint32_t)nch;
+        if (ok) umma_commit(&acc_full[i & 1]);  // also with no chunk of its own: the barrier counts the issuers
       }
       if (!ok) *s_fail = 1;
     }
   } else if (warp < TCP_GROUPS * 4) {
-    // ---------------- builders: TCP_GROUPS groups, thread = row ----------------
+    // ---------------- builders: TCP_GROUPS groups of 128 threads ----------------
+    // Group g takes the chunks whose running number (over all row blocks of this CTA) is g modulo
+    // TCP_GROUPS.  Per chunk: wait for the ring stage, ask for the B slice (first warp), clear the
+    // tile (16 bytes x 8 per thread), meet the group's other warps at a named barrier, then each
+    // thread copies the chunk's entries t, t + 128, ... from the staged values to the tile element
+    // its scatter word names, and the warp arrives on the stage's full barrier.  A warp whose wait
+    // ran out keeps walking the loop without waiting or storing, so the barrier counts still match.
     bool ok = true;
-    const int grp = warp >> 2;    // builder group: takes the chunks whose running number is = grp (mod TCP_GROUPS)
-    const int row = tid & 127;
-    int sa = 0;                   // ring stage / parity of the running chunk number (all chunks, both groups)
+    const int grp = warp >> 2;
+    const int gt = tid & 127;
+    int sa = grp;                 // ring stage and parity of the group's next chunk
     uint32_t ph = 0;
-    uint32_t cnum = 0;
-    const int row_off = (row >> 3) * 128 + (row & 7) * 16;  // this row inside an 8-column core-matrix column
-    // per-block scalars are fetched one block ahead
-    int n_e0 = 0, n_e1 = 0, n_nch = 0, n_k = 0, n_kend = 0;
+    while (sa >= sb) {
+      sa -= sb;
+      ph ^= 1u;
+    }
+    uint32_t cnum0 = 0;           // running number of the block's first chunk
+    uint32_t mine = (uint32_t)grp;  // running number of the group's next chunk
+    int n_e0 = 0, n_e1 = 0, n_nch = 0;  // per-block scalars, fetched one block ahead
     auto fetch = [&](int i) {
       const int b = first + i * stride;
       const int64_t r0 = (int64_t)b * TC_M;
@@ -690,74 +754,56 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       n_e0 = rp[r0];
       n_e1 = rp[r0 + nr];
       n_nch = chunk_cnt[b];
-      n_k = n_kend = 0;
-      if (row < nr) {
-        n_k = rp[r0 + row];
-        n_kend = rp[r0 + row + 1];
-      }
     };
     if (n_my > 0) fetch(0);
-    for (int i = 0; i < n_my && ok; ++i) {
+    for (int i = 0; i < n_my; ++i) {
       const int cs = i % TCP_CSR;
       const int e0 = n_e0, e1 = n_e1, nch = n_nch;
-      int k = n_k;
-      const int k_end = n_kend;
       const int a0 = e0 & ~7;
       const bool staged = (e1 - a0) <= TC_CAP;
       if (i + 1 < n_my) fetch(i + 1);
-      if (!mbar_wait_backoff(&csr_full[cs], (uint32_t)((i / TCP_CSR) & 1))) {
-        ok = false;
-        break;
-      }
-      const int* __restrict__ pc = staged ? s_col + cs * (TC_CAP + 8) - a0 : col;
-      const __nv_bfloat16* __restrict__ pv = staged ? s_val + cs * (TC_CAP + 8) - a0 : val;
+      if (ok && !mbar_wait_backoff(&csr_full[cs], (uint32_t)((i / TCP_CSR) & 1))) ok = false;
+      const uint32_t* __restrict__ psc = staged ? s_sc + cs * (TC_CAP + 8) - a0 : scatter;  // by entry number
+      const __nv_bfloat16* __restrict__ pv = staged ? s_val + cs * (TC_CAP + 8) : val + a0;  // by offset in the slice
       const int* pch = s_chunks + cs * TC_MAXCH;
-      for (int j = 0; j < nch; ++j, ++cnum) {
-        if ((int)(cnum % TCP_GROUPS) == grp) {
-          if (!mbar_wait_backoff(&st_empty[sa], ph ^ 1u)) {
-            ok = false;
-            break;
+      const int* pent = s_ent + cs * TC_MAXCH;
+      for (int j = (int)(mine - cnum0); j < nch; j += TCP_GROUPS, mine += TCP_GROUPS) {
+        if (ok && !mbar_wait_backoff(&st_empty[sa], ph ^ 1u)) ok = false;
+        __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(sA + sa * TC_A_BYTES);
+        if (ok) {
+          if ((warp & 3) == 0) {
+            // the slice's latency runs under the build, and four groups issue side by side
+            if (lane == 0) mbar_expect_tx(&st_full[sa], (uint32_t)b_stage_bytes);
+            if (lane < nblk)
+              tma_load_2d(sB + (size_t)sa * b_stage_bytes + lane * 8192, &tmB, lane * 64, pch[j] * TC_KC,
+                          &st_full[sa]);
           }
-          // A serial thread pays 4-6 cycles per dependent instruction, so the chunk's work is kept
-          // short and wide: the row is re-zeroed with eight independent 16-byte stores (one per
-          // 8-column core matrix) and entries are handled four at a time without a dependency
-          // between them (columns ascend, so "below cend" is monotone within the four).
-          unsigned char* trow = sA + sa * TC_A_BYTES + row_off;
-          if (cnum >= (uint32_t)sb) {
+          if (mine >= (uint32_t)sb) {
 #pragma unroll
-            for (int q = 0; q < TC_KC / 8; ++q) *reinterpret_cast<uint4*>(trow + q * 2048) = make_uint4(0, 0, 0, 0);
+            for (int q = 0; q < TC_KC / 8; ++q)
+              *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(tile) + q * 2048 + gt * 16) =
+                  make_uint4(0, 0, 0, 0);
           }
-          const int cbeg = pch[j] * TC_KC, cend = cbeg + TC_KC;
-          bool more = k < k_end;
-          while (more) {
-            int c[4];
-            __nv_bfloat16 v[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int kk = k + q < k_end ? k + q : k_end - 1;
-              c[q] = pc[kk];
-              v[q] = pv[kk];
-            }
-            int used = 0;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const bool live = (k + q < k_end) && (c[q] < cend);  // entries below cbeg belong to the other group
-              const int x = c[q] - cbeg;
-              if (live && x >= 0) *reinterpret_cast<__nv_bfloat16*>(trow + (x >> 3) * 2048 + (x & 7) * 2) = v[q];
-              used += live ? 1 : 0;
-            }
-            k += used;
-            more = (used == 4) && (k < k_end);
+        }
+        asm volatile("bar.sync %0, 128;" ::"r"(grp + 1) : "memory");
+        if (ok) {
+          const int beg = pent[j];
+          const int end = j + 1 < nch ? pent[j + 1] : e1;
+          for (int t = beg + gt; t < end; t += 128) {
+            const uint32_t w = psc[t];
+            tile[w & ((1u << TC_SRC_SHIFT) - 1u)] = pv[w >> TC_SRC_SHIFT];
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
           if (lane == 0) mbar_arrive(&st_full[sa]);
         }
-        if (++sa == sb) {
-          sa = 0;
+        sa += TCP_GROUPS;
+        while (sa >= sb) {
+          sa -= sb;
           ph ^= 1u;
         }
       }
+      cnum0 += (uint32_t)nch;
       __syncwarp();
       if (ok && lane == 0) mbar_arrive(&csr_empty[cs]);
     }
@@ -767,6 +813,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
     bool ok = true;
     const int row = tid - TCP_GROUPS * 128;
     int nch_next = n_my > 0 ? chunk_cnt[first] : 0;
+    uint32_t cnum0 = 0;  // running number of the block's first chunk: tells which issuers had a chunk
     for (int i = 0; i < n_my && ok; ++i) {
       const int acc = i & 1;
       const int b = first + i * stride;
@@ -788,8 +835,17 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       for (int cb = 0; cb < n; cb += 32) {
         uint32_t a[32];
         if (nch > 0) {
-          tmem_ld32(tmem + ((uint32_t)wrow0 << 16) + (uint32_t)acc * acc_cols + (uint32_t)cb, a);
+          // the issuer of the block's first chunk always has data; the other one from two chunks on
+          const uint32_t w0 = issuers == 2 ? (cnum0 & 1u) : 0u;
+          tmem_ld32(tmem + ((uint32_t)wrow0 << 16) + ((uint32_t)(acc * issuers) + w0) * acc_cols + (uint32_t)cb, a);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (issuers == 2 && nch > 1) {
+            uint32_t a2[32];
+            tmem_ld32(tmem + ((uint32_t)wrow0 << 16) + ((uint32_t)(acc * issuers) + (w0 ^ 1u)) * acc_cols + (uint32_t)cb, a2);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int q = 0; q < 32; ++q) a[q] = __float_as_uint(__uint_as_float(a[q]) + __uint_as_float(a2[q]));
+          }
         } else {
 #pragma unroll
           for (int q = 0; q < 32; ++q) a[q] = 0u;
@@ -809,6 +865,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      cnum0 += (uint32_t)nch;
     }
     if (!ok) *s_fail = 1;
   }
@@ -820,7 +877,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
     __nanosleep(1000000);  // let copies and MMAs still in flight retire before the memory goes away
   }
   if (warp == TCP_GROUPS * 4 + 5)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2u * acc_cols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2u * (uint32_t)issuers * acc_cols) : "memory");
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -900,6 +957,34 @@ alphasparseStatus_t build_plan(alphasparseHandle_t h, alphasparseSpMatDescr_t A,
     impl(h)->launches++;
     e = cudaStreamSynchronize(st);
   }
+  // the scatter list: count per chunk, scan, fill
+  if (e == cudaSuccess && tp->usable && total_padded > 0 && A->nnz > 0) {
+    int32_t* ent_cnt = nullptr;
+    size_t sb_bytes = 0;
+    cub::DeviceScan::ExclusiveSum(nullptr, sb_bytes, ent_cnt, tp->chunk_ent, total_padded, st);
+    if (cudaMalloc(&ent_cnt, sizeof(int32_t) * (size_t)total_padded) != cudaSuccess ||
+        cudaMalloc(&tp->chunk_ent, sizeof(int32_t) * (size_t)total_padded) != cudaSuccess ||
+        cudaMalloc(&tp->scatter, sizeof(uint32_t) * (size_t)A->nnz) != cudaSuccess ||
+        (sb_bytes > tmp_bytes && (cudaFree(tmp), tmp = nullptr, tmp_bytes = sb_bytes,
+                                  cudaMalloc(&tmp, sb_bytes) != cudaSuccess))) {
+      cudaFree(ent_cnt);
+      cleanup();
+      return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    cudaMemsetAsync(ent_cnt, 0, sizeof(int32_t) * (size_t)total_padded, st);
+    tc_scatter_kernel<false><<<(unsigned)nb, 128, 0, st>>>(A->const_row_data, A->const_col_data, A->rows,
+                                                          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, ent_cnt,
+                                                          nullptr, nullptr, flags);
+    cub::DeviceScan::ExclusiveSum(tmp, sb_bytes, ent_cnt, tp->chunk_ent, total_padded, st);
+    tc_scatter_kernel<true><<<(unsigned)nb, 128, 0, st>>>(A->const_row_data, A->const_col_data, A->rows,
+                                                         tp->chunk_off, tp->chunk_cnt, tp->chunk_list, nullptr,
+                                                         tp->chunk_ent, tp->scatter, nullptr);
+    impl(h)->launches += 3;
+    e = cudaMemcpyAsync(hflags, flags, sizeof hflags, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(ent_cnt);
+    if (e == cudaSuccess && hflags[1]) tp->usable = false;  // a repeated column inside a row
+  }
   // the largest chunk count of a block decides whether chunk ids fit the persistent kernel's staging
   if (e == cudaSuccess && tp->usable) {
     size_t rb = 0;
@@ -924,6 +1009,8 @@ void free_spmm_tc_plan(void* p) {
   cudaFree(tp->chunk_off);
   cudaFree(tp->chunk_cnt);
   cudaFree(tp->chunk_list);
+  cudaFree(tp->chunk_ent);
+  cudaFree(tp->scatter);
   delete tp;
 }
 
@@ -972,14 +1059,14 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
     return ALPHA_SPARSE_STATUS_INVALID_VALUE;
 
   const size_t b_stage = (size_t)(n / 64) * 8192;
-  if (env_int("ASP_TC_PERSISTENT", 1) && tp->max_chunks <= TC_MAXCH) {
+  if (env_int("ASP_TC_PERSISTENT", 1) && tp->max_chunks <= TC_MAXCH && tp->scatter &&
+      p->max_block_nnz + 8 < (int64_t)(1u << (32 - TC_SRC_SHIFT))) {
     // one CTA per SM; whatever shared memory the fixed parts leave goes to B stages
-    const size_t fixed = TCP_CSR * (size_t)(TC_CAP + 8) * 6 + TCP_CSR * TC_MAXCH * 4 + 4 * 32 * 33 * 4 + 16 + 1024 + 1024;
+    const size_t fixed = TCP_CSR * (size_t)(TC_CAP + 8) * 6 + TCP_CSR * TC_MAXCH * 8 + 4 * 32 * 33 * 4 + 16 + 1024 + 1024;
     const size_t budget = impl(h)->smem_optin ? impl(h)->smem_optin : 232448;
     int sb = (int)((budget - fixed) / (b_stage + TC_A_BYTES));
     const int cap = env_int("ASP_TC_STAGES", 4);  // more stages measured no faster (1.17 ms at 5, 1.12 ms at 3)
     if (sb > cap) sb = cap;
-    sb -= sb % TCP_GROUPS;  // a ring stage always returns to the same builder group
     if (sb >= TCP_GROUPS) {
       const size_t smem = fixed + (size_t)sb * (b_stage + TC_A_BYTES);
       static size_t attr_p = 0;
@@ -992,7 +1079,7 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
       spmm_tc_persistent_kernel<<<(unsigned)g, TCP_THREADS, smem, h->stream>>>(
           tm, A->const_row_data, A->const_col_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
           reinterpret_cast<float*>(C->values), C->ld, alpha, beta, A->rows, A->nnz, n, (int)tp->blocks, sb,
-          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, p->dev_err);
+          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, tp->chunk_ent, tp->scatter, p->dev_err);
       impl(h)->launches++;
       return status_of(cudaGetLastError());
     }
