@@ -477,26 +477,33 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
 
 // ------------------------------------------------------------------------------------------
 // Persistent, warp-specialised form: one CTA per SM walks row blocks blockIdx.x, +gridDim.x, ...
-// and splits the work of spmm_tc_kernel over four roles that only meet through mbarriers, so the
-// copy engine runs many chunks (and one row block) ahead of the tensor core and the epilogue of a
-// row block overlaps the MMAs of the next one:
-//   warps 0-15 builders : four groups of 128 threads (thread = row of the block) take chunks in
-//                         turn; a group clears what it last wrote in the chunk's ring stage and
-//                         scatters its rows' entries of the chunk into the A tile
-//                                                                       (st_empty -> st_full)
-//   warps 16-19 epilogue: tcgen05.ld of one of two accumulators, alpha/beta, store C
+// and splits the work of spmm_tc_kernel over roles that only meet through mbarriers, so that a
+// row block's slices are staged a block ahead, several chunks are in flight at once and the
+// epilogue of a row block overlaps the MMAs of the next one:
+//   warps 0-15 builders : four groups of 128 threads take chunks in turn (running chunk number
+//                         modulo four).  Per chunk a group waits for the ring stage, asks for the
+//                         chunk's B slice by TMA, clears the A tile and fills it from the plan's
+//                         scatter list: thread t copies the chunk's entries t, t+128, ... from
+//                         the staged values to the tile elements the list names - no walk along
+//                         rows, no column compare                     (st_empty -> st_full)
+//   warps 16-19 epilogue: tcgen05.ld of the block's accumulators, alpha/beta, store C
 //                                                                       (acc_full -> acc_empty)
-//   warp 20    producer : bulk copies of the next block's CSR slice and chunk ids (csr_empty ->
-//                         csr_full), TMA of every chunk's B slice into the same ring of `sb`
-//                         stages                                        (st_empty -> st_full)
-//   warp 21    MMA      : waits st_full (tile built + slice landed), issues the chunk's four tcgen05.mma, commits
-//                         once to st_empty, and to acc_full after the block's last chunk;
-//                         owns the tensor-memory allocation (two accumulators)
+//   warp 20    producer : bulk copies of the next block's slice of the scatter list, of the
+//                         values, and of the block's chunk ids and chunk offsets
+//                                                                       (csr_empty -> csr_full)
+//   warps 21-22 MMA     : one thread each.  A thread's stream of wait / 4 x tcgen05.mma / commit
+//                         takes about 560 cycles per chunk however small N is, the tensor core
+//                         about 260 (N = 128), so two threads issue: even running chunk numbers
+//                         to one, odd to the other, each into its own accumulator (tensor memory
+//                         holds 2 blocks x 2 issuers x N columns when N <= 128; at N = 256 one
+//                         thread issues).  Commits to st_empty per chunk and to acc_full per
+//                         block; warp 21 owns the tensor-memory allocation
 // A barrier of the "empty" kind is waited on with the inverted parity, so its first use passes.
-// Every wait is bounded; a role whose wait expires raises the CTA's fail flag and leaves its loop,
-// the other roles then run into their own limits, and all meet at the final __syncthreads.
+// Every wait is bounded; a role whose wait expires raises the CTA's fail flag and stops working
+// (builders keep walking their loop so that the groups' named barriers still match), the other
+// roles then run into their own limits, and all meet at the final __syncthreads.
 // ------------------------------------------------------------------------------------------
-constexpr int TCP_GROUPS = 4;                 // builder groups of 128 threads; the ring depth is a multiple of it
+constexpr int TCP_GROUPS = 4;                 // builder groups of 128 threads
 constexpr int TCP_THREADS = (TCP_GROUPS * 4 + 7) * 32;  // builders, 4 epilogue warps, producer, 2 MMA warps
 constexpr int TCP_CSR = 3;  // row-block CSR buffers: staging block i+1 never waits for the builders of block i-1
 #ifndef ASP_TC_BACKOFF_NS
@@ -735,9 +742,14 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
     // thread copies the chunk's entries t, t + 128, ... from the staged values to the tile element
     // its scatter word names, and the warp arrives on the stage's full barrier.  A warp whose wait
     // ran out keeps walking the loop without waiting or storing, so the barrier counts still match.
+    // A wait by parity is only right for a waiter that sees every phase of its barrier, so a ring
+    // stage must always come back to the same group: min(sb, TCP_GROUPS) groups work, group g on
+    // the chunks g modulo that number (the host makes sb 2 or 4; with 2 two groups idle).
     bool ok = true;
     const int grp = warp >> 2;
     const int gt = tid & 127;
+    const int ng = sb < TCP_GROUPS ? sb : TCP_GROUPS;
+    const bool active = grp < ng;
     int sa = grp;                 // ring stage and parity of the group's next chunk
     uint32_t ph = 0;
     while (sa >= sb) {
@@ -767,7 +779,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       const __nv_bfloat16* __restrict__ pv = staged ? s_val + cs * (TC_CAP + 8) : val + a0;  // by offset in the slice
       const int* pch = s_chunks + cs * TC_MAXCH;
       const int* pent = s_ent + cs * TC_MAXCH;
-      for (int j = (int)(mine - cnum0); j < nch; j += TCP_GROUPS, mine += TCP_GROUPS) {
+      for (int j = active ? (int)(mine - cnum0) : nch; j < nch; j += ng, mine += (uint32_t)ng) {
         if (ok && !mbar_wait_backoff(&st_empty[sa], ph ^ 1u)) ok = false;
         __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(sA + sa * TC_A_BYTES);
         if (ok) {
@@ -797,7 +809,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
           __syncwarp();
           if (lane == 0) mbar_arrive(&st_full[sa]);
         }
-        sa += TCP_GROUPS;
+        sa += ng;
         while (sa >= sb) {
           sa -= sb;
           ph ^= 1u;
@@ -1065,9 +1077,12 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
     const size_t fixed = TCP_CSR * (size_t)(TC_CAP + 8) * 6 + TCP_CSR * TC_MAXCH * 8 + 4 * 32 * 33 * 4 + 16 + 1024 + 1024;
     const size_t budget = impl(h)->smem_optin ? impl(h)->smem_optin : 232448;
     int sb = (int)((budget - fixed) / (b_stage + TC_A_BYTES));
-    const int cap = env_int("ASP_TC_STAGES", 4);  // more stages measured no faster (1.17 ms at 5, 1.12 ms at 3)
+    // Ring depth 4 (what fits at N = 128) or 2 (N = 256): the kernel's waits by parity need a
+    // depth that divides the builder groups, and an even one for two MMA issuers.
+    int cap = env_int("ASP_TC_STAGES", 4);
     if (sb > cap) sb = cap;
-    if (sb >= TCP_GROUPS) {
+    sb = sb >= 4 ? 4 : (sb >= 2 ? 2 : 0);
+    if (sb >= 2) {
       const size_t smem = fixed + (size_t)sb * (b_stage + TC_A_BYTES);
       static size_t attr_p = 0;
       if (smem > attr_p) {
