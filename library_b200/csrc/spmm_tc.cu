@@ -31,7 +31,11 @@ namespace asp {
 namespace {
 
 constexpr int TC_M = 128;       // rows per CTA (the MMA's M)
-constexpr int TC_KC = 64;       // columns of A per chunk (four K=16 MMAs)
+#ifndef ASP_TC_KC
+#define ASP_TC_KC 64
+#endif
+constexpr int TC_KC = ASP_TC_KC; // columns of A per chunk (TC_KC / 16 MMAs of K = 16)
+constexpr int TC_BBLK = TC_KC * 128;  // bytes of a chunk's B slice per 64 columns of B (TC_KC rows of 128 bytes)
 constexpr int TC_THREADS = 128;
 constexpr int TC_SPAN_WORDS = 2048;  // bitmap words: a row block may span 65,536 chunks
 constexpr uint32_t TC_MAX_TRIES = 1u << 22;
@@ -216,6 +220,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -282,7 +293,7 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
   // the swizzled B boxes (and the descriptors' address arithmetic) need a 1,024-byte aligned base
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int nblk = n / 64;                      // 64-column boxes of B per chunk
-  const int b_stage_bytes = nblk * 8192;        // 64 rows x 128 B per box
+  const int b_stage_bytes = nblk * TC_BBLK;        // 64 rows x 128 B per box
   unsigned char* sA = smem;                     // 2 x 16 KB
   unsigned char* sB = smem + 2 * TC_A_BYTES;    // TC_BSTAGES x b_stage_bytes, 1,024-byte aligned
   int* s_col = reinterpret_cast<int*>(sB + TC_BSTAGES * b_stage_bytes);            // TC_CAP + 8
@@ -372,7 +383,7 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
     const int bs = jj % TC_BSTAGES;
     mbar_expect_tx(&full[bs], (uint32_t)b_stage_bytes);
     for (int i = 0; i < nblk; ++i)
-      tma_load_2d(sB + bs * b_stage_bytes + i * 8192, &tmB, i * 64, pch[jj] * TC_KC, &full[bs]);
+      tma_load_2d(sB + bs * b_stage_bytes + i * TC_BBLK, &tmB, i * 64, pch[jj] * TC_KC, &full[bs]);
   };
   if (tid == 0) {
     if (nchunks > 0) request_b(0);
@@ -419,7 +430,7 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
 #pragma unroll
         for (int kk = 0; kk < TC_KC / 16; ++kk) {
           const uint64_t ad = umma_desc(a_base + kk * 4096, 2048, 128, 0);   // no swizzle, K-major
-          const uint64_t bd = umma_desc(b_base + kk * 2048, 8192, 1024, 2);  // 128-byte swizzle, MN-major
+          const uint64_t bd = umma_desc(b_base + kk * 2048, TC_BBLK, 1024, 2);  // 128-byte swizzle, MN-major
           umma_bf16(tmem, ad, bd, idesc, (j > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&done[s]);
@@ -549,11 +560,11 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
                           int64_t nnz, int n, int nblocks, int sb,
                           const int32_t* __restrict__ chunk_off, const int32_t* __restrict__ chunk_cnt,
                           const int32_t* __restrict__ chunk_list, const int32_t* __restrict__ chunk_ent,
-                          const uint32_t* __restrict__ scatter, int* __restrict__ err) {
+                          const uint32_t* __restrict__ scatter, int one_box, int* __restrict__ err) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int nblk = n / 64;
-  const int b_stage_bytes = nblk * 8192;
+  const int b_stage_bytes = nblk * TC_BBLK;
   unsigned char* sA = smem;                               // sb x 16 KB (A tiles and B slices share one ring)
   unsigned char* sB = sA + (size_t)sb * TC_A_BYTES;       // sb x b_stage_bytes
   unsigned char* p = sB + (size_t)sb * b_stage_bytes;
@@ -692,7 +703,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       // descriptors differ from stage 0's only in the low word (the 14-bit address field), so the
       // loop adds small constants instead of rebuilding 64-bit descriptors.
       const uint64_t ad0 = umma_desc(smem_u32(sA), 2048, 128, 0);
-      const uint64_t bd0 = umma_desc(smem_u32(sB), 8192, 1024, 2);
+      const uint64_t bd0 = umma_desc(smem_u32(sB), TC_BBLK, 1024, 2);
       const uint32_t a_hi = (uint32_t)(ad0 >> 32), b_hi = (uint32_t)(bd0 >> 32);
       const uint32_t a_lo0 = (uint32_t)ad0, b_lo0 = (uint32_t)bd0;
       const uint32_t a_step = TC_A_BYTES >> 4, b_step = (uint32_t)b_stage_bytes >> 4;
@@ -718,9 +729,9 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
           // fence in this loop would make the issuing thread wait for the previous chunk's MMAs
           const uint32_t a_lo = a_lo0 + (uint32_t)st * a_step, b_lo = b_lo0 + (uint32_t)st * b_step;
           umma_bf16_lohi(d, a_lo, a_hi, b_lo, b_hi, idesc, first_acc);
-          umma_bf16_lohi(d, a_lo + 256u, a_hi, b_lo + 128u, b_hi, idesc, 1u);
-          umma_bf16_lohi(d, a_lo + 512u, a_hi, b_lo + 256u, b_hi, idesc, 1u);
-          umma_bf16_lohi(d, a_lo + 768u, a_hi, b_lo + 384u, b_hi, idesc, 1u);
+#pragma unroll
+          for (uint32_t kk = 1; kk < TC_KC / 16; ++kk)
+            umma_bf16_lohi(d, a_lo + kk * 256u, a_hi, b_lo + kk * 128u, b_hi, idesc, 1u);
           first_acc = 1u;
           umma_commit(&st_empty[st]);
           st += issuers;
@@ -780,15 +791,23 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       const int* pch = s_chunks + cs * TC_MAXCH;
       const int* pent = s_ent + cs * TC_MAXCH;
       for (int j = active ? (int)(mine - cnum0) : nch; j < nch; j += ng, mine += (uint32_t)ng) {
+        // the chunk's scalars come out of shared memory while the stage is still awaited
+        const int brow = pch[j] * TC_KC;
+        const int beg = pent[j];
+        const int end = j + 1 < nch ? pent[j + 1] : e1;
         if (ok && !mbar_wait_backoff(&st_empty[sa], ph ^ 1u)) ok = false;
         __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(sA + sa * TC_A_BYTES);
         if (ok) {
           if ((warp & 3) == 0) {
             // the slice's latency runs under the build, and four groups issue side by side
-            if (lane == 0) mbar_expect_tx(&st_full[sa], (uint32_t)b_stage_bytes);
-            if (lane < nblk)
-              tma_load_2d(sB + (size_t)sa * b_stage_bytes + lane * 8192, &tmB, lane * 64, pch[j] * TC_KC,
-                          &st_full[sa]);
+            // (one instruction for the whole slice when the map is the three-dimensional view
+            // [column block][row][64 columns]: issuing a copy costs the warp some 300 cycles)
+            if (lane == 0) {
+              mbar_expect_tx(&st_full[sa], (uint32_t)b_stage_bytes);
+              if (one_box) tma_load_3d(sB + (size_t)sa * b_stage_bytes, &tmB, 0, brow, 0, &st_full[sa]);
+            }
+            if (!one_box && lane < nblk)
+              tma_load_2d(sB + (size_t)sa * b_stage_bytes + lane * TC_BBLK, &tmB, lane * 64, brow, &st_full[sa]);
           }
           if (mine >= (uint32_t)sb) {
 #pragma unroll
@@ -799,11 +818,19 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
         }
         asm volatile("bar.sync %0, 128;" ::"r"(grp + 1) : "memory");
         if (ok) {
-          const int beg = pent[j];
-          const int end = j + 1 < nch ? pent[j + 1] : e1;
-          for (int t = beg + gt; t < end; t += 128) {
+          // two entries per thread side by side (a chunk of a stencil matrix has under 256), the
+          // rest in a loop: a lone thread's chain of dependent shared-memory accesses is what a
+          // build's time is made of
+          constexpr uint32_t kPos = (1u << TC_SRC_SHIFT) - 1u;
+          const int t0 = beg + gt, t1 = t0 + 128;
+          const uint32_t w0 = t0 < end ? psc[t0] : 0u;
+          const uint32_t w1 = t1 < end ? psc[t1] : 0u;
+          const __nv_bfloat16 v0 = pv[w0 >> TC_SRC_SHIFT], v1 = pv[w1 >> TC_SRC_SHIFT];
+          if (t0 < end) tile[w0 & kPos] = v0;
+          if (t1 < end) tile[w1 & kPos] = v1;
+          for (int t = t1 + 128; t < end; t += 128) {
             const uint32_t w = psc[t];
-            tile[w & ((1u << TC_SRC_SHIFT) - 1u)] = pv[w >> TC_SRC_SHIFT];
+            tile[w & kPos] = pv[w >> TC_SRC_SHIFT];
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
@@ -1070,18 +1097,19 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return ALPHA_SPARSE_STATUS_INVALID_VALUE;
 
-  const size_t b_stage = (size_t)(n / 64) * 8192;
+  const size_t b_stage = (size_t)(n / 64) * TC_BBLK;
   if (env_int("ASP_TC_PERSISTENT", 1) && tp->max_chunks <= TC_MAXCH && tp->scatter &&
       p->max_block_nnz + 8 < (int64_t)(1u << (32 - TC_SRC_SHIFT))) {
     // one CTA per SM; whatever shared memory the fixed parts leave goes to B stages
     const size_t fixed = TCP_CSR * (size_t)(TC_CAP + 8) * 6 + TCP_CSR * TC_MAXCH * 8 + 4 * 32 * 33 * 4 + 16 + 1024 + 1024;
     const size_t budget = impl(h)->smem_optin ? impl(h)->smem_optin : 232448;
     int sb = (int)((budget - fixed) / (b_stage + TC_A_BYTES));
-    // Ring depth 4 (what fits at N = 128) or 2 (N = 256): the kernel's waits by parity need a
-    // depth that divides the builder groups, and an even one for two MMA issuers.
-    int cap = env_int("ASP_TC_STAGES", 4);
+    // Ring depth 8, 4 (what fits at N = 128) or 2 (N = 256): the kernel's waits by parity need a
+    // stage to come back to the same builder group (depth a multiple or a divisor of the number of
+    // groups) and, for two MMA issuers, an even depth.
+    int cap = env_int("ASP_TC_STAGES", 8);
     if (sb > cap) sb = cap;
-    sb = sb >= 4 ? 4 : (sb >= 2 ? 2 : 0);
+    sb = sb >= 8 ? 8 : (sb >= 4 ? 4 : (sb >= 2 ? 2 : 0));
     if (sb >= 2) {
       const size_t smem = fixed + (size_t)sb * (b_stage + TC_A_BYTES);
       static size_t attr_p = 0;
@@ -1091,10 +1119,21 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
       }
       int64_t g = impl(h)->sm_count;
       if (g > tp->blocks) g = tp->blocks;
+      // B as [column block of 64][row][64 columns]: one box {64, 64 rows, all column blocks} lands in
+      // shared memory as the column blocks' 8 KB tiles one after the other, what the MMA descriptor expects.
+      CUtensorMap tm3;
+      const cuuint64_t dims3[3] = {64, (cuuint64_t)B->rows, (cuuint64_t)(n / 64)};
+      const cuuint64_t strides3[2] = {(cuuint64_t)B->ld * 2, 128};
+      const cuuint32_t box3[3] = {64, (cuuint32_t)TC_KC, (cuuint32_t)(n / 64)};
+      const cuuint32_t estr3[3] = {1, 1, 1};
+      const int one_box = env_int("ASP_TC_ONE_BOX", 1) && n > 64 &&
+                          enc(&tm3, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, B->values, dims3, strides3, box3, estr3,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
       spmm_tc_persistent_kernel<<<(unsigned)g, TCP_THREADS, smem, h->stream>>>(
-          tm, A->const_row_data, A->const_col_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
+          one_box ? tm3 : tm, A->const_row_data, A->const_col_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
           reinterpret_cast<float*>(C->values), C->ld, alpha, beta, A->rows, A->nnz, n, (int)tp->blocks, sb,
-          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, tp->chunk_ent, tp->scatter, p->dev_err);
+          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, tp->chunk_ent, tp->scatter, one_box, p->dev_err);
       impl(h)->launches++;
       return status_of(cudaGetLastError());
     }
