@@ -514,8 +514,15 @@ spmm_tc_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t* __restric
 // (builders keep walking their loop so that the groups' named barriers still match), the other
 // roles then run into their own limits, and all meet at the final __syncthreads.
 // ------------------------------------------------------------------------------------------
-constexpr int TCP_GROUPS = 4;                 // builder groups of 128 threads
-constexpr int TCP_THREADS = (TCP_GROUPS * 4 + 7) * 32;  // builders, 4 epilogue warps, producer, 2 MMA warps
+#ifndef ASP_TCP_GROUPS
+#define ASP_TCP_GROUPS 4
+#endif
+constexpr int TCP_BWARPS = 16;                        // builder warps
+constexpr int TCP_GROUPS = ASP_TCP_GROUPS;            // builder groups (4 of four warps, or 8 of two)
+constexpr int TCP_GWARPS = TCP_BWARPS / TCP_GROUPS;   // warps of a group
+constexpr int TCP_GTHREADS = TCP_GWARPS * 32;
+constexpr int TCP_THREADS = (TCP_BWARPS + 7) * 32;    // builders, 4 epilogue warps, producer, 2 MMA warps
+static_assert(TCP_GROUPS * TCP_GWARPS == TCP_BWARPS && TC_M % TCP_GTHREADS == 0, "builder groups");
 constexpr int TCP_CSR = 3;  // row-block CSR buffers: staging block i+1 never waits for the builders of block i-1
 #ifndef ASP_TC_BACKOFF_NS
 #define ASP_TC_BACKOFF_NS 64
@@ -596,20 +603,20 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
   if (tid == 0) {
     for (int i = 0; i < TCP_CSR; ++i) {
       mbar_init(&csr_full[i], 1);
-      mbar_init(&csr_empty[i], TCP_GROUPS * 4);   // one arrival per builder warp
+      mbar_init(&csr_empty[i], TCP_BWARPS);   // one arrival per builder warp
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], (uint32_t)issuers);
       mbar_init(&acc_empty[i], 4);
     }
     for (int i = 0; i < sb; ++i) {
-      mbar_init(&st_full[i], 5);
+      mbar_init(&st_full[i], TCP_GWARPS + 1);   // the group's warps and the thread that announces the B slice's bytes
       mbar_init(&st_empty[i], 1);
     }
     *s_fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == TCP_GROUPS * 4 + 5) {
+  if (warp == TCP_BWARPS + 5) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
                  "r"(2u * (uint32_t)issuers * acc_cols)
                  : "memory");
@@ -623,7 +630,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
   const int first = blockIdx.x, stride = gridDim.x;
   const int n_my = first < nblocks ? (nblocks - first + stride - 1) / stride : 0;
 
-  if (warp == TCP_GROUPS * 4 + 4) {
+  if (warp == TCP_BWARPS + 4) {
     // ---------------- producer ----------------
     // The whole warp runs the loop (waits are warp-uniform): lane 0 stages the CSR slices and arms
     // the barriers, lanes 0..nblk-1 each issue one 64-column box of a chunk's B slice.  The scalars
@@ -685,9 +692,9 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
         if (i + 1 < n_my) ok = stage_csr(i + 1);
       if (!ok) *s_fail = 1;
     }
-  } else if (warp >= TCP_GROUPS * 4 + 5) {
+  } else if (warp >= TCP_BWARPS + 5) {
     // ---------------- MMA issuers ----------------
-    const int w = warp - (TCP_GROUPS * 4 + 5);
+    const int w = warp - (TCP_BWARPS + 5);
     if (lane == 0 && w < issuers) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(n >> 3) << 17) |
                              ((uint32_t)(TC_M >> 4) << 24);
@@ -745,7 +752,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       }
       if (!ok) *s_fail = 1;
     }
-  } else if (warp < TCP_GROUPS * 4) {
+  } else if (warp < TCP_BWARPS) {
     // ---------------- builders: TCP_GROUPS groups of 128 threads ----------------
     // Group g takes the chunks whose running number (over all row blocks of this CTA) is g modulo
     // TCP_GROUPS.  Per chunk: wait for the ring stage, ask for the B slice (first warp), clear the
@@ -757,8 +764,8 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
     // stage must always come back to the same group: min(sb, TCP_GROUPS) groups work, group g on
     // the chunks g modulo that number (the host makes sb 2 or 4; with 2 two groups idle).
     bool ok = true;
-    const int grp = warp >> 2;
-    const int gt = tid & 127;
+    const int grp = warp / TCP_GWARPS;
+    const int gt = tid % TCP_GTHREADS;
     const int ng = sb < TCP_GROUPS ? sb : TCP_GROUPS;
     const bool active = grp < ng;
     int sa = grp;                 // ring stage and parity of the group's next chunk
@@ -798,7 +805,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
         if (ok && !mbar_wait_backoff(&st_empty[sa], ph ^ 1u)) ok = false;
         __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(sA + sa * TC_A_BYTES);
         if (ok) {
-          if ((warp & 3) == 0) {
+          if (warp % TCP_GWARPS == 0) {
             // the slice's latency runs under the build, and four groups issue side by side
             // (one instruction for the whole slice when the map is the three-dimensional view
             // [column block][row][64 columns]: issuing a copy costs the warp some 300 cycles)
@@ -812,23 +819,25 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
           if (mine >= (uint32_t)sb) {
 #pragma unroll
             for (int q = 0; q < TC_KC / 8; ++q)
-              *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(tile) + q * 2048 + gt * 16) =
-                  make_uint4(0, 0, 0, 0);
+#pragma unroll
+              for (int r = gt; r < TC_M; r += TCP_GTHREADS)
+                *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(tile) + q * 2048 + r * 16) =
+                    make_uint4(0, 0, 0, 0);
           }
         }
-        asm volatile("bar.sync %0, 128;" ::"r"(grp + 1) : "memory");
+        asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "n"(TCP_GTHREADS) : "memory");
         if (ok) {
           // two entries per thread side by side (a chunk of a stencil matrix has under 256), the
           // rest in a loop: a lone thread's chain of dependent shared-memory accesses is what a
           // build's time is made of
           constexpr uint32_t kPos = (1u << TC_SRC_SHIFT) - 1u;
-          const int t0 = beg + gt, t1 = t0 + 128;
+          const int t0 = beg + gt, t1 = t0 + TCP_GTHREADS;
           const uint32_t w0 = t0 < end ? psc[t0] : 0u;
           const uint32_t w1 = t1 < end ? psc[t1] : 0u;
           const __nv_bfloat16 v0 = pv[w0 >> TC_SRC_SHIFT], v1 = pv[w1 >> TC_SRC_SHIFT];
           if (t0 < end) tile[w0 & kPos] = v0;
           if (t1 < end) tile[w1 & kPos] = v1;
-          for (int t = t1 + 128; t < end; t += 128) {
+          for (int t = t1 + TCP_GTHREADS; t < end; t += TCP_GTHREADS) {
             const uint32_t w = psc[t];
             tile[w & kPos] = pv[w >> TC_SRC_SHIFT];
           }
@@ -850,7 +859,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
   } else {
     // ---------------- epilogue: four warps (ids = 0..3 mod 4) read tensor-memory lanes 32*(id mod 4) .. ----------------
     bool ok = true;
-    const int row = tid - TCP_GROUPS * 128;
+    const int row = tid - TCP_BWARPS * 32;
     int nch_next = n_my > 0 ? chunk_cnt[first] : 0;
     uint32_t cnum0 = 0;  // running number of the block's first chunk: tells which issuers had a chunk
     for (int i = 0; i < n_my && ok; ++i) {
@@ -868,8 +877,8 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
       // tcgen05.ld hands lane l the 32 columns of row l; a per-warp 32 x 33 shared-memory tile turns
       // that around so that a store instruction writes 32 consecutive floats of one row (one line)
       // instead of 16 bytes of 32 different rows.
-      float* tr = s_tr + (warp - TCP_GROUPS * 4) * (32 * 33);
-      const int wrow0 = (warp - TCP_GROUPS * 4) * 32;
+      float* tr = s_tr + (warp - TCP_BWARPS) * (32 * 33);
+      const int wrow0 = (warp - TCP_BWARPS) * 32;
       (void)row;
       for (int cb = 0; cb < n; cb += 32) {
         uint32_t a[32];
@@ -915,7 +924,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
     if (tid == 0) atomicExch(err, 1);
     __nanosleep(1000000);  // let copies and MMAs still in flight retire before the memory goes away
   }
-  if (warp == TCP_GROUPS * 4 + 5)
+  if (warp == TCP_BWARPS + 5)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2u * (uint32_t)issuers * acc_cols) : "memory");
 }
 
