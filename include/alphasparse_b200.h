@@ -100,7 +100,8 @@ typedef enum { /* spdef.h:310-314 */
 /* spdef.h:345-365.  How this library maps them: DEFAULT picks from the analysed row-length
  * statistics; SCALAR / VECTOR / ADAPTIVE / CSR_ADAPTIVE / LINE* select the row-length-binned
  * kernel; MERGE / ROW_PARTITION / LOAD_BALANCE / FLAT* / CSR_STREAM select the merge-path
- * kernel.  COO and ELL are other formats' algorithms and are rejected for CSR. */
+ * kernel.  COO and ELL name other formats' algorithms; for a CSR matrix they are taken as DEFAULT
+ * (the reference's own CSR test drivers pass ALG_COO, and its dispatcher then does nothing). */
 typedef enum {
   ALPHA_SPARSE_SPMV_ALG_DEFAULT = 0,
   ALPHA_SPARSE_SPMV_ALG_COO = 1,
@@ -126,7 +127,7 @@ typedef enum {
 /* spdef.h:390-402.  DEFAULT picks per (N, row statistics); CSR_ALG1..5 select the SIMT
  * row-block kernel; CSR_ALG6 (the matrix-unit algorithm of the HIP backend,
  * hip/kernel/level3/alphasparse_spmm_tc4csr.h:228-255) selects the tcgen05 kernel and needs
- * bf16 A and X with fp32 Y.  COO algorithms are rejected for CSR. */
+ * bf16 A and X with fp32 Y.  COO algorithms are taken as DEFAULT for a CSR matrix. */
 typedef enum {
   ALPHASPARSE_SPMM_ALG_DEFAULT = 0,
   ALPHASPARSE_SPMM_COO_ALG1 = 1,
