@@ -38,6 +38,8 @@ WORKLOADS = {
     "spmm_s27_128_f32_n8": "CSR SpMM fp32, 27-point stencil 128^3, N=8",
     "spmm_s27_128_f32_n32": "CSR SpMM fp32, 27-point stencil 128^3, N=32",
     "spmm_s27_128_f32_n128": "CSR SpMM fp32, 27-point stencil 128^3, N=128",
+    "spmv_lap3d_f16_i64": "CSR SpMV fp16 A and x / fp32 y and arithmetic, 7-point Laplacian 512^3, int64 row offsets",
+    "spmv_poisson16_bf16": "CSR SpMV bf16 A, x and y / fp32 arithmetic, Poisson(16) row lengths, 4,194,304 rows, alpha=1.5 beta=0.5",
     "spmm_s27_128_bf16_n64": "CSR SpMM bf16 operands / fp32 accumulate (tcgen05), 27-point stencil 128^3, N=64",
     "spmm_s27_128_bf16_n128": "CSR SpMM bf16 operands / fp32 accumulate (tcgen05), 27-point stencil 128^3, N=128",
     "spmm_s27_128_bf16_n256": "CSR SpMM bf16 operands / fp32 accumulate (tcgen05), 27-point stencil 128^3, N=256",
@@ -104,6 +106,16 @@ def make_workload(name, device, rank, scale):
         n = max(16, int(round(512 * scale ** (1.0 / 3.0))))
         A = G.laplacian_3d_7pt(n, dtype=torch.float64, device=device, index64=True)
         return dict(A=A, kind="spmv", n=1, alpha=1.0, beta=0.0, lo=-1.0, dtype=torch.float64)
+    if name == "spmv_lap3d_f16_i64":
+        n = max(16, int(round(512 * scale ** (1.0 / 3.0))))
+        A = G.laplacian_3d_7pt(n, dtype=torch.float32, device=device, index64=True)
+        A.val = A.val.to(torch.float16)
+        return dict(A=A, kind="spmv", n=1, alpha=1.0, beta=0.0, lo=-1.0, dtype=torch.float16, ydtype=torch.float32)
+    if name == "spmv_poisson16_bf16":
+        rows = max(1024, int(4194304 * scale))
+        A = G.poisson_random(rows, rows, 16.0, dtype=torch.float32, device=device, seed=2 + seed)
+        A.val = A.val.to(torch.bfloat16)
+        return dict(A=A, kind="spmv", n=1, alpha=1.5, beta=0.5, lo=-1.0, dtype=torch.bfloat16, ydtype=torch.bfloat16)
     if name.startswith("spmm_s27_128"):
         n = int(name.rsplit("_n", 1)[1])
         g = max(8, int(round(128 * scale ** (1.0 / 3.0))))
@@ -122,6 +134,9 @@ def algorithmic_bytes(w):
     vb = A.val.element_size()
     ob = A.row_ptr.element_size()
     if w["kind"] == "spmv":
+        if "ydtype" in w:  # 16-bit operands: x in the matrix type, y in its own
+            yb = 4 if w["ydtype"] == __import__("torch").float32 else 2
+            return A.nnz * (vb + 4) + (A.rows + 1) * ob + A.cols * vb + A.rows * yb * (2 if w["beta"] != 0 else 1)
         return G.spmv_bytes(A.rows, A.cols, A.nnz, vb, ob, w["beta"] != 0)
     yb = 4 if vb == 2 else vb
     return G.spmm_bytes(A.rows, A.cols, A.nnz, w["n"], vb, ob, vb, yb, w["beta"] != 0)
@@ -228,8 +243,8 @@ def cpu_reference_time(w, repeats, threads):
     from library_b200 import generators as G
     A = w["A"]
     rp, ci = A.row_ptr.cpu().numpy(), A.col_idx.cpu().numpy()
-    ddt = torch.float32 if w["dtype"] == torch.bfloat16 else w["dtype"]
-    v = A.val.to(ddt).cpu().numpy()   # bf16 operands are timed as the fp32 CPU kernel
+    ddt = torch.float32 if w["dtype"] in (torch.bfloat16, torch.float16) else w["dtype"]
+    v = A.val.to(ddt).cpu().numpy()   # 16-bit operands are timed as the fp32 CPU kernel (the CPU path has no 16-bit types)
     kind = "reference" if (oracle.have_ref() and rp.dtype == np.int32) else "port"
     if w["kind"] == "spmv":
         x = G.uniform((A.cols,), w["lo"], 1.0, dtype=ddt, seed=11).numpy()
@@ -331,7 +346,7 @@ def run_ours(args):
     A = w["A"]
     nbytes = algorithmic_bytes(w)
     Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr, A.col_idx, A.val)
-    ydt = torch.float32 if w["dtype"] == torch.bfloat16 else w["dtype"]
+    ydt = w.get("ydtype", torch.float32 if w["dtype"] == torch.bfloat16 else w["dtype"])
 
     # x lives on rank 0 and is replicated over NVLink once: it is constant across the repeats
     if w["kind"] == "spmv":
@@ -523,7 +538,7 @@ def run_ours(args):
             "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak",
             "vs_baseline": None,
-            "dtype": {torch.float32: "f32", torch.float64: "f64", torch.bfloat16: "bf16"}[w["dtype"]],
+            "dtype": {torch.float32: "f32", torch.float64: "f64", torch.bfloat16: "bf16", torch.float16: "f16"}[w["dtype"]],
             "data": "synthetic", "gflops": total_flops / (ms_step * 1e-3) / 1e9,
             "frac_of_nominal_8TBs": value / world / 8000.0,
             "config": {"workload": args.workload, "description": WORKLOADS[args.workload],

@@ -242,7 +242,11 @@ alphasparseStatus_t alphasparseDnVecSetValues(alphasparseDnVecDescr_t descr, voi
 alphasparseStatus_t alphasparseDnMatSetValues(alphasparseDnMatDescr_t descr, void* values);
 
 /* ---- SpMV: y = alpha*op(A)*x + beta*y ----------------------------------------------- */
-/* spapi.h:6895-6905; cuda/kernel/level2/alphasparse_spmv.cu:221-339 */
+/* spapi.h:6895-6905; cuda/kernel/level2/alphasparse_spmv.cu:221-339.  Type combinations
+ * (A and x / y / computeType, alpha and beta host pointers of the compute type):
+ *   R_32F / R_32F / R_32F  (:234)      R_64F / R_64F / R_64F  (:240)
+ *   R_16F / R_32F / R_32F  (:288-292)  R_16BF / R_16BF / R_32F (:294-300)
+ * with 32- or 64-bit row offsets.  The reference's complex and int8 instances are not provided. */
 alphasparseStatus_t alphasparseSpMV(alphasparseHandle_t handle, alphasparseOperation_t opA,
                                     const void* alpha, alphasparseSpMatDescr_t matA,
                                     alphasparseDnVecDescr_t vecX, const void* beta,

@@ -84,6 +84,11 @@ def _dtype_code(dt: torch.dtype) -> int:
             torch.float16: R_16F}[dt]
 
 
+def _spmv_compute_code(dt: torch.dtype) -> int:
+    """16-bit matrices are multiplied in fp32 (alpha and beta are floats then)."""
+    return R_32F if dt in (torch.float16, torch.bfloat16) else _dtype_code(dt)
+
+
 def _scalar(value, code):
     return C.c_double(value) if code == R_64F else C.c_float(value)
 
@@ -210,7 +215,7 @@ class CsrMatrix:
 
 def spmv_buffer_size(handle: Handle, A: CsrMatrix, x: DnVec, y: DnVec, alpha=1.0, beta=0.0,
                      alg=SPMV_ALG_DEFAULT) -> int:
-    code = _dtype_code(A.val.dtype)
+    code = _spmv_compute_code(A.val.dtype)
     a, b = _scalar(alpha, code), _scalar(beta, code)
     size = C.c_size_t(0)
     _check(load().alphasparseSpMV_bufferSize(handle.h, OP_N, C.byref(a), A.d, x.d, C.byref(b), y.d,
@@ -221,7 +226,7 @@ def spmv_buffer_size(handle: Handle, A: CsrMatrix, x: DnVec, y: DnVec, alpha=1.0
 def spmv(handle: Handle, A: CsrMatrix, x: DnVec, y: DnVec, alpha=1.0, beta=0.0,
          alg=SPMV_ALG_DEFAULT, buffer: torch.Tensor | None = None, op=OP_N):
     """y = alpha*A*x + beta*y on handle's stream (asynchronous)."""
-    code = _dtype_code(A.val.dtype)
+    code = _spmv_compute_code(A.val.dtype)
     a, b = _scalar(alpha, code), _scalar(beta, code)
     buf = C.c_void_p(buffer.data_ptr()) if buffer is not None else C.c_void_p()
     _check(load().alphasparseSpMV(handle.h, op, C.byref(a), A.d, x.d, C.byref(b), y.d, code, alg, buf),

@@ -109,4 +109,10 @@ alphasparseStatus_t validate_csr(alphasparseSpMatDescr_t A);
 // spmm_tc.cu
 void free_spmm_tc_plan(void* p);
 
+// spmv_lowp.cu: 16-bit A and x with fp32 arithmetic (fp16 -> fp32 y, bf16 -> bf16 y)
+bool spmv_lowp_types(alphasparseDataType a, alphasparseDataType x, alphasparseDataType y,
+                     alphasparseDataType compute);
+alphasparseStatus_t spmv_lowp_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A, const Plan* p,
+                                  const void* x, void* y, float alpha, float beta);
+
 }  // namespace asp

@@ -12,6 +12,9 @@
 //   - no atomics on y: a row is summed by one lane group, warp or CTA, and the merge-path
 //     kernel passes partial sums of rows that straddle CTAs through a carry array that a
 //     second small kernel adds in tile order, so results are reproducible run to run.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include <climits>
 #include <cstring>
 #include <mutex>
@@ -217,6 +220,9 @@ constexpr int kMergeShortSeg = 64;
 #define ASP_TILE_MIN_CTAS 6
 #endif
 constexpr int kTileMinCtas = ASP_TILE_MIN_CTAS;
+#ifndef ASP_TILE_MIN_CTAS_LOWP
+#define ASP_TILE_MIN_CTAS_LOWP 8   // 16-bit values: a tile is 12 KB, more tiles in flight per SM
+#endif
 #ifndef ASP_TILE_SHORT_SEG
 #define ASP_TILE_SHORT_SEG 32
 #endif
@@ -432,19 +438,37 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
       : "memory");
 }
 
-constexpr int kTileSlot = kMergeItems + 8;     // entries per staged array (widening adds < 8)
+constexpr int kTileSlot = kMergeItems + 16;    // entries per staged array (widening adds < 16)
 constexpr int kTileShortSeg = ASP_TILE_SHORT_SEG;
 constexpr uint32_t kTileMaxTries = 1u << 22;
 
-template <typename T, typename OffT>
-__global__ void __launch_bounds__(kThreads, kTileMinCtas)
-spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const T* __restrict__ val,
-                 const T* __restrict__ x, T* __restrict__ y, T alpha, T beta, int64_t rows,
+// Storage <-> arithmetic conversions of the mixed-precision instances (TA = __half or __nv_bfloat16
+// for A and x, arithmetic in T = float); identity for the fp32 / fp64 instances.
+template <typename T> __device__ __forceinline__ T widen(T v) { return v; }
+__device__ __forceinline__ float widen(__half v) { return __half2float(v); }
+__device__ __forceinline__ float widen(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename TY, typename T> __device__ __forceinline__ TY narrow(T v) { return (TY)v; }
+template <> __device__ __forceinline__ __half narrow<__half, float>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 narrow<__nv_bfloat16, float>(float v) { return __float2bfloat16_rn(v); }
+template <typename T, typename TY>
+__device__ __forceinline__ TY finish_as(T alpha, T sum, T beta, const TY* y) {
+  return narrow<TY, T>(beta == T(0) ? alpha * sum : fma(alpha, sum, beta * widen(*y)));
+}
+
+// T: arithmetic type (and the carries'), TA: type of A's values and of x, TY: type of y.
+template <typename T, typename OffT, typename TA = T, typename TY = T>
+__global__ void __launch_bounds__(kThreads, (sizeof(TA) < 4 ? ASP_TILE_MIN_CTAS_LOWP : kTileMinCtas))
+spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const TA* __restrict__ val,
+                 const TA* __restrict__ x, TY* __restrict__ y, T alpha, T beta, int64_t rows,
                  int64_t nnz, const int32_t* __restrict__ tile_row, T* __restrict__ carry,
                  int* __restrict__ err) {
   constexpr int ITEMS = kMergeItems;
   constexpr int IPT = kMergeIpt;
-  __shared__ __align__(128) T s_val[kTileSlot];
+  constexpr bool kSame = std::is_same<TA, T>::value;
+  // a bulk copy moves whole 16-byte units of both arrays: groups of GA entries
+  constexpr int GA = sizeof(TA) >= 4 ? 4 : 16 / (int)sizeof(TA);
+  static_assert(kSame || sizeof(T) == sizeof(int), "mixed precision parks fp32 products in the column slots");
+  __shared__ __align__(128) TA s_val[kTileSlot];
   __shared__ __align__(128) int s_col[kTileSlot];
   __shared__ __align__(8) unsigned char s_flags[ITEMS];  // 1 where an item of the merge list is a row end
   __shared__ __align__(8) uint64_t s_bar;
@@ -462,23 +486,23 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   const int64_t nz_s = diag_s - row_s, nz_e = diag_e - row_e;
   const int tile_rows = row_e - row_s;
   const int tile_nnz = (int)(nz_e - nz_s);
-  const int64_t a0 = nz_s & ~(int64_t)3;
+  const int64_t a0 = nz_s & ~(int64_t)(GA - 1);
   const int lo = (int)(nz_s - a0);
 
   if (tid == 0) {
     mbar_init(&s_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    const int64_t nnz4 = nnz & ~(int64_t)3;
-    int64_t a1 = (nz_e + 3) & ~(int64_t)3;
+    const int64_t nnz4 = nnz & ~(int64_t)(GA - 1);
+    int64_t a1 = (nz_e + (GA - 1)) & ~(int64_t)(GA - 1);
     if (a1 > nnz4) a1 = nnz4;
     if (a1 < a0) a1 = a0;
     const uint32_t cnt = (uint32_t)(a1 - a0);
-    mbar_expect_tx(&s_bar, cnt * (uint32_t)(sizeof(T) + sizeof(int)));
+    mbar_expect_tx(&s_bar, cnt * (uint32_t)(sizeof(TA) + sizeof(int)));
     if (cnt) {
-      bulk_g2s(s_val, val + a0, cnt * (uint32_t)sizeof(T), &s_bar);
+      bulk_g2s(s_val, val + a0, cnt * (uint32_t)sizeof(TA), &s_bar);
       bulk_g2s(s_col, col + a0, cnt * (uint32_t)sizeof(int), &s_bar);
     }
-    for (int64_t e = a1 > nz_s ? a1 : nz_s; e < nz_e; ++e) {  // past the last full group of four
+    for (int64_t e = a1 > nz_s ? a1 : nz_s; e < nz_e; ++e) {  // past the last full group of entries
       s_val[e - a0] = val[e];
       s_col[e - a0] = col[e];
     }
@@ -513,7 +537,7 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
     __nanosleep(1000000);  // let a copy still in flight land before the CTA's memory is released
     return;
   }
-  const T* sv = s_val + lo;
+  const TA* sv = s_val + lo;
   const int* sc = s_col + lo;
 
   if (!(vote & 1)) {
@@ -531,22 +555,23 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
       int k = b;
       for (; k + 4 <= e; k += 4) {
         const int c0 = sc[k], c1 = sc[k + 1], c2 = sc[k + 2], c3 = sc[k + 3];
-        const T x0 = __ldg(x + c0), x1 = __ldg(x + c1), x2 = __ldg(x + c2), x3 = __ldg(x + c3);
-        sum = fma(sv[k], x0, sum);
-        sum = fma(sv[k + 1], x1, sum);
-        sum = fma(sv[k + 2], x2, sum);
-        sum = fma(sv[k + 3], x3, sum);
+        const T x0 = widen(__ldg(x + c0)), x1 = widen(__ldg(x + c1)), x2 = widen(__ldg(x + c2)),
+                x3 = widen(__ldg(x + c3));
+        sum = fma(widen(sv[k]), x0, sum);
+        sum = fma(widen(sv[k + 1]), x1, sum);
+        sum = fma(widen(sv[k + 2]), x2, sum);
+        sum = fma(widen(sv[k + 3]), x3, sum);
       }
       if (k < e) {
         const int c0 = sc[k];
         const int c1 = k + 1 < e ? sc[k + 1] : c0;
         const int c2 = k + 2 < e ? sc[k + 2] : c0;
-        const T x0 = __ldg(x + c0), x1 = __ldg(x + c1), x2 = __ldg(x + c2);
-        sum = fma(sv[k], x0, sum);
-        if (k + 1 < e) sum = fma(sv[k + 1], x1, sum);
-        if (k + 2 < e) sum = fma(sv[k + 2], x2, sum);
+        const T x0 = widen(__ldg(x + c0)), x1 = widen(__ldg(x + c1)), x2 = widen(__ldg(x + c2));
+        sum = fma(widen(sv[k]), x0, sum);
+        if (k + 1 < e) sum = fma(widen(sv[k + 1]), x1, sum);
+        if (k + 2 < e) sum = fma(widen(sv[k + 2]), x2, sum);
       }
-      if (i < tile_rows) y[row_s + i] = finish(alpha, sum, beta, y + row_s + i);
+      if (i < tile_rows) y[row_s + i] = finish_as(alpha, sum, beta, y + row_s + i);
       else carry[t] = sum;
     }
     return;
@@ -556,11 +581,14 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   // merge list, so the rows mark their end items in a byte map and a thread learns from its eight
   // bytes which of its items are row ends; the number of row ends before its first item (a block
   // scan of the byte counts) is the row it starts in.  No search, no per-item offset reads.
-  T* sp = s_val + lo;
+  // (with 16-bit values the fp32 product goes into the entry's column slot, which is dead after the gather)
+  T* sp;
+  if constexpr (kSame) sp = s_val + lo;
+  else sp = reinterpret_cast<T*>(s_col) + lo;
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
     const int e = i * kThreads + tid;
-    if (e < tile_nnz) sp[e] = sp[e] * __ldg(x + sc[e]);
+    if (e < tile_nnz) sp[e] = widen(sv[e]) * widen(__ldg(x + sc[e]));
   }
   *reinterpret_cast<uint2*>(s_flags + IPT * tid) = make_uint2(0u, 0u);
   __syncthreads();
@@ -598,7 +626,7 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
           first_row = i;
           first_val = running;
         } else {
-          y[row_s + i] = finish(alpha, running, beta, y + row_s + i);
+          y[row_s + i] = finish_as(alpha, running, beta, y + row_s + i);
         }
         running = T(0);
         ++i;
@@ -632,7 +660,7 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   const T carry_in = ef ? ev : pv + ev;
   if (first_row >= 0) {
     const int r = row_s + first_row;
-    y[r] = finish(alpha, carry_in + first_val, beta, y + r);
+    y[r] = finish_as(alpha, carry_in + first_val, beta, y + r);
   }
   if (tid == kThreads - 1) carry[t] = flag ? acc : pv + acc;
 }
@@ -640,11 +668,11 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
 // Adds the sums that left tiles to the rows they belong to.  Tile t's carry belongs to row
 // tile_row[t+1].  The thread of the first tile of a run of tiles that all end inside the same
 // row adds the whole run, in tile order.
-template <typename T>
+template <typename T, typename TY = T>
 __global__ void __launch_bounds__(256) spmv_merge_fixup_kernel(const int32_t* __restrict__ tile_row,
                                                                const T* __restrict__ carry,
                                                                int64_t tiles, int64_t rows,
-                                                               T* __restrict__ y, T alpha) {
+                                                               TY* __restrict__ y, T alpha) {
   const int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (t >= tiles) return;
   const int32_t r = tile_row[t + 1];
@@ -652,7 +680,7 @@ __global__ void __launch_bounds__(256) spmv_merge_fixup_kernel(const int32_t* __
   if (t > 0 && tile_row[t] == r) return;
   T sum = T(0);
   for (int64_t u = t; u < tiles && tile_row[u + 1] == r; ++u) sum += carry[u];
-  y[r] = fma(alpha, sum, y[r]);
+  y[r] = narrow<TY, T>(fma(alpha, sum, widen(y[r])));
 }
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
@@ -724,6 +752,20 @@ alphasparseStatus_t spmv_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, Pla
   return status_of(cudaGetLastError());
 }
 
+template <typename TA, typename TY, typename OffT>
+alphasparseStatus_t spmv_lowp_tile(alphasparseHandle_t h, alphasparseSpMatDescr_t A, Plan* p, const void* x,
+                                   void* y, float alpha, float beta, void* ext) {
+  float* carry = reinterpret_cast<float*>(ext ? ext : p->carry);
+  spmv_tile_kernel<float, OffT, TA, TY><<<(unsigned)p->merge_tiles, kThreads, 0, h->stream>>>(
+      reinterpret_cast<const OffT*>(A->row_offsets), A->const_col_data, reinterpret_cast<const TA*>(A->const_val_data),
+      reinterpret_cast<const TA*>(x), reinterpret_cast<TY*>(y), alpha, beta, p->rows, p->nnz, p->merge_tile_row,
+      carry, p->dev_err);
+  spmv_merge_fixup_kernel<float, TY><<<(unsigned)((p->merge_tiles + 255) / 256), 256, 0, h->stream>>>(
+      p->merge_tile_row, carry, p->merge_tiles, p->rows, reinterpret_cast<TY*>(y), alpha);
+  impl(h)->launches += 2;
+  return status_of(cudaGetLastError());
+}
+
 int variant_for(const Plan* p, alphasparseSpMVAlg_t alg) {
   const char* f = getenv("ASP_SPMV_VARIANT");
   if (f && !strcmp(f, "binned")) return kVariantBinned;
@@ -763,9 +805,11 @@ alphasparseStatus_t check_spmv_args(alphasparseHandle_t h, alphasparseOperation_
   alphasparseStatus_t s = validate_csr(A);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   if (!x->init || !y->init) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
-  if (A->data_type != ALPHA_R_32F && A->data_type != ALPHA_R_64F) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
-  if (x->data_type != A->data_type || y->data_type != A->data_type || computeType != A->data_type)
-    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (!spmv_lowp_types(A->data_type, x->data_type, y->data_type, computeType)) {
+    if (A->data_type != ALPHA_R_32F && A->data_type != ALPHA_R_64F) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    if (x->data_type != A->data_type || y->data_type != A->data_type || computeType != A->data_type)
+      return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  }
   if (x->size != A->cols || y->size != A->rows) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
   if ((A->cols > 0 && !x->values) || (A->rows > 0 && !y->values)) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
   return ALPHA_SPARSE_STATUS_SUCCESS;
@@ -791,6 +835,22 @@ alphasparseStatus_t alphasparseSpMV(alphasparseHandle_t h, alphasparseOperation_
   }
   Plan* p = plan_of(A);
   if (p->rows != A->rows || p->nnz != A->nnz || p->cols != A->cols) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+  if (A->data_type == ALPHA_R_16F || A->data_type == ALPHA_R_16BF) {
+    // 16-bit operands, fp32 arithmetic: the TMA-staged merge-path kernel when the plan chose merge-path
+    // and the arrays can be bulk-copied, else the row-length-binned kernel of spmv_lowp.cu
+    const float al = *(const float*)alpha, be = *(const float*)beta;
+    const int variant = variant_for(p, alg);
+    const bool tile_ok = variant == kVariantMerge && aligned(A->const_val_data, 16) && aligned(A->const_col_data, 16) &&
+                         p->merge_tiles <= INT_MAX && p->rows > 0;
+    p->last_variant = tile_ok ? kVariantMerge : kVariantBinned;
+    if (!tile_ok) return spmv_lowp_run(h, A, p, x->values, y->values, al, be);
+    const bool o64 = A->row_type == ALPHA_SPARSE_INDEXTYPE_I64;
+    if (A->data_type == ALPHA_R_16F)
+      return o64 ? spmv_lowp_tile<__half, float, int64_t>(h, A, p, x->values, y->values, al, be, externalBuffer)
+                 : spmv_lowp_tile<__half, float, int32_t>(h, A, p, x->values, y->values, al, be, externalBuffer);
+    return o64 ? spmv_lowp_tile<__nv_bfloat16, __nv_bfloat16, int64_t>(h, A, p, x->values, y->values, al, be, externalBuffer)
+               : spmv_lowp_tile<__nv_bfloat16, __nv_bfloat16, int32_t>(h, A, p, x->values, y->values, al, be, externalBuffer);
+  }
   const int variant = variant_for(p, alg);
   p->last_variant = variant;
   const bool o64 = A->row_type == ALPHA_SPARSE_INDEXTYPE_I64;
@@ -816,7 +876,8 @@ alphasparseStatus_t alphasparseSpMV_bufferSize(alphasparseHandle_t h, alphaspars
   // One carry slot per merge-path tile, in 64-bit arithmetic (the reference adds rows+nnz in
   // int, cuda/kernel/level2/alphasparse_spmv.cu:357).
   const int64_t tiles = (A->rows + A->nnz + kMergeItems - 1) / kMergeItems;
-  size_t bytes = (size_t)(tiles > 0 ? tiles : 1) * elem_size(A->data_type);
+  const size_t slot = elem_size(A->data_type) < 4 ? 4 : elem_size(A->data_type);  // 16-bit matrices carry in fp32
+  size_t bytes = (size_t)(tiles > 0 ? tiles : 1) * slot;
   *bufferSize = (bytes + 255) & ~(size_t)255;
   return ALPHA_SPARSE_STATUS_SUCCESS;
 }
