@@ -302,8 +302,12 @@ alphasparseStatus_t alphasparseSpMVCsrNoAlloc(cudaStream_t stream, int64_t rows,
                                               alphasparseDataType valueType, const void* alpha,
                                               const void* x, const void* beta, void* y);
 
-/* ---- SpMM: C = alpha*op(A)*op(B) + beta*C, B and C row-major ------------------------ */
-/* spapi.h:6963-6974; cuda/kernel/level3/alphasparse_spmm.cu:531-612 */
+/* ---- SpMM: C = alpha*op(A)*op(B) + beta*C ------------------------------------------- */
+/* spapi.h:6963-6974; cuda/kernel/level3/alphasparse_spmm.cu:531-612.  B and C both row-major
+ * (no external buffer needed) or both column-major: then externalBuffer must hold
+ * alphasparseSpMM_bufferSize bytes, into which row-major copies of B and C are made (the
+ * reference transposes B and C in place with buffers it allocates per call, :131-285); B is
+ * left untouched and C keeps its layout. */
 alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t handle, alphasparseOperation_t opA,
                                     alphasparseOperation_t opB, const void* alpha,
                                     alphasparseSpMatDescr_t matA, alphasparseDnMatDescr_t matB,

@@ -153,14 +153,20 @@ class DnVecWindow(DnVec):
 
 
 class DnMat:
+    """Dense matrix descriptor over a 2-D device tensor: row-major when its columns are contiguous
+    (stride(1) == 1), column-major when its rows are (stride(0) == 1, e.g. ``x.t()`` of a
+    contiguous tensor); the other stride is the leading dimension."""
+
     def __init__(self, t: torch.Tensor):
-        assert t.is_cuda and t.dim() == 2 and t.stride(1) == 1
+        assert t.is_cuda and t.dim() == 2 and (t.stride(1) == 1 or t.stride(0) == 1)
         self.t = t
         self.d = C.c_void_p()
+        row = t.stride(1) == 1
+        self.order = ORDER_ROW if row else ORDER_COL
         _check(load().alphasparseCreateDnMat(C.byref(self.d), C.c_int64(t.shape[0]),
-                                             C.c_int64(t.shape[1]), C.c_int64(t.stride(0)),
+                                             C.c_int64(t.shape[1]), C.c_int64(t.stride(0) if row else t.stride(1)),
                                              C.c_void_p(t.data_ptr()), _dtype_code(t.dtype),
-                                             ORDER_ROW), "alphasparseCreateDnMat")
+                                             self.order), "alphasparseCreateDnMat")
 
     def __del__(self):
         if getattr(self, "d", None):
@@ -233,13 +239,24 @@ def spmv(handle: Handle, A: CsrMatrix, x: DnVec, y: DnVec, alpha=1.0, beta=0.0,
            "alphasparseSpMV")
 
 
+def spmm_buffer_size(handle: Handle, A: CsrMatrix, B: DnMat, Cm: DnMat, alg=SPMM_ALG_DEFAULT) -> int:
+    code = _dtype_code(Cm.t.dtype)
+    a, b = _scalar(1.0, code), _scalar(0.0, code)
+    size = C.c_size_t(0)
+    _check(load().alphasparseSpMM_bufferSize(handle.h, OP_N, OP_N, C.byref(a), A.d, B.d, C.byref(b), Cm.d,
+                                             code, alg, C.byref(size)), "alphasparseSpMM_bufferSize")
+    return int(size.value)
+
+
 def spmm(handle: Handle, A: CsrMatrix, B: DnMat, Cm: DnMat, alpha=1.0, beta=0.0,
-         alg=SPMM_ALG_DEFAULT, compute=None):
-    """C = alpha*A*B + beta*C (row-major B and C) on handle's stream (asynchronous)."""
+         alg=SPMM_ALG_DEFAULT, compute=None, buffer: torch.Tensor | None = None):
+    """C = alpha*A*B + beta*C on handle's stream (asynchronous).  B and C both row-major, or both
+    column-major with a ``buffer`` of spmm_buffer_size bytes."""
     code = _dtype_code(Cm.t.dtype) if compute is None else compute
     a, b = _scalar(alpha, code), _scalar(beta, code)
+    buf = C.c_void_p(buffer.data_ptr()) if buffer is not None else C.c_void_p()
     _check(load().alphasparseSpMM(handle.h, OP_N, OP_N, C.byref(a), A.d, B.d, C.byref(b), Cm.d, code,
-                                  alg, C.c_void_p()), "alphasparseSpMM")
+                                  alg, buf), "alphasparseSpMM")
 
 
 def spmm_preprocess(handle: Handle, A: CsrMatrix, B: DnMat, Cm: DnMat, alg=SPMM_ALG_DEFAULT):

@@ -360,6 +360,48 @@ alphasparseStatus_t spmm_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, con
   return launch_rb<T, OffT, 32, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
 }
 
+// dst[c * ld_dst + r] = src[r * ld_src + c] for an r_n x c_n row-major source: 32 x 32 tiles through
+// shared memory, both sides coalesced.  Used to present column-major B and C to the row-major kernels
+// (the reference transposes them in place with freshly allocated buffers on every call,
+// cuda/kernel/level3/alphasparse_spmm.cu:131-285, cuda/format/transpose_dn_mat.h:17-34).
+template <typename W>
+__global__ void __launch_bounds__(256) transpose_kernel(const W* __restrict__ src, int64_t ld_src, int64_t r_n,
+                                                        int64_t c_n, W* __restrict__ dst, int64_t ld_dst) {
+  __shared__ W tile[32][33];
+  const int64_t tiles_c = (c_n + 31) / 32;
+  const int64_t tiles = ((r_n + 31) / 32) * tiles_c;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+    const int64_t r0 = (t / tiles_c) * 32, c0 = (t % tiles_c) * 32;
+#pragma unroll
+    for (int i = ty; i < 32; i += 8)
+      if (r0 + i < r_n && c0 + tx < c_n) tile[i][tx] = src[(r0 + i) * ld_src + c0 + tx];
+    __syncthreads();
+#pragma unroll
+    for (int i = ty; i < 32; i += 8)
+      if (c0 + i < c_n && r0 + tx < r_n) dst[(c0 + i) * ld_dst + r0 + tx] = tile[tx][i];
+    __syncthreads();
+  }
+}
+
+alphasparseStatus_t transpose_any(alphasparseHandle_t h, const void* src, int64_t ld_src, int64_t r_n, int64_t c_n,
+                                  void* dst, int64_t ld_dst, size_t elem) {
+  if (r_n == 0 || c_n == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+  int64_t tiles = ((r_n + 31) / 32) * ((c_n + 31) / 32);
+  const int64_t cap = (int64_t)impl(h)->sm_count * 16;
+  const unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
+  if (elem == 2)
+    transpose_kernel<uint16_t><<<grid, 256, 0, h->stream>>>((const uint16_t*)src, ld_src, r_n, c_n, (uint16_t*)dst, ld_dst);
+  else if (elem == 4)
+    transpose_kernel<uint32_t><<<grid, 256, 0, h->stream>>>((const uint32_t*)src, ld_src, r_n, c_n, (uint32_t*)dst, ld_dst);
+  else
+    transpose_kernel<uint64_t><<<grid, 256, 0, h->stream>>>((const uint64_t*)src, ld_src, r_n, c_n, (uint64_t*)dst, ld_dst);
+  impl(h)->launches++;
+  return status_of(cudaGetLastError());
+}
+
+inline size_t round256(size_t b) { return (b + 255) & ~(size_t)255; }
+
 alphasparseStatus_t check_spmm_args(alphasparseHandle_t h, alphasparseOperation_t opA,
                                     alphasparseOperation_t opB, const void* alpha,
                                     alphasparseSpMatDescr_t A, alphasparseDnMatDescr_t B,
@@ -373,10 +415,10 @@ alphasparseStatus_t check_spmm_args(alphasparseHandle_t h, alphasparseOperation_
   alphasparseStatus_t s = validate_csr(A);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   if (!B->init || !C->init) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
-  if (B->order != ALPHASPARSE_ORDER_ROW || C->order != ALPHASPARSE_ORDER_ROW)
-    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (B->order != C->order) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;  // both row-major or both column-major
   if (B->rows != A->cols || C->rows != A->rows || B->cols != C->cols) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
-  if (B->ld < B->cols || C->ld < C->cols) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  const bool row = B->order == ALPHASPARSE_ORDER_ROW;
+  if (B->ld < (row ? B->cols : B->rows) || C->ld < (row ? C->cols : C->rows)) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
   if (!B->values || !C->values) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
   const bool plain = (A->data_type == ALPHA_R_32F || A->data_type == ALPHA_R_64F) &&
                      B->data_type == A->data_type && C->data_type == A->data_type &&
@@ -399,12 +441,31 @@ alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t h, alphasparseOperation_
                                     alphasparseSpMatDescr_t A, alphasparseDnMatDescr_t B,
                                     const void* beta, alphasparseDnMatDescr_t C,
                                     alphasparseDataType computeType, alphasparseSpMMAlg_t alg,
-                                    void* /*externalBuffer*/) {
+                                    void* externalBuffer) {
   alphasparseStatus_t s = check_spmm_args(h, opA, opB, alpha, A, B, beta, C, computeType);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   if (!A->info) {
     s = analyse(h, A);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  }
+  if (B->order == ALPHASPARSE_ORDER_COL) {
+    // Column-major B and C: row-major copies in the caller's buffer (sizes: alphasparseSpMM_bufferSize),
+    // the row-major kernel, and C copied back.  B and C themselves keep their layout.
+    if (!externalBuffer) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+    const size_t eb = elem_size(B->data_type), ec = elem_size(C->data_type);
+    const int64_t n = C->cols;
+    _alphasparse_dnmat_descr Bt = *B, Ct = *C;
+    Bt.order = Ct.order = ALPHASPARSE_ORDER_ROW;
+    Bt.ld = Ct.ld = n;
+    Bt.values = externalBuffer;
+    Ct.values = reinterpret_cast<unsigned char*>(externalBuffer) + round256((size_t)B->rows * n * eb);
+    s = transpose_any(h, B->values, B->ld, n, B->rows, Bt.values, n, eb);
+    const bool reads_c = computeType == ALPHA_R_64F ? *(const double*)beta != 0.0 : *(const float*)beta != 0.f;
+    if (s == ALPHA_SPARSE_STATUS_SUCCESS && reads_c) s = transpose_any(h, C->values, C->ld, n, C->rows, Ct.values, n, ec);
+    if (s == ALPHA_SPARSE_STATUS_SUCCESS)
+      s = alphasparseSpMM(h, opA, opB, alpha, A, &Bt, beta, &Ct, computeType, alg, nullptr);
+    if (s == ALPHA_SPARSE_STATUS_SUCCESS) s = transpose_any(h, Ct.values, n, C->rows, n, C->values, C->ld, ec);
+    return s;
   }
   const int64_t n = C->cols;
   if (A->data_type == ALPHA_R_16BF) {
@@ -433,7 +494,10 @@ alphasparseStatus_t alphasparseSpMM_bufferSize(alphasparseHandle_t h, alphaspars
   if (!bufferSize) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
   alphasparseStatus_t s = check_spmm_args(h, opA, opB, alpha, A, B, beta, C, computeType);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-  *bufferSize = 256;  // no kernel of this path needs caller scratch; non-zero so cudaMalloc returns a pointer
+  *bufferSize = 256;  // no row-major kernel needs caller scratch; non-zero so cudaMalloc returns a pointer
+  if (B->order == ALPHASPARSE_ORDER_COL)  // row-major copies of B and C
+    *bufferSize = round256((size_t)B->rows * B->cols * elem_size(B->data_type)) +
+                  round256((size_t)C->rows * C->cols * elem_size(C->data_type));
   return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
@@ -445,14 +509,25 @@ alphasparseStatus_t alphasparseSpMM_preprocess(alphasparseHandle_t h, alphaspars
                                                alphasparseSpMMAlg_t, size_t* bufferSize) {
   alphasparseStatus_t s = check_spmm_args(h, opA, opB, alpha, A, B, beta, C, computeType);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-  if (bufferSize) *bufferSize = 256;
+  if (bufferSize) {
+    *bufferSize = 256;
+    if (B->order == ALPHASPARSE_ORDER_COL)
+      *bufferSize = round256((size_t)B->rows * B->cols * elem_size(B->data_type)) +
+                    round256((size_t)C->rows * C->cols * elem_size(C->data_type));
+  }
   if (!A->info) {
     s = analyse(h, A);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   }
   if (A->data_type == ALPHA_R_16BF) {
-    if (!spmm_tc_applicable(A, B, C)) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
-    return spmm_tc_run(h, A, B, C, 0.f, 0.f, true);
+    _alphasparse_dnmat_descr Bt = *B, Ct = *C;
+    if (B->order == ALPHASPARSE_ORDER_COL) {  // the kernel will see the row-major copies (aligned, ld = N)
+      Bt.order = Ct.order = ALPHASPARSE_ORDER_ROW;
+      Bt.ld = Ct.ld = C->cols;
+      Bt.values = Ct.values = reinterpret_cast<void*>(uintptr_t(256));
+    }
+    if (!spmm_tc_applicable(A, &Bt, &Ct)) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    return spmm_tc_run(h, A, &Bt, &Ct, 0.f, 0.f, true);
   }
   return ALPHA_SPARSE_STATUS_SUCCESS;
 }

@@ -107,8 +107,42 @@ def test_status_codes(handle):
     t = torch.zeros(12, 8, device="cuda")
     assert lib.alphasparseCreateDnMat(C.byref(d), C.c_int64(12), C.c_int64(8), C.c_int64(12),
                                       C.c_void_p(t.data_ptr()), api.R_32F, api.ORDER_COL) == 0
-    assert call(b=d) == 6  # column-major operands are not supported
+    assert call(b=d) == 6  # B column-major with C row-major: orders must agree
+    dc = C.c_void_p()
+    tc = torch.zeros(10, 8, device="cuda")
+    assert lib.alphasparseCreateDnMat(C.byref(dc), C.c_int64(10), C.c_int64(8), C.c_int64(10),
+                                      C.c_void_p(tc.data_ptr()), api.R_32F, api.ORDER_COL) == 0
+    assert call(b=d, c=dc) == 7  # both column-major: needs the external buffer (invalid pointer without)
     lib.alphasparseDestroyDnMat(d)
+    lib.alphasparseDestroyDnMat(dc)
     size = C.c_size_t()
     assert lib.alphasparseSpMM_bufferSize(handle.h, 0, 0, C.byref(one), Am.d, B.d, C.byref(one), Cm.d,
                                           api.R_32F, 0, C.byref(size)) == 0 and size.value > 0
+
+
+@pytest.mark.parametrize("dtype,n", [(np.float32, 8), (np.float32, 20), (np.float64, 32), (np.float32, 128)])
+def test_column_major_operands(handle, dtype, n):
+    """Column-major B and C (leading dimensions larger than the row counts): same result, bit for bit,
+    as the row-major call, padding untouched, B unchanged."""
+    A = G.stencil_3d_27pt(12, seed=5)
+    rp, ci, v = A.row_ptr.numpy(), A.col_idx.numpy(), A.val.numpy().astype(dtype)
+    X = G.uniform((A.cols, n), -1, 1, dtype=torch.from_numpy(np.zeros(1, dtype)).dtype, seed=30).numpy()
+    Y0 = G.uniform((A.rows, n), -1, 1, dtype=torch.from_numpy(np.zeros(1, dtype)).dtype, seed=31).numpy()
+    Am = api.CsrMatrix(A.rows, A.cols, torch.from_numpy(rp).cuda(), torch.from_numpy(ci).cuda(),
+                       torch.from_numpy(v).cuda())
+    for alpha, beta in ((1.0, 0.0), (0.5, 2.0)):
+        want = oracle.spmm(rp, ci, v, X, alpha, beta, Y0)
+        ldb, ldc = A.cols + 3, A.rows + 5
+        bbuf = torch.full((n, ldb), 9.0, dtype=torch.from_numpy(X).dtype, device="cuda")
+        cbuf = torch.full((n, ldc), 7.0, dtype=torch.from_numpy(X).dtype, device="cuda")
+        bbuf[:, :A.cols] = torch.from_numpy(X).cuda().t()
+        cbuf[:, :A.rows] = torch.from_numpy(Y0).cuda().t()
+        Bd, Cd = api.DnMat(bbuf[:, :A.cols].t()), api.DnMat(cbuf[:, :A.rows].t())
+        assert Bd.order == api.ORDER_COL and Cd.order == api.ORDER_COL
+        b_before = bbuf.clone()
+        buf = torch.empty(api.spmm_buffer_size(handle, Am, Bd, Cd), dtype=torch.uint8, device="cuda")
+        api.spmm(handle, Am, Bd, Cd, alpha, beta, buffer=buf)
+        torch.cuda.synchronize()
+        got = cbuf[:, :A.rows].t().cpu().numpy()
+        assert np.array_equal(got, want)
+        assert bool((cbuf[:, A.rows:] == 7.0).all()) and torch.equal(bbuf, b_before)

@@ -100,3 +100,23 @@ def test_sparse_random_matrix_is_refused(handle):
     with pytest.raises(api.AlphaSparseError) as e:
         api.spmm(handle, Am, B, C)
     assert e.value.status == 6
+
+
+def test_column_major_bf16(handle):
+    """Column-major B (bf16) and C (fp32) through the row-major copies in the caller's buffer."""
+    A = G.stencil_3d_27pt(12, seed=4)
+    A.val = A.val.to(torch.bfloat16)
+    n = 64
+    X = G.uniform((A.cols, n), -1, 1, dtype=torch.bfloat16, seed=75)
+    Y0 = G.uniform((A.rows, n), -1, 1, seed=76)
+    want = oracle.spmm(A.row_ptr.numpy(), A.col_idx.numpy(), bits(A.val), bits(X), 1.5, 0.5, Y0.numpy())
+    Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr.cuda(), A.col_idx.cuda(), A.val.cuda())
+    Bc = X.cuda().t().contiguous().t()        # column-major storage of the same matrix
+    Cc = Y0.cuda().t().contiguous().t()
+    Bd, Cd = api.DnMat(Bc), api.DnMat(Cc)
+    assert Bd.order == api.ORDER_COL
+    api.spmm_preprocess(handle, Am, Bd, Cd)
+    buf = torch.empty(api.spmm_buffer_size(handle, Am, Bd, Cd), dtype=torch.uint8, device="cuda")
+    api.spmm(handle, Am, Bd, Cd, 1.5, 0.5, buffer=buf)
+    torch.cuda.synchronize()
+    assert rel_l2(Cc.cpu().numpy(), want) <= 1e-5
