@@ -246,7 +246,13 @@ alphasparseStatus_t alphasparseDnMatSetValues(alphasparseDnMatDescr_t descr, voi
  * (A and x / y / computeType, alpha and beta host pointers of the compute type):
  *   R_32F / R_32F / R_32F  (:234)      R_64F / R_64F / R_64F  (:240)
  *   R_16F / R_32F / R_32F  (:288-292)  R_16BF / R_16BF / R_32F (:294-300)
- * with 32- or 64-bit row offsets.  The reference's complex and int8 instances are not provided. */
+ * with 32- or 64-bit row offsets.  The reference's complex and int8 instances are not provided.
+ * opA = TRANSPOSE (or CONJUGATE_TRANSPOSE, the same for real types): x has A's row count, y its
+ * column count; the first such call (or alphasparseSpMV_analysis with that opA) builds a
+ * transposed copy of A on the device, which allocates and synchronises; A itself is not
+ * modified (the reference's transpose_csr overwrites A, cuda/format/transpose_csr.h:9-78).  The
+ * copy holds A's values as of then: after changing them call alphasparseSpMV_clearMat.
+ * Matrices with 2^31 or more entries are not transposed (NOT_SUPPORTED). */
 alphasparseStatus_t alphasparseSpMV(alphasparseHandle_t handle, alphasparseOperation_t opA,
                                     const void* alpha, alphasparseSpMatDescr_t matA,
                                     alphasparseDnVecDescr_t vecX, const void* beta,
@@ -368,6 +374,23 @@ alphasparseStatus_t alphasparseCsrColumnRange(alphasparseHandle_t handle, int64_
 alphasparseStatus_t alphasparseCreateDnVecWindow(alphasparseDnVecDescr_t* descr, int64_t size,
                                                  int64_t first, int64_t count,
                                                  void* window_values, alphasparseDataType data_type);
+
+/* ---- the step before the path: MatrixMarket file -> COO (host) ------------------------- */
+/* cuda/test/io.cu:1227-1238 (alpha_read_coo<T>(file, &m, &n, &nnz, &row_index, &col_index,
+ * &values)), MatrixMarket part (:103-184, :490-575).  Reads a coordinate file into HOST arrays
+ * allocated with malloc (release them with alphasparseFreeHost): zero-based indices, value 1
+ * for pattern entries, and for symmetric / Hermitian / skew-symmetric files each off-diagonal
+ * entry followed by its mirror image with the same value, as the reference's reader does.
+ * valueType R_32F or R_64F.  Status instead of exit(): INVALID_VALUE for a missing or malformed
+ * file or an index outside the announced size, NOT_SUPPORTED for array or complex files.  The
+ * reference's ".bin" dump format is not read. */
+alphasparseStatus_t alphasparseReadMtxCoo(const char* file, int64_t* rows, int64_t* cols, int64_t* nnz,
+                                          int32_t** row_index, int32_t** col_index, void** values,
+                                          alphasparseDataType valueType);
+void alphasparseFreeHost(void* p);
+/* cuda/format/coo_order.h:25-43: HOST arrays sorted by (row, column), stable. */
+alphasparseStatus_t alphasparseCooOrder(int64_t nnz, int32_t* row_index, int32_t* col_index,
+                                        void* values, alphasparseDataType valueType);
 
 /* ---- the step before the path: COO -> CSR row offsets -------------------------------- */
 /* cuda/format/coo2csr.h:82-92 (template alphasparseXcoo2csr<T>(row_data, nnz, m, csrRowPtr), default

@@ -43,7 +43,7 @@ EXPORTS = [
     "alphasparseCsrPartitionRowsByNnz", "alphasparseCsrRebaseRowOffsets", "alphasparseCsrPlanGet",
     "alphasparseCsrLastVariant", "alphasparseGetLaunchCount", "get_time_us", "get_avg_time_n",
     "alphasparseSpMVCsrNoAlloc", "alphasparseXcoo2csr", "alphasparseCsrColumnRange",
-    "alphasparseCreateDnVecWindow",
+    "alphasparseCreateDnVecWindow", "alphasparseReadMtxCoo", "alphasparseFreeHost", "alphasparseCooOrder",
 ]
 
 
@@ -327,3 +327,30 @@ def coo2csr(coo_row: torch.Tensor, rows: int, out_dtype=torch.int32, stream=None
                                       C.c_int64(rows), C.c_void_p(out.data_ptr()),
                                       INDEX_I64 if out_dtype == torch.int64 else INDEX_I32), "alphasparseXcoo2csr")
     return out
+
+
+def read_mtx(path: str, dtype=torch.float32, ordered: bool = True):
+    """MatrixMarket coordinate file -> (rows, cols, row_index, col_index, values) as host tensors,
+    sorted by (row, column) when ``ordered`` (what coo2csr needs)."""
+    import numpy as np
+    lib = load()
+    lib.alphasparseFreeHost.restype = None
+    code = _dtype_code(dtype)
+    m, n, nnz = C.c_int64(), C.c_int64(), C.c_int64()
+    ri, ci, v = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    _check(lib.alphasparseReadMtxCoo(path.encode(), C.byref(m), C.byref(n), C.byref(nnz), C.byref(ri), C.byref(ci),
+                                     C.byref(v), code), "alphasparseReadMtxCoo")
+    try:
+        k = nnz.value
+        if ordered:
+            _check(lib.alphasparseCooOrder(C.c_int64(k), ri, ci, v, code), "alphasparseCooOrder")
+        npdt = np.float32 if dtype == torch.float32 else np.float64
+        def arr(p, t):
+            return np.ctypeslib.as_array(C.cast(p, C.POINTER(t)), shape=(k,)).copy() if k else np.zeros(0, dtype=t)
+        rows_i = arr(ri, C.c_int32)
+        cols_i = arr(ci, C.c_int32)
+        vals = arr(v, C.c_float if npdt == np.float32 else C.c_double)
+    finally:
+        for p in (ri, ci, v):
+            lib.alphasparseFreeHost(p)
+    return m.value, n.value, torch.from_numpy(rows_i), torch.from_numpy(cols_i), torch.from_numpy(vals)

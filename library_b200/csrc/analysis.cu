@@ -9,6 +9,7 @@
 // (cuda/kernel/level2/alphasparse_spmv_csr_adaptive2.h:6-48), and the merge-path search runs
 // per SpMV (alphasparse_spmv_csr_merge_ginkgo.h:133-158).  Here both are computed once,
 // deterministically, and kept in the descriptor.
+#include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_select.cuh>
 #include <thrust/iterator/counting_iterator.h>
 
@@ -182,6 +183,31 @@ __global__ void __launch_bounds__(256) col_range_kernel(const int32_t* __restric
   }
 }
 
+// Transposition, after the entries were sorted by column (stable, so rows ascend inside a column):
+// entry i of the transposed matrix is entry perm[i] of A; its column index there is the row of A that
+// holds perm[i] (last row whose offset is <= perm[i]), its value a copy.
+template <typename OffT, typename W>
+__global__ void __launch_bounds__(256) transpose_fill_kernel(const OffT* __restrict__ rp, int64_t rows,
+                                                             const uint32_t* __restrict__ perm, int64_t nnz,
+                                                             const W* __restrict__ val, int32_t* __restrict__ t_col,
+                                                             W* __restrict__ t_val) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nnz; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t e = perm[i];
+    int64_t lo = 0, hi = rows;  // first row whose end offset is > e
+    while (lo < hi) {
+      const int64_t mid = (lo + hi) >> 1;
+      if ((int64_t)rp[mid + 1] <= e) lo = mid + 1;
+      else hi = mid;
+    }
+    t_col[i] = (int32_t)lo;
+    t_val[i] = val[e];
+  }
+}
+__global__ void __launch_bounds__(256) iota_kernel(uint32_t* __restrict__ out, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = (uint32_t)i;
+}
+
 // csrRowPtr[r] = number of COO entries whose (ascending) row index is below r.
 template <typename OutT>
 __global__ void __launch_bounds__(256) coo2csr_kernel(const int32_t* __restrict__ coo_row, int64_t nnz,
@@ -341,6 +367,25 @@ alphasparseStatus_t validate_csr(alphasparseSpMatDescr_t A) {
   return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
+// The transposed matrix a plan may own: three device arrays, a descriptor over them, that
+// descriptor's own plan.
+struct Transposed {
+  void* rp = nullptr;
+  int32_t* col = nullptr;
+  void* val = nullptr;
+  _alphasparseSpMatDescr d{};
+};
+
+void free_transposed(void* q) {
+  Transposed* t = reinterpret_cast<Transposed*>(q);
+  if (!t) return;
+  if (t->d.info) free_plan(plan_of(&t->d));
+  cudaFree(t->rp);
+  cudaFree(t->col);
+  cudaFree(t->val);
+  delete t;
+}
+
 void free_plan(Plan* p) {
   if (!p) return;
   cudaFree(p->bin_rows);
@@ -348,7 +393,102 @@ void free_plan(Plan* p) {
   cudaFree(p->carry);
   cudaFree(p->dev_err);
   if (p->spmm_tc) free_spmm_tc_plan(p->spmm_tc);
+  if (p->transposed) free_transposed(p->transposed);
   delete p;
+}
+
+// A^T in CSR, on the device (the reference's transpose_csr copies the matrix to the host, transposes
+// it there and overwrites A's arrays, cuda/format/transpose_csr.h:9-78).  Stable radix sort of the
+// entry numbers by column, row offsets of the result by one search per column, then a gather of
+// rows and values.  A itself is left as it is; the copy of the values is as of this call.
+alphasparseStatus_t transposed_of(alphasparseHandle_t h, alphasparseSpMatDescr_t A, alphasparseSpMatDescr_t* At) {
+  if (!A->info) {
+    alphasparseStatus_t s = analyse(h, A);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  }
+  Plan* p = plan_of(A);
+  if (p->transposed) {
+    *At = &reinterpret_cast<Transposed*>(p->transposed)->d;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+  }
+  if (A->nnz >= (int64_t(1) << 31) || A->rows >= (int64_t(1) << 31) || A->cols >= (int64_t(1) << 31))
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  const size_t es = elem_size(A->data_type);
+  if (es == 0) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  Transposed* t = new (std::nothrow) Transposed();
+  if (!t) return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+  cudaStream_t st = h->stream;
+  const int64_t nnz = A->nnz, n1 = nnz > 0 ? nnz : 1;
+  const bool o64 = A->row_type == ALPHA_SPARSE_INDEXTYPE_I64;
+  int32_t* keys = nullptr;
+  uint32_t *ent = nullptr, *perm = nullptr;
+  void* tmp = nullptr;
+  size_t tmp_bytes = 0;
+  int bits = 1;
+  while ((int64_t(1) << bits) < A->cols && bits < 31) ++bits;
+  cub::DeviceRadixSort::SortPairs(nullptr, tmp_bytes, (const int32_t*)nullptr, (int32_t*)nullptr, (const uint32_t*)nullptr,
+                                  (uint32_t*)nullptr, (int)nnz, 0, bits, st);
+  cudaError_t e = cudaMalloc(&t->rp, (size_t)(A->cols + 1) * (o64 ? 8 : 4));
+  if (e == cudaSuccess) e = cudaMalloc(&t->col, (size_t)n1 * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&t->val, (size_t)n1 * es);
+  if (e == cudaSuccess) e = cudaMalloc(&keys, (size_t)n1 * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&ent, (size_t)n1 * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&perm, (size_t)n1 * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&tmp, tmp_bytes ? tmp_bytes : 16);
+  alphasparseStatus_t s = status_of(e);
+  if (s == ALPHA_SPARSE_STATUS_SUCCESS && nnz > 0) {
+    const int g = grid_for(nnz, impl(h)->sm_count);
+    iota_kernel<<<g, 256, 0, st>>>(ent, nnz);
+    // keys: column of every entry, sorted into t->col for the moment (it is overwritten by the rows below
+    // only after the offsets were derived from it)
+    cub::DeviceRadixSort::SortPairs(tmp, tmp_bytes, A->const_col_data, keys, ent, perm, (int)nnz, 0, bits, st);
+    if (o64) coo2csr_kernel<int64_t><<<grid_for(A->cols + 1, impl(h)->sm_count), 256, 0, st>>>(keys, nnz, A->cols, (int64_t*)t->rp);
+    else coo2csr_kernel<int32_t><<<grid_for(A->cols + 1, impl(h)->sm_count), 256, 0, st>>>(keys, nnz, A->cols, (int32_t*)t->rp);
+#define ASP_FILL(OFF, W)                                                                                         \
+  transpose_fill_kernel<OFF, W><<<g, 256, 0, st>>>((const OFF*)A->row_offsets, A->rows, perm, nnz,                \
+                                                  (const W*)A->const_val_data, t->col, (W*)t->val)
+    if (o64) {
+      if (es == 2) ASP_FILL(int64_t, uint16_t);
+      else if (es == 4) ASP_FILL(int64_t, uint32_t);
+      else ASP_FILL(int64_t, uint64_t);
+    } else {
+      if (es == 2) ASP_FILL(int32_t, uint16_t);
+      else if (es == 4) ASP_FILL(int32_t, uint32_t);
+      else ASP_FILL(int32_t, uint64_t);
+    }
+#undef ASP_FILL
+    impl(h)->launches += 4;
+    s = status_of(cudaGetLastError());
+  } else if (s == ALPHA_SPARSE_STATUS_SUCCESS) {
+    s = status_of(cudaMemsetAsync(t->rp, 0, (size_t)(A->cols + 1) * (o64 ? 8 : 4), st));
+  }
+  if (s == ALPHA_SPARSE_STATUS_SUCCESS) s = status_of(cudaStreamSynchronize(st));
+  cudaFree(keys);
+  cudaFree(ent);
+  cudaFree(perm);
+  cudaFree(tmp);
+  if (s == ALPHA_SPARSE_STATUS_SUCCESS) {
+    t->d = *A;
+    t->d.rows = A->cols;
+    t->d.cols = A->rows;
+    t->d.info = nullptr;
+    t->d.analysed = false;
+    t->d.row_offsets = t->rp;
+    t->d.row_data = o64 ? nullptr : reinterpret_cast<int*>(t->rp);
+    t->d.const_row_data = t->d.row_data;
+    t->d.col_data = t->col;
+    t->d.const_col_data = t->col;
+    t->d.val_data = t->val;
+    t->d.const_val_data = t->val;
+    s = analyse(h, &t->d);
+  }
+  if (s != ALPHA_SPARSE_STATUS_SUCCESS) {
+    free_transposed(t);
+    return s;
+  }
+  p->transposed = t;
+  *At = &t->d;
+  return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
 alphasparseStatus_t analyse(alphasparseHandle_t h, alphasparseSpMatDescr_t A) {
@@ -386,8 +526,10 @@ alphasparseStatus_t alphasparseSpMV_analysis(alphasparseHandle_t h, alphasparseO
                                              alphasparseSpMatDescr_t A, alphasparseSpMVAlg_t) {
   if (!h || !h->impl) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
   if (!A) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
-  if (opA != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
-  return analyse(h, A);
+  alphasparseStatus_t s = analyse(h, A);
+  if (s != ALPHA_SPARSE_STATUS_SUCCESS || opA == ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) return s;
+  alphasparseSpMatDescr_t At = nullptr;  // a transposed product will follow: build and analyse A^T now
+  return transposed_of(h, A, &At);
 }
 
 alphasparseStatus_t alphasparseSpMV_clear(alphasparseHandle_t h, alphasparseSpMVAlg_t) {

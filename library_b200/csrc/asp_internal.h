@@ -61,6 +61,7 @@ struct Plan {
   // SpMM
   int64_t max_block_nnz = 0;          // most entries in an aligned block of kSpmmRowBlock rows
   void* spmm_tc = nullptr;            // plan of the tcgen05 variant (spmm_tc.cu)
+  void* transposed = nullptr;         // CSR of the transposed matrix with its own descriptor and plan (analysis.cu)
 };
 
 inline HandleImpl* impl(alphasparseHandle_t h) { return reinterpret_cast<HandleImpl*>(h->impl); }
@@ -105,6 +106,8 @@ inline int env_int(const char* name, int dflt) {
 alphasparseStatus_t analyse(alphasparseHandle_t h, alphasparseSpMatDescr_t A);
 void free_plan(Plan* p);
 alphasparseStatus_t validate_csr(alphasparseSpMatDescr_t A);
+// The CSR descriptor of A^T (built on the device at first use, owned by A's plan, analysed).
+alphasparseStatus_t transposed_of(alphasparseHandle_t h, alphasparseSpMatDescr_t A, alphasparseSpMatDescr_t* At);
 
 // spmm_tc.cu
 void free_spmm_tc_plan(void* p);

@@ -410,13 +410,14 @@ alphasparseStatus_t check_spmm_args(alphasparseHandle_t h, alphasparseOperation_
   if (!h || !h->impl) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
   if (!alpha || !beta || !A || !B || !C) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
   if (h->pointer_mode != ALPHA_SPARSE_POINTER_MODE_HOST) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
-  if (opA != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE || opB != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE)
-    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (opB != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  const bool tr = opA != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE;  // runs on the transposed matrix the plan keeps
   alphasparseStatus_t s = validate_csr(A);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   if (!B->init || !C->init) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
   if (B->order != C->order) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;  // both row-major or both column-major
-  if (B->rows != A->cols || C->rows != A->rows || B->cols != C->cols) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  if (B->rows != (tr ? A->rows : A->cols) || C->rows != (tr ? A->cols : A->rows) || B->cols != C->cols)
+    return ALPHA_SPARSE_STATUS_INVALID_SIZE;
   const bool row = B->order == ALPHASPARSE_ORDER_ROW;
   if (B->ld < (row ? B->cols : B->rows) || C->ld < (row ? C->cols : C->rows)) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
   if (!B->values || !C->values) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
@@ -444,6 +445,13 @@ alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t h, alphasparseOperation_
                                     void* externalBuffer) {
   alphasparseStatus_t s = check_spmm_args(h, opA, opB, alpha, A, B, beta, C, computeType);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  if (opA != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) {
+    alphasparseSpMatDescr_t At = nullptr;
+    s = transposed_of(h, A, &At);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    return alphasparseSpMM(h, ALPHA_SPARSE_OPERATION_NON_TRANSPOSE, opB, alpha, At, B, beta, C, computeType, alg,
+                           externalBuffer);
+  }
   if (!A->info) {
     s = analyse(h, A);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
@@ -509,6 +517,13 @@ alphasparseStatus_t alphasparseSpMM_preprocess(alphasparseHandle_t h, alphaspars
                                                alphasparseSpMMAlg_t, size_t* bufferSize) {
   alphasparseStatus_t s = check_spmm_args(h, opA, opB, alpha, A, B, beta, C, computeType);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  if (opA != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) {
+    alphasparseSpMatDescr_t At = nullptr;
+    s = transposed_of(h, A, &At);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    return alphasparseSpMM_preprocess(h, ALPHA_SPARSE_OPERATION_NON_TRANSPOSE, opB, alpha, At, B, beta, C, computeType,
+                                      ALPHASPARSE_SPMM_ALG_DEFAULT, bufferSize);
+  }
   if (bufferSize) {
     *bufferSize = 256;
     if (B->order == ALPHASPARSE_ORDER_COL)

@@ -801,7 +801,9 @@ alphasparseStatus_t check_spmv_args(alphasparseHandle_t h, alphasparseOperation_
   if (!h || !h->impl) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
   if (!alpha || !beta || !A || !x || !y) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
   if (h->pointer_mode != ALPHA_SPARSE_POINTER_MODE_HOST) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
-  if (opA != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  // a transposed product runs on the transposed matrix the plan keeps; for these real types the
+  // conjugate transpose is the transpose
+  const bool tr = opA != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE;
   alphasparseStatus_t s = validate_csr(A);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   if (!x->init || !y->init) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
@@ -810,8 +812,8 @@ alphasparseStatus_t check_spmv_args(alphasparseHandle_t h, alphasparseOperation_
     if (x->data_type != A->data_type || y->data_type != A->data_type || computeType != A->data_type)
       return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
   }
-  if (x->size != A->cols || y->size != A->rows) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
-  if ((A->cols > 0 && !x->values) || (A->rows > 0 && !y->values)) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  if (x->size != (tr ? A->rows : A->cols) || y->size != (tr ? A->cols : A->rows)) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  if ((x->size > 0 && !x->values) || (y->size > 0 && !y->values)) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
   return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
@@ -829,6 +831,13 @@ alphasparseStatus_t alphasparseSpMV(alphasparseHandle_t h, alphasparseOperation_
                                     alphasparseSpMVAlg_t alg, void* externalBuffer) {
   alphasparseStatus_t s = check_spmv_args(h, opA, alpha, A, x, beta, y, computeType);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  if (opA != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) {
+    alphasparseSpMatDescr_t At = nullptr;  // built (allocating, synchronising) at the first transposed call
+    s = transposed_of(h, A, &At);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    return alphasparseSpMV(h, ALPHA_SPARSE_OPERATION_NON_TRANSPOSE, alpha, At, x, beta, y, computeType, alg,
+                           externalBuffer);
+  }
   if (!A->info) {
     s = analyse(h, A);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
@@ -875,7 +884,7 @@ alphasparseStatus_t alphasparseSpMV_bufferSize(alphasparseHandle_t h, alphaspars
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   // One carry slot per merge-path tile, in 64-bit arithmetic (the reference adds rows+nnz in
   // int, cuda/kernel/level2/alphasparse_spmv.cu:357).
-  const int64_t tiles = (A->rows + A->nnz + kMergeItems - 1) / kMergeItems;
+  const int64_t tiles = ((A->rows > A->cols ? A->rows : A->cols) + A->nnz + kMergeItems - 1) / kMergeItems;  // either op
   const size_t slot = elem_size(A->data_type) < 4 ? 4 : elem_size(A->data_type);  // 16-bit matrices carry in fp32
   size_t bytes = (size_t)(tiles > 0 ? tiles : 1) * slot;
   *bufferSize = (bytes + 255) & ~(size_t)255;

@@ -21,7 +21,7 @@ def declared_functions():
         text = open(os.path.join(inc, fn)).read()
         text = text.split("#ifdef __cplusplus\n} /* extern \"C\" */")[0]  # C part only
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-        for m in re.finditer(r"^(?:alphasparseStatus_t|double|int64_t|const char\*)\s+(\w+)\s*\(", text, re.M):
+        for m in re.finditer(r"^(?:alphasparseStatus_t|double|int64_t|void|const char\*)\s+(\w+)\s*\(", text, re.M):
             names.append(m.group(1))
     return names
 

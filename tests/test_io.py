@@ -1,0 +1,91 @@
+"""MatrixMarket reader and COO ordering (host functions of the C ABI): what the reference's test
+drivers do before alphasparseXcoo2csr (cuda/test/io.cu:1227-1238, cuda/format/coo_order.h:25-43).
+The file contents below are written by this test."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from library_b200 import api
+
+
+def write(tmp_path, name, text):
+    p = tmp_path / name
+    p.write_text(text)
+    return str(p)
+
+
+def test_general_real(tmp_path):
+    f = write(tmp_path, "g.mtx", "%%MatrixMarket matrix coordinate real general\n% a comment\n\n"
+              "3 4 4\n3 1 2.5\n1 4 -1e-2\n1 2 7\n2 2 0.125\n")
+    m, n, r, c, v = api.read_mtx(f, torch.float64, ordered=False)
+    assert (m, n) == (3, 4)
+    assert r.tolist() == [2, 0, 0, 1] and c.tolist() == [0, 3, 1, 1]        # file order, zero-based
+    assert v.tolist() == [2.5, -1e-2, 7.0, 0.125]
+    m, n, r, c, v = api.read_mtx(f, torch.float32)                           # sorted by (row, column)
+    assert r.tolist() == [0, 0, 1, 2] and c.tolist() == [1, 3, 1, 0]
+    assert np.allclose(v.numpy(), np.array([7, -1e-2, 0.125, 2.5], np.float32))
+
+
+def test_symmetric_pattern_and_integer(tmp_path):
+    f = write(tmp_path, "s.mtx", "%%MatrixMarket matrix coordinate pattern symmetric\n3 3 3\n1 1\n3 1\n3 2\n")
+    m, n, r, c, v = api.read_mtx(f, torch.float32, ordered=False)
+    # an off-diagonal entry is followed by its mirror image; pattern entries are 1
+    assert r.tolist() == [0, 2, 0, 2, 1] and c.tolist() == [0, 0, 2, 1, 2] and v.tolist() == [1.0] * 5
+    f = write(tmp_path, "k.mtx", "%%MatrixMarket matrix coordinate integer skew-symmetric\n2 2 1\n2 1 3\n")
+    _, _, r, c, v = api.read_mtx(f, torch.float64, ordered=False)
+    assert r.tolist() == [1, 0] and c.tolist() == [0, 1] and v.tolist() == [3.0, 3.0]   # same value, as the reference
+
+
+def test_errors(tmp_path):
+    with pytest.raises(api.AlphaSparseError) as e:
+        api.read_mtx(str(tmp_path / "missing.mtx"))
+    assert e.value.status == 3
+    f = write(tmp_path, "a.mtx", "%%MatrixMarket matrix array real general\n2 2\n1\n2\n3\n4\n")
+    with pytest.raises(api.AlphaSparseError) as e:
+        api.read_mtx(f)
+    assert e.value.status == 6
+    f = write(tmp_path, "b.mtx", "%%MatrixMarket matrix coordinate real general\n2 2 2\n1 1 1.0\n3 1 2.0\n")
+    with pytest.raises(api.AlphaSparseError) as e:       # row 3 of a 2 x 2 matrix
+        api.read_mtx(f)
+    assert e.value.status == 3
+    f = write(tmp_path, "t.mtx", "%%MatrixMarket matrix coordinate real general\n2 2 3\n1 1 1.0\n")
+    with pytest.raises(api.AlphaSparseError):             # fewer entries than announced
+        api.read_mtx(f)
+
+
+def test_order_is_stable():
+    lib = api.load()
+    r = np.array([1, 0, 1, 0, 1], np.int32)
+    c = np.array([2, 5, 2, 1, 0], np.int32)
+    v = np.array([10, 20, 30, 40, 50], np.float64)
+    assert lib.alphasparseCooOrder(C.c_int64(5), r.ctypes.data_as(C.c_void_p), c.ctypes.data_as(C.c_void_p),
+                                   v.ctypes.data_as(C.c_void_p), api.R_64F) == 0
+    assert r.tolist() == [0, 0, 1, 1, 1] and c.tolist() == [1, 5, 0, 2, 2]
+    assert v.tolist() == [40, 20, 50, 10, 30]             # the two (1, 2) entries keep their file order
+
+
+@pytest.mark.gpu
+def test_file_to_spmv(handle, tmp_path):
+    """File -> COO -> ordered -> device CSR (alphasparseXcoo2csr) -> SpMV, against the oracle."""
+    import oracle
+    from conftest import rel_l2
+    from library_b200 import generators as G
+    A = G.poisson_random(300, 400, 6.0, dtype=torch.float64, seed=17)
+    rp, ci, v = A.numpy()
+    rows_of = np.repeat(np.arange(A.rows), np.diff(rp))
+    perm = np.random.default_rng(0).permutation(A.nnz)     # entries in arbitrary order in the file
+    lines = [f"{rows_of[k] + 1} {ci[k] + 1} {v[k]!r}" for k in perm]
+    f = write(tmp_path, "p.mtx", "%%MatrixMarket matrix coordinate real general\n"
+              f"{A.rows} {A.cols} {A.nnz}\n" + "\n".join(lines) + "\n")
+    m, n, r, c, vals = api.read_mtx(f, torch.float64)
+    assert (m, n, len(r)) == (A.rows, A.cols, A.nnz) and np.array_equal(c.numpy(), ci) and np.array_equal(vals.numpy(), v)
+    row_ptr = api.coo2csr(r.cuda(), m)
+    assert np.array_equal(row_ptr.cpu().numpy(), rp)
+    Am = api.CsrMatrix(m, n, row_ptr, c.cuda(), vals.cuda())
+    x = G.uniform((n,), -1, 1, dtype=torch.float64, seed=3)
+    y = torch.zeros(m, dtype=torch.float64, device="cuda")
+    api.spmv(handle, Am, api.DnVec(x.cuda()), api.DnVec(y), 1.0, 0.0)
+    torch.cuda.synchronize()
+    assert rel_l2(y.cpu().numpy(), oracle.spmv(rp, ci, v, x.numpy(), 1.0, 0.0)) <= 1e-12

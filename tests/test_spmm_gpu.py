@@ -99,7 +99,7 @@ def test_status_codes(handle):
     def call(opa=0, opb=0, b=B.d, c=Cm.d, ct=api.R_32F, alg=0):
         return lib.alphasparseSpMM(handle.h, opa, opb, C.byref(one), Am.d, b, C.byref(one), c, ct, alg, None)
     assert call() == 0
-    assert call(opa=1) == 6 and call(opb=1) == 6
+    assert call(opa=1) == 10 and call(opb=1) == 6   # transposed A: B must have A's row count
     assert call(b=api.DnMat(torch.zeros(11, 8, device="cuda")).d) == 10
     assert call(c=api.DnMat(torch.zeros(10, 4, device="cuda")).d) == 10
     assert call(ct=api.R_64F) == 6
@@ -146,3 +146,26 @@ def test_column_major_operands(handle, dtype, n):
         got = cbuf[:, :A.rows].t().cpu().numpy()
         assert np.array_equal(got, want)
         assert bool((cbuf[:, A.rows:] == 7.0).all()) and torch.equal(bbuf, b_before)
+
+
+def test_transposed_a(handle):
+    """C = alpha * A^T * B + beta * C equals the oracle on the host-transposed matrix."""
+    A = G.poisson_random(700, 900, 7.0, seed=41)
+    rp, ci, v = A.row_ptr.numpy(), A.col_idx.numpy(), A.val.numpy()
+    rows_of = np.repeat(np.arange(A.rows, dtype=np.int32), np.diff(rp).astype(np.int64))
+    order = np.argsort(ci, kind="stable")
+    t_rp = np.zeros(A.cols + 1, dtype=rp.dtype)
+    np.cumsum(np.bincount(ci, minlength=A.cols), out=t_rp[1:])
+    X = G.uniform((A.rows, 16), -1, 1, seed=42).numpy()
+    Y0 = G.uniform((A.cols, 16), -1, 1, seed=43).numpy()
+    want = oracle.spmm(t_rp, rows_of[order], v[order], X, 2.0, -1.0, Y0)
+    Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr.cuda(), A.col_idx.cuda(), A.val.cuda())
+    Y = torch.from_numpy(Y0.copy()).cuda()
+    import ctypes as C
+    al, be = C.c_float(2.0), C.c_float(-1.0)
+    B, Cm = api.DnMat(torch.from_numpy(X).cuda()), api.DnMat(Y)
+    st = api.load().alphasparseSpMM(handle.h, api.OP_T, api.OP_N, C.byref(al), Am.d, B.d, C.byref(be), Cm.d,
+                                    api.R_32F, 0, None)
+    torch.cuda.synchronize()
+    assert st == 0
+    assert np.array_equal(Y.cpu().numpy(), want)

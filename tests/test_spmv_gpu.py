@@ -235,7 +235,7 @@ def test_status_codes(handle):
     def call(op=0, a=C.byref(one), mat=Am.d, vx=x.d, b=C.byref(one), vy=y.d, ct=api.R_32F):
         return lib.alphasparseSpMV(handle.h, op, a, mat, vx, b, vy, ct, 0, None)
     assert call() == 0
-    assert call(op=api.OP_T) == 6
+    assert call(op=api.OP_T) == (0 if A.rows == A.cols else 10)   # transposed: x and y swap sizes
     assert call(a=None) == 7
     assert call(mat=None) == 7
     assert call(ct=api.R_64F) == 6
@@ -289,3 +289,40 @@ def test_coo2csr_matches_row_offsets(handle):
         torch.cuda.synchronize()
         assert np.array_equal(got.cpu().numpy(), rp)
     assert np.array_equal(api.coo2csr(d[:0], 5).cpu().numpy(), np.zeros(6, np.int32))
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("kind", ["rect_poisson", "rmat", "i64"])
+def test_transposed(handle, dtype, kind):
+    """y = alpha * A^T * x + beta * y through the transposed copy the plan builds on the device: the same
+    numbers as the library's own product with an explicitly transposed matrix (scipy-free CSR transpose on
+    the host), and as the oracle on that matrix."""
+    tdt = torch.float32 if dtype == np.float32 else torch.float64
+    if kind == "rect_poisson":
+        A = G.poisson_random(3000, 5000, 9.0, dtype=tdt, seed=21)
+    elif kind == "rmat":
+        A = G.rmat(12, 8, dtype=tdt, seed=22)
+    else:
+        A = G.laplacian_3d_7pt(20, dtype=tdt, index64=True)
+    rp, ci, v = A.row_ptr.numpy(), A.col_idx.numpy(), A.val.numpy()
+    # host transpose: stable sort of the entries by column keeps rows ascending inside a column
+    rows_of = np.repeat(np.arange(A.rows, dtype=np.int32), np.diff(rp).astype(np.int64))
+    order = np.argsort(ci, kind="stable")
+    t_ci, t_v = rows_of[order], v[order]
+    t_rp = np.zeros(A.cols + 1, dtype=rp.dtype)
+    np.cumsum(np.bincount(ci, minlength=A.cols), out=t_rp[1:])
+    x = G.uniform((A.rows,), -1, 1, dtype=tdt, seed=23).numpy()
+    y0 = G.uniform((A.cols,), -1, 1, dtype=tdt, seed=24).numpy()
+    want = oracle.spmv(t_rp, t_ci, t_v, x, 1.5, 0.5, y0)
+    Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr.cuda(), A.col_idx.cuda(), A.val.cuda())
+    y = torch.from_numpy(y0.copy()).cuda()
+    api.spmv(handle, Am, api.DnVec(torch.from_numpy(x).cuda()), api.DnVec(y), 1.5, 0.5, op=api.OP_T)
+    torch.cuda.synchronize()
+    assert rel_l2(y.cpu().numpy(), want) <= TOL[np.dtype(dtype)]
+    # the plain product still works on the same descriptor, and A's arrays are untouched
+    x2 = G.uniform((A.cols,), -1, 1, dtype=tdt, seed=25).numpy()
+    y2 = torch.zeros(A.rows, dtype=tdt, device="cuda")
+    api.spmv(handle, Am, api.DnVec(torch.from_numpy(x2).cuda()), api.DnVec(y2), 1.0, 0.0)
+    torch.cuda.synchronize()
+    assert rel_l2(y2.cpu().numpy(), oracle.spmv(rp, ci, v, x2, 1.0, 0.0)) <= TOL[np.dtype(dtype)]
+    assert np.array_equal(Am.col_idx.cpu().numpy(), ci) and np.array_equal(Am.val.cpu().numpy(), v)
