@@ -66,21 +66,38 @@ def test_order_is_stable():
     assert v.tolist() == [40, 20, 50, 10, 30]             # the two (1, 2) entries keep their file order
 
 
+def _write_random_matrix(tmp_path):
+    from library_b200 import generators as G
+    A = G.poisson_random(300, 400, 6.0, dtype=torch.float64, seed=17)
+    rp, ci, v = A.numpy()
+    rows_of = np.repeat(np.arange(A.rows), np.diff(rp))
+    perm = np.random.default_rng(0).permutation(A.nnz)     # entries in arbitrary order in the file
+    lines = [f"{rows_of[k] + 1} {ci[k] + 1} {float(v[k])!r}" for k in perm]
+    f = write(tmp_path, "p.mtx", "%%MatrixMarket matrix coordinate real general\n"
+              f"{A.rows} {A.cols} {A.nnz}\n" + "\n".join(lines) + "\n")
+    return A, f
+
+
+def test_file_round_trip(tmp_path):
+    """A matrix written entry by entry in random order comes back, after ordering, as its CSR arrays
+    (repr of a double is exact, so values match bit for bit)."""
+    A, f = _write_random_matrix(tmp_path)
+    rp, ci, v = A.numpy()
+    m, n, r, c, vals = api.read_mtx(f, torch.float64)
+    assert (m, n, len(r)) == (A.rows, A.cols, A.nnz)
+    assert np.array_equal(c.numpy(), ci) and np.array_equal(vals.numpy(), v)
+    assert np.array_equal(np.searchsorted(r.numpy(), np.arange(m + 1)), rp)
+
+
 @pytest.mark.gpu
 def test_file_to_spmv(handle, tmp_path):
     """File -> COO -> ordered -> device CSR (alphasparseXcoo2csr) -> SpMV, against the oracle."""
     import oracle
     from conftest import rel_l2
     from library_b200 import generators as G
-    A = G.poisson_random(300, 400, 6.0, dtype=torch.float64, seed=17)
+    A, f = _write_random_matrix(tmp_path)
     rp, ci, v = A.numpy()
-    rows_of = np.repeat(np.arange(A.rows), np.diff(rp))
-    perm = np.random.default_rng(0).permutation(A.nnz)     # entries in arbitrary order in the file
-    lines = [f"{rows_of[k] + 1} {ci[k] + 1} {v[k]!r}" for k in perm]
-    f = write(tmp_path, "p.mtx", "%%MatrixMarket matrix coordinate real general\n"
-              f"{A.rows} {A.cols} {A.nnz}\n" + "\n".join(lines) + "\n")
     m, n, r, c, vals = api.read_mtx(f, torch.float64)
-    assert (m, n, len(r)) == (A.rows, A.cols, A.nnz) and np.array_equal(c.numpy(), ci) and np.array_equal(vals.numpy(), v)
     row_ptr = api.coo2csr(r.cuda(), m)
     assert np.array_equal(row_ptr.cpu().numpy(), rp)
     Am = api.CsrMatrix(m, n, row_ptr, c.cuda(), vals.cuda())
