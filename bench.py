@@ -246,6 +246,9 @@ def cpu_reference_time(w, repeats, threads):
     ddt = torch.float32 if w["dtype"] in (torch.bfloat16, torch.float16) else w["dtype"]
     v = A.val.to(ddt).cpu().numpy()   # 16-bit operands are timed as the fp32 CPU kernel (the CPU path has no 16-bit types)
     kind = "reference" if (oracle.have_ref() and rp.dtype == np.int32) else "port"
+    # the reference re-reads OMP_NUM_THREADS on every call (hygon/util/thread.cpp:32-42), and a
+    # torchrun launch sets it to 1: give the CPU arm the cores it is entitled to
+    os.environ["OMP_NUM_THREADS"] = str(threads)
     if w["kind"] == "spmv":
         x = G.uniform((A.cols,), w["lo"], 1.0, dtype=ddt, seed=11).numpy()
         y0 = G.uniform((A.rows,), -1.0, 1.0, dtype=ddt, seed=12).numpy()
@@ -564,6 +567,9 @@ def run_ours(args):
 def main():
     args = parse_args()
     if args.impl == "reference":
+        # before any OpenMP runtime is loaded: a torchrun launch exports OMP_NUM_THREADS=1, and the CPU arm
+        # is meant to use every core it may run on
+        os.environ["OMP_NUM_THREADS"] = str(host_cores())
         run_reference(args)
     else:
         run_ours(args)

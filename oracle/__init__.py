@@ -124,7 +124,16 @@ def partition_rows_by_nnz(row_ptr, parts: int) -> np.ndarray:
 # ---- the reference's own code (int32 only) ---------------------------------------------
 
 def ref_set_threads(n: int) -> None:
-    ref_lib().ref_set_threads(C.c_int(n))
+    """Threads of the reference's OpenMP regions: its own setting, the environment variable it re-reads
+    on every call (hygon/util/thread.cpp:32-42) and the OpenMP runtime's default (a torchrun launch
+    starts the process with OMP_NUM_THREADS=1)."""
+    os.environ["OMP_NUM_THREADS"] = str(n)
+    lib = ref_lib()
+    lib.ref_set_threads(C.c_int(n))
+    try:
+        lib.omp_set_num_threads(C.c_int(n))   # resolved through the library's dependency on libgomp
+    except AttributeError:
+        pass
 
 
 def ref_threads() -> int:
