@@ -1121,10 +1121,11 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
     sb = sb >= 8 ? 8 : (sb >= 4 ? 4 : (sb >= 2 ? 2 : 0));
     if (sb >= 2) {
       const size_t smem = fixed + (size_t)sb * (b_stage + TC_A_BYTES);
-      static size_t attr_p = 0;
-      if (smem > attr_p) {
+      static size_t attr_p[64] = {0};  // the attribute belongs to the device: remembered per device
+      size_t& set_p = attr_p[h->device & 63];
+      if (smem > set_p) {
         ASP_CUDA(cudaFuncSetAttribute(spmm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_p = smem;
+        set_p = smem;
       }
       int64_t g = impl(h)->sm_count;
       if (g > tp->blocks) g = tp->blocks;
@@ -1148,10 +1149,11 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
     }
   }
   const size_t smem = 2 * TC_A_BYTES + TC_BSTAGES * b_stage + (TC_CAP + 8) * 6 + TC_MAXCH * 4 + 128 + 1024;
-  static size_t attr_bytes = 0;
-  if (smem > attr_bytes) {
+  static size_t attr_bytes[64] = {0};
+  size_t& set_b = attr_bytes[h->device & 63];
+  if (smem > set_b) {
     ASP_CUDA(cudaFuncSetAttribute(spmm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_bytes = smem;
+    set_b = smem;
   }
   spmm_tc_kernel<<<(unsigned)tp->blocks, TC_THREADS, smem, h->stream>>>(
       tm, A->const_row_data, A->const_col_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
