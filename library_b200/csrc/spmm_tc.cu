@@ -1111,8 +1111,8 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
       p->max_block_nnz + 8 < (int64_t)(1u << (32 - TC_SRC_SHIFT))) {
     // one CTA per SM; whatever shared memory the fixed parts leave goes to B stages
     const size_t fixed = TCP_CSR * (size_t)(TC_CAP + 8) * 6 + TCP_CSR * TC_MAXCH * 8 + 4 * 32 * 33 * 4 + 16 + 1024 + 1024;
-    const size_t budget = impl(h)->smem_optin ? impl(h)->smem_optin : 232448;
-    int sb = (int)((budget - fixed) / (b_stage + TC_A_BYTES));
+    const size_t smem_max = impl(h)->smem_optin ? impl(h)->smem_optin : 232448;
+    int sb = (int)((smem_max - fixed) / (b_stage + TC_A_BYTES));
     // Ring depth 8, 4 (what fits at N = 128) or 2 (N = 256): the kernel's waits by parity need a
     // stage to come back to the same builder group (depth a multiple or a divisor of the number of
     // groups) and, for two MMA issuers, an even depth.
