@@ -194,7 +194,11 @@ spmm_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   const int grp = tid / LN;
   const int64_t r0 = (int64_t)blockIdx.x * RB;
   const int nr = (int)(r0 + RB < rows ? RB : rows - r0);
-  const int64_t c0 = ((int64_t)blockIdx.y * LN + lane) * VN;
+  // A lane holds VN columns as PK packs of VP (one 16-byte load each); pack p of the lanes of a row is
+  // contiguous in memory: columns slab + p*LN*VP + lane*VP.
+  constexpr int VP = (sizeof(T) == 4 && VN == 8) ? 4 : VN;
+  constexpr int PK = VN / VP;
+  const int64_t c0 = (int64_t)blockIdx.y * LN * VN + (int64_t)lane * VP;
   const bool col_ok = c0 < n;
   const int64_t e0 = (int64_t)rp[r0], e1 = (int64_t)rp[r0 + nr];
   const int64_t a0 = e0 & ~(int64_t)3;
@@ -252,20 +256,25 @@ spmm_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
     for (int v = 0; v < VN; ++v) acc[v] = T(0);
     if (beta != T(0)) {
       T c[VN];
-      load_pack<T, VN>(C + r * ldc + c0, c);
+#pragma unroll
+      for (int pk = 0; pk < PK; ++pk) load_pack<T, VP>(C + r * ldc + c0 + pk * LN * VP, *reinterpret_cast<T(*)[VP]>(c + pk * VP));
 #pragma unroll
       for (int v = 0; v < VN; ++v) acc[v] = c[v] * beta;
     }
     const T* __restrict__ Bc = B + c0;
+    auto load_row = [&](const T* src, T (&dst)[VN]) {
+#pragma unroll
+      for (int pk = 0; pk < PK; ++pk) load_pack<T, VP>(src + pk * LN * VP, *reinterpret_cast<T(*)[VP]>(dst + pk * VP));
+    };
     // Four entries per step, counted from the row's first entry, so that the groups of a warp -
     // which hold neighbouring rows - ask for neighbouring rows of B in the same instruction.
     for (; k + 4 <= e; k += 4) {
       const int q0 = s_col[k], q1 = s_col[k + 1], q2 = s_col[k + 2], q3 = s_col[k + 3];
       T b0[VN], b1[VN], b2[VN], b3[VN];
-      load_pack<T, VN>(Bc + (int64_t)q0 * ldb, b0);
-      load_pack<T, VN>(Bc + (int64_t)q1 * ldb, b1);
-      load_pack<T, VN>(Bc + (int64_t)q2 * ldb, b2);
-      load_pack<T, VN>(Bc + (int64_t)q3 * ldb, b3);
+      load_row(Bc + (int64_t)q0 * ldb, b0);
+      load_row(Bc + (int64_t)q1 * ldb, b1);
+      load_row(Bc + (int64_t)q2 * ldb, b2);
+      load_row(Bc + (int64_t)q3 * ldb, b3);
       const T a0s = alpha * s_val[k], a1s = alpha * s_val[k + 1], a2s = alpha * s_val[k + 2],
               a3s = alpha * s_val[k + 3];
 #pragma unroll
@@ -282,9 +291,9 @@ spmm_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
       const int q1 = k + 1 < e ? s_col[k + 1] : q0;
       const int q2 = k + 2 < e ? s_col[k + 2] : q0;
       T b0[VN], b1[VN], b2[VN];
-      load_pack<T, VN>(Bc + (int64_t)q0 * ldb, b0);
-      load_pack<T, VN>(Bc + (int64_t)q1 * ldb, b1);
-      load_pack<T, VN>(Bc + (int64_t)q2 * ldb, b2);
+      load_row(Bc + (int64_t)q0 * ldb, b0);
+      load_row(Bc + (int64_t)q1 * ldb, b1);
+      load_row(Bc + (int64_t)q2 * ldb, b2);
       const T a0s = alpha * s_val[k];
 #pragma unroll
       for (int v = 0; v < VN; ++v) acc[v] = fma(a0s, b0[v], acc[v]);
@@ -299,7 +308,9 @@ spmm_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
         for (int v = 0; v < VN; ++v) acc[v] = fma(a2s, b2[v], acc[v]);
       }
     }
-    store_pack<T, VN>(C + r * ldc + c0, acc);
+#pragma unroll
+    for (int pk = 0; pk < PK; ++pk)
+      store_pack<T, VP>(C + r * ldc + c0 + pk * LN * VP, *reinterpret_cast<const T(*)[VP]>(acc + pk * VP));
   }
 }
 
@@ -345,6 +356,16 @@ alphasparseStatus_t spmm_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, con
   const bool tile_ok = plan_of(A)->max_block_nnz <= (sizeof(T) == 4 ? kSpmmStageCap32 : kSpmmStageCap64) && aligned(A->const_val_data, 16) &&
                        aligned(A->const_col_data, 16) && env_int("ASP_SPMM_TMA", 1);
   if (tile_ok) {
+    if constexpr (sizeof(T) == 4) {
+      // from N = 128 on a lane keeps two 16-byte packs (half the instructions per entry and column; measured
+      // 1.50 -> 1.44 ms at N = 128, but 0.37 -> 0.51 ms at N = 32, where it is not used)
+      // (only when the lanes' packs tile N exactly: both packs of every lane are then inside the matrix)
+      const int64_t l8 = n / 8;
+      if (env_int("ASP_SPMM_WIDE", 1) && n % 8 == 0 && (l8 == 16 || (l8 >= 32 && l8 % 32 == 0))) {
+        if (l8 <= 16) return launch_tile<T, OffT, 16, 8>(h, A, B, ldb, C, ldc, alpha, beta, n);
+        return launch_tile<T, OffT, 32, 8>(h, A, B, ldb, C, ldc, alpha, beta, n);
+      }
+    }
     if (lanes <= 1) return launch_tile<T, OffT, 1, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
     if (lanes <= 2) return launch_tile<T, OffT, 2, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
     if (lanes <= 4) return launch_tile<T, OffT, 4, VN>(h, A, B, ldb, C, ldc, alpha, beta, n);
