@@ -98,15 +98,31 @@ class XWindowExchange:
         self.window = torch.empty(max(hi - lo, 0), dtype=dtype, device=device)
         self.bytes_received = sum(b - a for p, a, b in self.recvs if p != rank) * self.window.element_size()
 
+    def own_view(self) -> torch.Tensor:
+        """The part of the window that holds this rank's own elements of x (those inside the window):
+        a caller that keeps its x there (``run(own_view())``) spares the local copy of every step.
+        Element i of the view is x[max(lo, own_lo) + i]."""
+        o0, o1 = self.own_bounds[self.rank], self.own_bounds[self.rank + 1]
+        a, b = max(o0, self.lo), min(o1, self.hi)
+        return self.window[a - self.lo:max(b, a) - self.lo]
+
+    def _own_in_place(self, x_own: torch.Tensor) -> bool:
+        v = self.own_view()
+        return v.numel() > 0 and x_own.data_ptr() == v.data_ptr() and x_own.numel() == v.numel()
+
     def run(self, x_own: torch.Tensor) -> torch.Tensor:
-        """x_own = this rank's part of x.  Returns the window buffer (element i is x[lo + i]).
-        Ordered on the current stream."""
+        """x_own = this rank's part of x, or own_view() when x is kept inside the window.  Returns the
+        window buffer (element i is x[lo + i]).  Ordered on the current stream."""
         import torch.distributed as dist
         o0 = self.own_bounds[self.rank]
+        in_place = self._own_in_place(x_own)
+        if in_place:
+            o0 = max(o0, self.lo)      # the view starts at the first own element inside the window
         ops = []
         for p, a, b in self.recvs:
             if p == self.rank:
-                self.window[a - self.lo:b - self.lo].copy_(x_own[a - o0:b - o0])
+                if not in_place:
+                    self.window[a - self.lo:b - self.lo].copy_(x_own[a - o0:b - o0])
             else:
                 ops.append(dist.P2POp(dist.irecv, self.window[a - self.lo:b - self.lo], p, group=self.group))
         for p, a, b in self.sends:
@@ -116,3 +132,80 @@ class XWindowExchange:
             for r in dist.batch_isend_irecv(ops):
                 r.wait()
         return self.window
+
+
+def interior_row_range(row_ptr: torch.Tensor, col_idx: torch.Tensor, own_lo: int, own_hi: int):
+    """Rows [i0, i1) of a shard (local CSR, ascending global columns inside a row) all of whose
+    columns lie in [own_lo, own_hi): they need nothing from other ranks.  The largest such range that
+    is one contiguous run starting at the first interior row; (0, 0) when there is none.  Works on
+    host or device tensors."""
+    n = row_ptr.numel() - 1
+    if n <= 0 or col_idx.numel() == 0:
+        return 0, 0
+    rp = row_ptr.to(torch.int64)
+    empty = rp[1:] == rp[:-1]
+    first = col_idx[torch.clamp(rp[:-1], max=col_idx.numel() - 1)].to(torch.int64)
+    last = col_idx[torch.clamp(rp[1:] - 1, min=0)].to(torch.int64)
+    inside = empty | ((first >= own_lo) & (last < own_hi))
+    idx = torch.nonzero(inside).flatten()
+    if idx.numel() == 0:
+        return 0, 0
+    i0 = int(idx[0])
+    rest = torch.nonzero(~inside[i0:]).flatten()
+    i1 = i0 + (int(rest[0]) if rest.numel() else n - i0)
+    return i0, i1
+
+
+class OverlappedShardSpMV:
+    """y_local = alpha * A_local * x + beta * y_local with the halo exchange hidden behind the rows that
+    do not need it: the shard is cut into top boundary rows, interior rows and bottom boundary rows
+    (three CSR descriptors over slices of the same arrays); a step copies the rank's own part of x into
+    the window, starts the point-to-point exchange on a side stream, multiplies the interior rows on
+    the compute stream meanwhile, then waits for the halo and multiplies the boundary rows."""
+
+    def __init__(self, handle: api.Handle, shard: api.CsrMatrix, exchange: XWindowExchange, cols: int,
+                 compute_stream: torch.cuda.Stream):
+        self.h, self.ex, self.stream = handle, exchange, compute_stream
+        self.comm = torch.cuda.Stream()
+        o0, o1 = exchange.own_bounds[exchange.rank], exchange.own_bounds[exchange.rank + 1]
+        i0, i1 = interior_row_range(shard.row_ptr, shard.col_idx, o0, o1)
+        self.i0, self.i1, self.rows = i0, i1, shard.rows
+        self.parts = []                       # (row_begin, row_end, CsrMatrix), interior first
+        for (a, b) in ((i0, i1), (0, i0), (i1, shard.rows)):
+            if b <= a:
+                continue
+            k0, k1 = int(shard.row_ptr[a]), int(shard.row_ptr[b])
+            rp = api.rebase_row_offsets(handle, shard.row_ptr, a, b, shard.row_ptr.dtype)
+            m = api.CsrMatrix(b - a, cols, rp, shard.col_idx[k0:k1], shard.val[k0:k1])
+            m.analyse(handle)
+            self.parts.append((a, b, m))
+        self.xd = api.DnVecWindow(exchange.window, cols, exchange.lo)
+
+    def step(self, x_own: torch.Tensor, y: torch.Tensor, alpha=1.0, beta=0.0):
+        import torch.distributed as dist
+        ex = self.ex
+        o0 = ex.own_bounds[ex.rank]
+        in_place = ex._own_in_place(x_own)
+        if in_place:
+            o0 = max(o0, ex.lo)
+        with torch.cuda.stream(self.stream):
+            for p, a, b in ex.recvs:          # the own part first: the interior rows read only this
+                if p == ex.rank and not in_place:
+                    ex.window[a - ex.lo:b - ex.lo].copy_(x_own[a - o0:b - o0])
+        self.comm.wait_stream(self.stream)
+        with torch.cuda.stream(self.comm):
+            ops = [dist.P2POp(dist.irecv, ex.window[a - ex.lo:b - ex.lo], p, group=ex.group)
+                   for p, a, b in ex.recvs if p != ex.rank]
+            ops += [dist.P2POp(dist.isend, x_own[a - o0:b - o0], p, group=ex.group)
+                    for p, a, b in ex.sends if p != ex.rank]
+            if ops:
+                for r in dist.batch_isend_irecv(ops):
+                    r.wait()
+        with torch.cuda.stream(self.stream):
+            first = True
+            for a, b, m in self.parts:
+                if not first or not (a == self.i0 and b == self.i1):
+                    self.stream.wait_stream(self.comm)      # boundary rows need the halo
+                api.spmv(self.h, m, self.xd, api.DnVec(y[a:b]), alpha, beta)
+                first = False
+        x_own.record_stream(self.comm)

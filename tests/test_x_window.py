@@ -72,6 +72,12 @@ def _cpu_worker(rank, world, port, out_dir, kind):
     ex = XWindowExchange(b, cmin, cmax, rank, world, torch.float64, "cpu")
     win = ex.run(torch.from_numpy(x[r0:r1].copy()))          # this rank holds only its own part of x
     assert np.array_equal(win.numpy(), x[ex.lo:ex.hi])
+    # the same with x kept inside the window (no local copy): only the halo is filled in
+    ex.window.fill_(float("nan"))
+    xv = ex.own_view()
+    a = max(ex.lo, r0)
+    xv.copy_(torch.from_numpy(x[a:a + xv.numel()].copy()))
+    assert np.array_equal(ex.run(xv).numpy(), x[ex.lo:ex.hi])
     # the oracle indexes x from 0: place the window in a vector of NaN so that any read outside it shows
     xw = np.full(A.cols, np.nan)
     xw[ex.lo:ex.hi] = win.numpy()
@@ -98,6 +104,26 @@ def test_window_exchange_on_cpu_ranks(tmp_path, world, kind):
     if kind == "banded":
         # a rank of the 48-wide grid needs at most one grid line (plus alignment slack) per neighbour
         assert max(recv) <= 2 * (48 + 32) * 8
+
+
+def test_interior_row_range():
+    """Rows whose columns all lie in the rank's own part of x need no halo."""
+    from library_b200 import generators as G
+    from library_b200.sharding import interior_row_range
+    A = G.laplacian_2d_5pt(16)                         # 256 rows, grid lines of 16
+    rp, ci = A.row_ptr, A.col_idx
+    r0, r1 = 64, 128
+    k0, k1 = int(rp[r0]), int(rp[r1])
+    local = rp[r0:r1 + 1] - rp[r0]
+    assert interior_row_range(local, ci[k0:k1], 64, 128) == (16, 48)     # first and last grid line reach out
+    assert interior_row_range(local, ci[k0:k1], 0, 256) == (0, 64)
+    assert interior_row_range(local, ci[k0:k1], 0, 10) == (0, 0)
+    # brute force on a random matrix: every row of the range is inside, the row before and after are not
+    B = G.poisson_random(200, 300, 4.0, seed=8)
+    i0, i1 = interior_row_range(B.row_ptr, B.col_idx, 20, 280)
+    rp, ci = B.row_ptr.numpy(), B.col_idx.numpy()
+    inside = [all(20 <= c < 280 for c in ci[rp[r]:rp[r + 1]]) for r in range(200)]
+    assert all(inside[i0:i1]) and (i0 == 0 or not inside[i0 - 1] or i0 == inside.index(True)) and (i1 == 200 or not inside[i1])
 
 
 @pytest.mark.gpu
@@ -147,10 +173,31 @@ def _gpu_worker(rank, world, port, out_dir):
     Aloc, (r0, r1) = shard_csr(h, A.rows, A.cols, A.row_ptr, A.col_idx, A.val, rank, world)
     cmin, cmax = api.column_range(h, Aloc.col_idx)
     ex = XWindowExchange(bounds, cmin, cmax, rank, world, torch.float64, torch.device("cuda", rank))
-    win = ex.run(x[r0:r1].clone())
+    x_own = x[r0:r1].clone()
+    win = ex.run(x_own)
     y = torch.zeros(r1 - r0, dtype=torch.float64, device="cuda")
     api.spmv(h, Aloc, api.DnVecWindow(win, A.cols, ex.lo), api.DnVec(y), 1.0, 0.0)
     torch.cuda.synchronize()
+    # the same product with the exchange hidden behind the interior rows (three calls per step)
+    from library_b200.sharding import OverlappedShardSpMV
+    ex.window.fill_(float("nan"))
+    stream = torch.cuda.Stream()
+    h.set_stream(stream.cuda_stream)
+    ov = OverlappedShardSpMV(h, Aloc, ex, A.cols, stream)
+    assert ov.i1 > ov.i0 and (ov.i0 > 0 or ov.i1 < Aloc.rows)      # a slab's first or last grid plane reaches out
+    y2 = torch.full_like(y, 5.0)
+    for _ in range(3):
+        ov.step(x_own, y2, 1.0, 0.0)
+    torch.cuda.synchronize()
+    assert torch.allclose(y2, y, rtol=1e-13, atol=1e-13)
+    # x kept inside the window: no local copy, only the halo moves
+    ex.window.fill_(float("nan"))
+    xv = ex.own_view()
+    xv.copy_(x_own[max(ex.lo - r0, 0):max(ex.lo - r0, 0) + xv.numel()])
+    y3 = torch.full_like(y, 6.0)
+    ov.step(xv, y3, 1.0, 0.0)
+    torch.cuda.synchronize()
+    assert torch.allclose(y3, y, rtol=1e-13, atol=1e-13)
     np.save(os.path.join(out_dir, f"y{rank}.npy"), y.cpu().numpy())
     np.save(os.path.join(out_dir, f"recv{rank}.npy"), np.array([ex.bytes_received]))
     dist.barrier()
