@@ -48,9 +48,11 @@ alphasparseStatus_t read_t(FILE* fp, bool mirror, int64_t m, int64_t n, int64_t 
                            void** vals, int64_t* nnz) {
   std::vector<int32_t> r, c;
   std::vector<T> v;
-  r.reserve((size_t)lines * (mirror ? 2 : 1));
-  c.reserve(r.capacity());
-  v.reserve(r.capacity());
+  // the announced count comes from the file: reserve at most 64 M entries ahead, the vectors grow beyond that
+  const size_t ahead = (size_t)(lines < (1ll << 26) ? lines : (1ll << 26)) * (mirror ? 2 : 1);
+  r.reserve(ahead);
+  c.reserve(ahead);
+  v.reserve(ahead);
   std::string line;
   for (int64_t i = 0; i < lines; ++i) {
     if (!next_data_line(fp, line)) return ALPHA_SPARSE_STATUS_INVALID_VALUE;  // fewer entries than announced
@@ -150,9 +152,14 @@ alphasparseStatus_t alphasparseReadMtxCoo(const char* file, int64_t* rows, int64
       (!next_data_line(fp, line) || sscanf(line.c_str(), "%lld %lld %lld", &m, &n, &lines) != 3 || m < 0 || n < 0 ||
        lines < 0 || m >= (1ll << 31) || n >= (1ll << 31)))
     st = ALPHA_SPARSE_STATUS_INVALID_VALUE;
-  if (st == ALPHA_SPARSE_STATUS_SUCCESS)
-    st = valueType == ALPHA_R_32F ? read_t<float>(fp, mirror, m, n, lines, row_index, col_index, values, nnz)
-                                  : read_t<double>(fp, mirror, m, n, lines, row_index, col_index, values, nnz);
+  if (st == ALPHA_SPARSE_STATUS_SUCCESS) {
+    try {  // no C++ exception may cross the C boundary
+      st = valueType == ALPHA_R_32F ? read_t<float>(fp, mirror, m, n, lines, row_index, col_index, values, nnz)
+                                    : read_t<double>(fp, mirror, m, n, lines, row_index, col_index, values, nnz);
+    } catch (...) {
+      st = ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+  }
   fclose(fp);
   if (st == ALPHA_SPARSE_STATUS_SUCCESS) {
     *rows = m;
@@ -165,9 +172,13 @@ alphasparseStatus_t alphasparseCooOrder(int64_t nnz, int32_t* row_index, int32_t
                                         alphasparseDataType valueType) {
   if (nnz < 0) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
   if (nnz > 0 && (!row_index || !col_index || !values)) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
-  if (valueType == ALPHA_R_32F) order_t<float>(nnz, row_index, col_index, (float*)values);
-  else if (valueType == ALPHA_R_64F) order_t<double>(nnz, row_index, col_index, (double*)values);
-  else return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  try {
+    if (valueType == ALPHA_R_32F) order_t<float>(nnz, row_index, col_index, (float*)values);
+    else if (valueType == ALPHA_R_64F) order_t<double>(nnz, row_index, col_index, (double*)values);
+    else return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  } catch (...) {
+    return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+  }
   return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
