@@ -1,0 +1,112 @@
+"""The configurations at their full sizes, checked through properties that need no CPU oracle run:
+
+* checksum: sum(y) = (column sums of A) . x, with the column sums formed by torch in float64
+  (an independent scatter-add, not a kernel of the library);
+* linearity: A (a x1 + x2) = a A x1 + A x2;
+* the two SpMV kernel families agree;
+* analytic: the 7-point Laplacian (diagonal 6, off-diagonals -1) times the vector of ones is 0 on
+  interior grid points and the number of missing neighbours on the boundary.
+
+Sizes: Poisson(16) 4,194,304 rows; R-MAT scale 22; 27-point stencil 128^3 with N = 32 (fp32) and
+N = 128 (bf16, tcgen05); Laplacian 512^3 with 64-bit row offsets (937,951,232 entries, ~15 GB).
+"""
+import os
+
+import pytest
+import torch
+
+from library_b200 import api
+from library_b200 import generators as G
+
+pytestmark = pytest.mark.gpu
+
+
+def col_sums(A, dtype=torch.float64):
+    cs = torch.zeros(A.cols, dtype=dtype, device=A.val.device)
+    cs.index_add_(0, A.col_idx.long(), A.val.to(dtype))
+    return cs
+
+
+def rel(a, b):
+    return float(abs(a - b) / max(abs(b), 1e-300))
+
+
+@pytest.mark.parametrize("kind", ["poisson16", "rmat22"])
+def test_spmv_full_size_properties(handle, kind, monkeypatch):
+    A = (G.poisson_random(4194304, 4194304, 16.0, device="cuda", seed=2) if kind == "poisson16"
+         else G.rmat(22, 16, device="cuda", seed=3))
+    Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr, A.col_idx, A.val)
+    x1 = G.uniform((A.cols,), -1, 1, device="cuda", seed=11)
+    x2 = G.uniform((A.cols,), -1, 1, device="cuda", seed=12)
+    cs = col_sums(A)
+    ys = {}
+    for variant in ("merge", "binned"):
+        monkeypatch.setenv("ASP_SPMV_VARIANT", variant)
+        y = torch.zeros(A.rows, device="cuda")
+        api.spmv(handle, Am, api.DnVec(x1), api.DnVec(y), 1.0, 0.0)
+        torch.cuda.synchronize()
+        ys[variant] = y
+        # checksum against the independent column sums; the terms have mixed signs, so the error is
+        # measured against the sum of magnitudes
+        scale = float((cs.abs() * x1.double().abs()).sum())
+        assert abs(float(y.double().sum()) - float((cs * x1.double()).sum())) <= 1e-6 * scale
+    d = (ys["merge"].double() - ys["binned"].double()).norm() / ys["binned"].double().norm()
+    assert float(d) <= 1e-6
+    monkeypatch.setenv("ASP_SPMV_VARIANT", "merge")
+    y2 = torch.zeros(A.rows, device="cuda")
+    y12 = torch.zeros(A.rows, device="cuda")
+    api.spmv(handle, Am, api.DnVec(x2), api.DnVec(y2), 1.0, 0.0)
+    api.spmv(handle, Am, api.DnVec(0.5 * x1 + x2), api.DnVec(y12), 1.0, 0.0)
+    torch.cuda.synchronize()
+    lin = (y12.double() - (0.5 * ys["merge"].double() + y2.double())).norm() / y12.double().norm()
+    assert float(lin) <= 1e-5
+    assert Am.plan(handle)[0]["device_error"] == 0
+
+
+def test_laplacian_512_cubed_times_ones(handle):
+    if torch.cuda.mem_get_info()[0] < 60e9:
+        pytest.skip("needs about 40 GB of free device memory")
+    n = 512
+    A = G.laplacian_3d_7pt(n, dtype=torch.float64, device="cuda", index64=True)
+    assert A.nnz == 7 * n ** 3 - 6 * n ** 2 and A.row_ptr.dtype == torch.int64
+    Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr, A.col_idx, A.val)
+    x = torch.ones(A.cols, dtype=torch.float64, device="cuda")
+    y = torch.full((A.rows,), 7.0, dtype=torch.float64, device="cuda")
+    api.spmv(handle, Am, api.DnVec(x), api.DnVec(y), 1.0, 0.0)
+    torch.cuda.synchronize()
+    # 6 minus the number of neighbours = faces of the cube the grid point lies on; exact in floating point
+    y3 = y.view(n, n, n)
+    assert float(y3[1:-1, 1:-1, 1:-1].abs().max()) == 0.0
+    idx = torch.arange(n, device="cuda")
+    on = ((idx == 0) | (idx == n - 1)).double()
+    want = on.view(n, 1, 1) + on.view(1, n, 1) + on.view(1, 1, n)
+    assert torch.equal(y3, want)
+    assert Am.plan(handle)[0]["device_error"] == 0
+
+
+def test_spmm_stencil_128_cubed_checksum(handle):
+    A = G.stencil_3d_27pt(128, device="cuda", seed=4)
+    assert A.nnz == 382 ** 3
+    cs = col_sums(A)
+    Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr, A.col_idx, A.val)
+    X = G.uniform((A.cols, 32), -1, 1, device="cuda", seed=21)
+    Y = torch.zeros(A.rows, 32, device="cuda")
+    api.spmm(handle, Am, api.DnMat(X), api.DnMat(Y), 1.0, 0.0)
+    torch.cuda.synchronize()
+    got = Y.double().sum(dim=0)                       # per column of Y: sum over rows
+    want = cs @ X.double()
+    scale = cs.abs() @ X.double().abs()
+    assert bool(((got - want).abs() <= 1e-6 * scale).all())
+    # bf16 operands on the tensor-core kernel, N = 128
+    Ab = G.Csr(A.rows, A.cols, A.row_ptr, A.col_idx, A.val.to(torch.bfloat16))
+    csb = col_sums(Ab)
+    Xb = G.uniform((A.cols, 128), -1, 1, device="cuda", seed=22).to(torch.bfloat16)
+    Yb = torch.zeros(A.rows, 128, device="cuda")
+    Amb = api.CsrMatrix(A.rows, A.cols, Ab.row_ptr, Ab.col_idx, Ab.val)
+    api.spmm(handle, Amb, api.DnMat(Xb), api.DnMat(Yb), 1.0, 0.0)
+    torch.cuda.synchronize()
+    got = Yb.double().sum(dim=0)
+    want = csb @ Xb.double()
+    scale = csb.abs() @ Xb.double().abs()
+    assert bool(((got - want).abs() <= 1e-6 * scale).all())
+    assert Amb.plan(handle)[0]["device_error"] == 0
