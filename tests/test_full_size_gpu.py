@@ -84,6 +84,26 @@ def test_laplacian_512_cubed_times_ones(handle):
     assert Am.plan(handle)[0]["device_error"] == 0
 
 
+def test_more_than_2_to_31_entries(handle):
+    """A matrix whose entry count does not fit 32 bits (7-point Laplacian on 680^3: 2,198,249,600 entries,
+    fp32 values, 64-bit row offsets): the analytic result again, so every 64-bit offset path is exercised."""
+    if torch.cuda.mem_get_info()[0] < 90e9:
+        pytest.skip("needs about 60 GB of free device memory")
+    n = 680
+    A = G.laplacian_3d_7pt(n, dtype=torch.float32, device="cuda", index64=True)
+    assert A.nnz == 7 * n ** 3 - 6 * n ** 2 and A.nnz > 2 ** 31
+    Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr, A.col_idx, A.val)
+    x = torch.ones(A.cols, device="cuda")
+    y = torch.full((A.rows,), 7.0, device="cuda")
+    api.spmv(handle, Am, api.DnVec(x), api.DnVec(y), 1.0, 0.0)
+    torch.cuda.synchronize()
+    idx = torch.arange(n, device="cuda")
+    on = ((idx == 0) | (idx == n - 1)).float()
+    want = on.view(n, 1, 1) + on.view(1, n, 1) + on.view(1, 1, n)
+    assert torch.equal(y.view(n, n, n), want)
+    assert Am.plan(handle)[0]["device_error"] == 0
+
+
 def test_spmm_stencil_128_cubed_checksum(handle):
     A = G.stencil_3d_27pt(128, device="cuda", seed=4)
     assert A.nnz == 382 ** 3
