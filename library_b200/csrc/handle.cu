@@ -188,7 +188,7 @@ alphasparseStatus_t alphasparseCreateDnMat(alphasparseDnMatDescr_t* descr, int64
                                            alphasparseOrder_t order) {
   if (!descr) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
   if (rows < 0 || cols < 0) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
-  if (!values) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  if (!values && rows > 0 && cols > 0) return ALPHA_SPARSE_STATUS_INVALID_POINTER;  // an empty matrix needs no storage
   // The reference stores ld unchecked; a leading dimension shorter than a row (or column)
   // would make rows overlap, so it is rejected here.
   if (ld < (order == ALPHASPARSE_ORDER_ROW ? cols : rows)) return ALPHA_SPARSE_STATUS_INVALID_SIZE;

@@ -441,7 +441,8 @@ alphasparseStatus_t check_spmm_args(alphasparseHandle_t h, alphasparseOperation_
     return ALPHA_SPARSE_STATUS_INVALID_SIZE;
   const bool row = B->order == ALPHASPARSE_ORDER_ROW;
   if (B->ld < (row ? B->cols : B->rows) || C->ld < (row ? C->cols : C->rows)) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
-  if (!B->values || !C->values) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  if ((!B->values && B->rows > 0 && B->cols > 0) || (!C->values && C->rows > 0 && C->cols > 0))
+    return ALPHA_SPARSE_STATUS_INVALID_POINTER;
   const bool plain = (A->data_type == ALPHA_R_32F || A->data_type == ALPHA_R_64F) &&
                      B->data_type == A->data_type && C->data_type == A->data_type &&
                      computeType == A->data_type;

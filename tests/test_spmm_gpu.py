@@ -169,3 +169,24 @@ def test_transposed_a(handle):
     torch.cuda.synchronize()
     assert st == 0
     assert np.array_equal(Y.cpu().numpy(), want)
+
+
+def test_empty_inputs(handle):
+    """A matrix without entries scales C by beta; zero columns of B and C and zero rows are no-ops."""
+    dev = "cuda"
+    rows, cols, n = 300, 200, 16
+    Am = api.CsrMatrix(rows, cols, torch.zeros(rows + 1, dtype=torch.int32, device=dev),
+                       torch.zeros(0, dtype=torch.int32, device=dev), torch.zeros(0, device=dev))
+    X = torch.ones(cols, n, device=dev)
+    Y0 = G.uniform((rows, n), -1, 1, seed=6).to(dev)
+    Y = Y0.clone()
+    api.spmm(handle, Am, api.DnMat(X), api.DnMat(Y), 1.0, -2.0)
+    torch.cuda.synchronize()
+    assert torch.equal(Y, -2.0 * Y0)
+    Y = torch.full((rows, n), float("nan"), device=dev)
+    api.spmm(handle, Am, api.DnMat(X), api.DnMat(Y), 1.0, 0.0)
+    torch.cuda.synchronize()
+    assert torch.equal(Y, torch.zeros(rows, n, device=dev))
+    Az = api.CsrMatrix(0, cols, torch.zeros(1, dtype=torch.int32, device=dev),
+                       torch.zeros(0, dtype=torch.int32, device=dev), torch.zeros(0, device=dev))
+    api.spmm(handle, Az, api.DnMat(X), api.DnMat(torch.zeros(0, n, device=dev)), 1.0, 0.0)

@@ -326,3 +326,36 @@ def test_transposed(handle, dtype, kind):
     torch.cuda.synchronize()
     assert rel_l2(y2.cpu().numpy(), oracle.spmv(rp, ci, v, x2, 1.0, 0.0)) <= TOL[np.dtype(dtype)]
     assert np.array_equal(Am.col_idx.cpu().numpy(), ci) and np.array_equal(Am.val.cpu().numpy(), v)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_empty_inputs(handle, variant, monkeypatch):
+    """No entries at all (y = beta * y), no rows, one row: nothing to launch or a single tiny launch, never
+    an error."""
+    monkeypatch.setenv("ASP_SPMV_VARIANT", variant)
+    dev = "cuda"
+    # rows but no entries
+    rows, cols = 1000, 700
+    Am = api.CsrMatrix(rows, cols, torch.zeros(rows + 1, dtype=torch.int32, device=dev),
+                       torch.zeros(0, dtype=torch.int32, device=dev), torch.zeros(0, device=dev))
+    x = torch.ones(cols, device=dev)
+    y0 = G.uniform((rows,), -1, 1, seed=5).to(dev)
+    y = y0.clone()
+    api.spmv(handle, Am, api.DnVec(x), api.DnVec(y), 2.0, 0.5)
+    torch.cuda.synchronize()
+    assert torch.equal(y, 0.5 * y0)
+    y = torch.full((rows,), float("nan"), device=dev)
+    api.spmv(handle, Am, api.DnVec(x), api.DnVec(y), 2.0, 0.0)
+    torch.cuda.synchronize()
+    assert torch.equal(y, torch.zeros(rows, device=dev))
+    # no rows
+    Az = api.CsrMatrix(0, cols, torch.zeros(1, dtype=torch.int32, device=dev),
+                       torch.zeros(0, dtype=torch.int32, device=dev), torch.zeros(0, device=dev))
+    api.spmv(handle, Az, api.DnVec(x), api.DnVec(torch.zeros(0, device=dev)), 1.0, 0.0)
+    # one row, one entry
+    A1 = api.CsrMatrix(1, cols, torch.tensor([0, 1], dtype=torch.int32, device=dev),
+                       torch.tensor([699], dtype=torch.int32, device=dev), torch.tensor([3.0], device=dev))
+    y1 = torch.tensor([10.0], device=dev)
+    api.spmv(handle, A1, api.DnVec(x), api.DnVec(y1), 2.0, 1.0)
+    torch.cuda.synchronize()
+    assert float(y1[0]) == 16.0
