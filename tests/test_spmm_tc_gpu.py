@@ -120,3 +120,17 @@ def test_column_major_bf16(handle):
     api.spmm(handle, Am, Bd, Cd, 1.5, 0.5, buffer=buf)
     torch.cuda.synchronize()
     assert rel_l2(Cc.cpu().numpy(), want) <= 1e-5
+
+
+def test_matrix_without_entries_bf16(handle):
+    """No entries: C = beta * C, also on the bf16 path (no chunk, no MMA)."""
+    rows, cols, n = 300, 256, 64
+    Am = api.CsrMatrix(rows, cols, torch.zeros(rows + 1, dtype=torch.int32, device="cuda"),
+                       torch.zeros(0, dtype=torch.int32, device="cuda"),
+                       torch.zeros(0, dtype=torch.bfloat16, device="cuda"))
+    X = torch.ones(cols, n, dtype=torch.bfloat16, device="cuda")
+    Y0 = G.uniform((rows, n), -1, 1, seed=9).cuda()
+    Y = Y0.clone()
+    api.spmm(handle, Am, api.DnMat(X), api.DnMat(Y), 1.0, 0.25)
+    torch.cuda.synchronize()
+    assert torch.equal(Y, 0.25 * Y0)

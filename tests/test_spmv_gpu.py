@@ -359,3 +359,14 @@ def test_empty_inputs(handle, variant, monkeypatch):
     api.spmv(handle, A1, api.DnVec(x), api.DnVec(y1), 2.0, 1.0)
     torch.cuda.synchronize()
     assert float(y1[0]) == 16.0
+
+
+def test_transposed_without_entries(handle):
+    rows, cols = 40, 70
+    Am = api.CsrMatrix(rows, cols, torch.zeros(rows + 1, dtype=torch.int32, device="cuda"),
+                       torch.zeros(0, dtype=torch.int32, device="cuda"), torch.zeros(0, device="cuda"))
+    y0 = G.uniform((cols,), -1, 1, seed=4).cuda()
+    y = y0.clone()
+    api.spmv(handle, Am, api.DnVec(torch.ones(rows, device="cuda")), api.DnVec(y), 1.0, 3.0, op=api.OP_T)
+    torch.cuda.synchronize()
+    assert torch.equal(y, 3.0 * y0)

@@ -85,3 +85,15 @@ def test_lowp_type_combinations(handle):
         api.spmv(handle, Am, api.DnVec(x), api.DnVec(torch.zeros(A.rows, dtype=torch.float16, device="cuda")))
     with pytest.raises(api.AlphaSparseError):
         api.spmv(handle, Am, api.DnVec(x.float()), api.DnVec(torch.zeros(A.rows, device="cuda")))
+
+
+def test_lowp_without_entries(handle):
+    rows, cols = 500, 300
+    Am = api.CsrMatrix(rows, cols, torch.zeros(rows + 1, dtype=torch.int32, device="cuda"),
+                       torch.zeros(0, dtype=torch.int32, device="cuda"),
+                       torch.zeros(0, dtype=torch.float16, device="cuda"))
+    y0 = G.uniform((rows,), -1, 1, seed=4).cuda()
+    y = y0.clone()
+    api.spmv(handle, Am, api.DnVec(torch.ones(cols, dtype=torch.float16, device="cuda")), api.DnVec(y), 1.0, -1.0)
+    torch.cuda.synchronize()
+    assert torch.equal(y, -y0)
