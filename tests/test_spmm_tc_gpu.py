@@ -2,6 +2,8 @@
 of the same arithmetic.  Tolerance: relative L2 1e-2 (the stated bound for bf16 operands); the
 products are exact in fp32 and only the summation order differs, so the observed error is
 orders of magnitude smaller and is also checked against 1e-5."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -134,3 +136,45 @@ def test_matrix_without_entries_bf16(handle):
     api.spmm(handle, Am, api.DnMat(X), api.DnMat(Y), 1.0, 0.25)
     torch.cuda.synchronize()
     assert torch.equal(Y, 0.25 * Y0)
+
+
+def test_repeated_and_unsorted_columns(handle):
+    """CSR allows a column to appear twice in a row and rows in any column order.  The SIMT kernels add
+    entries in storage order whatever it is (checked against the oracle, SpMM bit for bit); the tensor-core
+    plan places one entry per tile element and walks ascending columns, so it refuses such a matrix."""
+    rng = np.random.default_rng(5)
+    rows, cols, per = 512, 256, 24
+    ci = rng.integers(0, cols, size=(rows, per)).astype(np.int32)     # repeats and no order
+    ci[:, 1] = ci[:, 0]                                                # a certain repeat in every row
+    rp = (np.arange(rows + 1) * per).astype(np.int32)
+    v = rng.standard_normal(rows * per).astype(np.float32)
+    ci = ci.reshape(-1)
+    x = rng.standard_normal(cols).astype(np.float32)
+    want = oracle.spmv(rp, ci, v, x, 1.0, 0.0)
+    Am = api.CsrMatrix(rows, cols, torch.from_numpy(rp).cuda(), torch.from_numpy(ci).cuda(), torch.from_numpy(v).cuda())
+    for variant in ("binned", "merge"):
+        os.environ["ASP_SPMV_VARIANT"] = variant
+        try:
+            y = torch.zeros(rows, device="cuda")
+            api.spmv(handle, Am, api.DnVec(torch.from_numpy(x).cuda()), api.DnVec(y), 1.0, 0.0)
+            torch.cuda.synchronize()
+        finally:
+            del os.environ["ASP_SPMV_VARIANT"]
+        assert rel_l2(y.cpu().numpy(), want) <= 1e-5
+    X = rng.standard_normal((cols, 64)).astype(np.float32)
+    Y = torch.zeros(rows, 64, device="cuda")
+    api.spmm(handle, Am, api.DnMat(torch.from_numpy(X).cuda()), api.DnMat(Y), 1.0, 0.0)
+    torch.cuda.synchronize()
+    assert np.array_equal(Y.cpu().numpy(), oracle.spmm(rp, ci, v, X, 1.0, 0.0))
+    Ab = api.CsrMatrix(rows, cols, torch.from_numpy(rp).cuda(), torch.from_numpy(ci).cuda(),
+                       torch.from_numpy(v).cuda().to(torch.bfloat16))
+    with pytest.raises(api.AlphaSparseError) as e:
+        api.spmm(handle, Ab, api.DnMat(torch.from_numpy(X).cuda().to(torch.bfloat16)), api.DnMat(Y), 1.0, 0.0)
+    assert e.value.status == 6
+    # sorted rows with one repeated column: refused as well
+    cs = np.sort(ci.reshape(rows, per), axis=1).reshape(-1)
+    Ab2 = api.CsrMatrix(rows, cols, torch.from_numpy(rp).cuda(), torch.from_numpy(cs).cuda(),
+                        torch.from_numpy(v).cuda().to(torch.bfloat16))
+    with pytest.raises(api.AlphaSparseError) as e:
+        api.spmm(handle, Ab2, api.DnMat(torch.from_numpy(X).cuda().to(torch.bfloat16)), api.DnMat(Y), 1.0, 0.0)
+    assert e.value.status == 6
