@@ -14,9 +14,12 @@
  *     plan with cudaMalloc and synchronises once);
  *   - errors come back as alphasparseStatus_t, nothing is printed, nothing exits;
  *   - beta == 0 means y / Y is written without being read.
- * Not supported (ALPHA_SPARSE_STATUS_NOT_SUPPORTED): transposed A or B, index base one,
- * formats other than CSR, column-major dense operands, value types other than
- * fp32 / fp64 (and bf16 A,X with fp32 Y for SpMM).  There is no CPU fallback.
+ * Supported beyond the plain case: opA = TRANSPOSE for SpMV and SpMM (on a transposed copy the
+ * plan builds on the device, A itself untouched), column-major B and C in SpMM (through
+ * row-major copies in the caller's buffer), fp16 / bf16 A and x with fp32 arithmetic in SpMV,
+ * bf16 A and B with fp32 C in SpMM (the tcgen05 kernel), 32- or 64-bit row offsets.
+ * Not supported (ALPHA_SPARSE_STATUS_NOT_SUPPORTED): transposed B, index base one, formats
+ * other than CSR, complex and int8 values, device pointer mode.  There is no CPU fallback.
  */
 #ifndef ALPHASPARSE_B200_H
 #define ALPHASPARSE_B200_H
@@ -295,7 +298,10 @@ alphasparseStatus_t alphasparseSpMV_clearMat(alphasparseHandle_t handle,
  *   - The CSR structure is NOT validated (validation needs scratch of its own): offsets must be
  *     non-decreasing from 0 to nnz and columns inside [0, cols).
  *   - The first call on each device looks the array's device address up once (with that device
- *     current); make that first call outside any stream capture.
+ *     current), and with CUDA's lazy module loading it may also be the moment the library's device
+ *     code - this array included - is loaded onto that GPU.  Make that first call at start-up,
+ *     before a memory pool claims the device and outside any stream capture (rows = 1, nnz = 0 is
+ *     enough); only the calls after it are free of any allocation.
  *   - All calls on a device share the one array.  Nothing in it has to be cleared between calls
  *     (every slot a call reads it has written first), but two calls whose kernels overlap on the
  *     GPU - different streams, or different host threads - race on it: keep calls on one device
@@ -375,6 +381,73 @@ alphasparseStatus_t alphasparseCreateDnVecWindow(alphasparseDnVecDescr_t* descr,
                                                  int64_t first, int64_t count,
                                                  void* window_values, alphasparseDataType data_type);
 
+/* ---- multi-GPU SpMV (extension; the reference is single-device) ----------------------- *
+ * One process (or thread) per GPU.  Every rank holds a contiguous row range of one matrix
+ * (alphasparseCsrPartitionRowsByNnz + alphasparseCsrRebaseRowOffsets; column indices stay
+ * global) and the matching part of y; x is brought into the rank's own memory through NCCL
+ * before its kernels read it.  The communicator is the caller's (an ncclComm_t passed as
+ * void*); NCCL is looked up at run time, so this library loads without it and these calls
+ * return NOT_SUPPORTED when no libnccl.so.2 can be found.  Work is ordered on handle->stream
+ * (the overlapped mode adds one high-priority stream of its own, tied in with events).
+ * Nothing here waits on the device; a failing peer shows as a status: arguments that do not
+ * match the communicator are refused before anything is enqueued, and every call ends with one
+ * non-blocking ncclCommGetAsyncError look (EXECUTION_FAILED when the communicator reports an
+ * error). */
+struct alphasparseMg;
+typedef struct alphasparseMg* alphasparseMgHandle_t;
+typedef enum {
+  ALPHASPARSE_MG_X_BROADCAST = 0,      /* x whole on rank `root`, ncclBroadcast before the product */
+  ALPHASPARSE_MG_X_ALLGATHER = 1,      /* x sharded; every rank collects the whole vector */
+  ALPHASPARSE_MG_X_WINDOW = 2,         /* x sharded; a rank receives only x[min_col, max_col] of its rows */
+  ALPHASPARSE_MG_X_WINDOW_OVERLAP = 3  /* WINDOW with the halo hidden behind the rows that need none */
+} alphasparseMgExchange_t;
+/* comm: ncclComm_t of `world` ranks in which this process is `rank` (checked); ignored when
+ * world == 1.  The handle's device must be the communicator's. */
+alphasparseStatus_t alphasparseMgCreate(alphasparseMgHandle_t* mg, alphasparseHandle_t handle,
+                                        void* ncclComm, int rank, int world);
+alphasparseStatus_t alphasparseMgDestroy(alphasparseMgHandle_t mg);
+/* Set-up for one shard (allocates, synchronises, collective over the communicator: every rank
+ * calls it).  matA_local: this rank's rows, column indices global, cols = length of x; fp32 or
+ * fp64.  x_bounds (HOST, world+1 ascending, x_bounds[0] = 0, x_bounds[world] = cols): rank p owns
+ * x[x_bounds[p], x_bounds[p+1]) - for a square matrix the row bounds; unused (may be NULL) for
+ * BROADCAST, where `root` names the rank that holds x. */
+alphasparseStatus_t alphasparseMgSetShard(alphasparseMgHandle_t mg, alphasparseSpMatDescr_t matA_local,
+                                          const int64_t* x_bounds, alphasparseMgExchange_t mode,
+                                          int root);
+/* y_local = alpha * A_local * x + beta * y_local.  x (DEVICE): BROADCAST - the whole vector on
+ * root (replicated in place), ignored elsewhere; other modes - this rank's own part of x, or the
+ * pointer alphasparseMgOwnView returned (then no local copy is made).  alpha, beta: HOST
+ * pointers of the matrix type.  Asynchronous. */
+alphasparseStatus_t alphasparseMgSpMV(alphasparseMgHandle_t mg, const void* alpha, const void* x,
+                                      const void* beta, void* y_local, alphasparseSpMVAlg_t alg);
+/* The exchange step alone (what alphasparseMgSpMV runs before the product in the modes without
+ * overlap), on handle->stream. */
+alphasparseStatus_t alphasparseMgExchange(alphasparseMgHandle_t mg, const void* x);
+/* Where this rank's own part of x lives inside its window buffer, for callers that keep x
+ * there: element i of *ptr is x[*first + i].  NOT_SUPPORTED when the window does not hold the
+ * whole own part (peers are sent from the caller's array then). */
+alphasparseStatus_t alphasparseMgOwnView(alphasparseMgHandle_t mg, void** ptr, int64_t* first,
+                                         int64_t* count);
+enum {
+  ASP_MG_INFO_WINDOW_LO = 0, ASP_MG_INFO_WINDOW_HI = 1, ASP_MG_INFO_BYTES_RECEIVED = 2,
+  ASP_MG_INFO_INTERIOR_BEGIN = 3, ASP_MG_INFO_INTERIOR_END = 4, ASP_MG_INFO_NUM_SENDS = 5,
+  ASP_MG_INFO_NUM_RECVS = 6, ASP_MG_INFO_MODE = 7, ASP_MG_INFO_COUNT = 8
+};
+alphasparseStatus_t alphasparseMgGetInfo(alphasparseMgHandle_t mg, int64_t* info /* ASP_MG_INFO_COUNT */);
+/* Host-only planning of the window exchange (no GPU, no NCCL): rank p owns
+ * x[own_bounds[p], own_bounds[p+1]) and needs x[windows[2p], windows[2p+1]) (nothing when the
+ * second is not larger).  Outputs, triples (peer, begin, end) in global element indices, peers
+ * ascending, the rank's own overlap listed with peer == rank: sends[3*world], recvs[3*world]. */
+alphasparseStatus_t alphasparseMgExchangePlan(int world, int rank, const int64_t* own_bounds,
+                                              const int64_t* windows, int64_t* sends, int* n_sends,
+                                              int64_t* recvs, int* n_recvs);
+/* Thin wrappers over ncclGetUniqueId / ncclCommInitRank / ncclCommDestroy of the NCCL this
+ * library resolved, for callers that have no NCCL binding of their own (id128: 128 bytes, made
+ * on one rank and handed to the others by any means). */
+alphasparseStatus_t alphasparseMgGetUniqueId(void* id128);
+alphasparseStatus_t alphasparseMgCommInitRank(void** ncclComm, int world, const void* id128, int rank);
+alphasparseStatus_t alphasparseMgCommDestroy(void* ncclComm);
+
 /* ---- the step before the path: MatrixMarket file -> COO (host) ------------------------- */
 /* cuda/test/io.cu:1227-1238 (alpha_read_coo<T>(file, &m, &n, &nnz, &row_index, &col_index,
  * &values)), MatrixMarket part (:103-184, :490-575).  Reads a coordinate file into HOST arrays
@@ -417,6 +490,8 @@ alphasparseStatus_t alphasparseCsrPlanGet(alphasparseHandle_t handle,
 /* Name of the SpMV kernel variant the last alphasparseSpMV call on this matrix ran
  * ("binned" or "merge"), and how many kernels this library has launched on the handle. */
 const char* alphasparseCsrLastVariant(alphasparseSpMatDescr_t matA);
+/* The SpMM kernel family of the last alphasparseSpMM call on this matrix. */
+const char* alphasparseCsrLastSpmmVariant(alphasparseSpMatDescr_t matA);
 int64_t alphasparseGetLaunchCount(alphasparseHandle_t handle);
 
 /* ---- timers the reference's test drivers call: handle.h:532-539, handle.cu:547-599 --- */
@@ -425,6 +500,27 @@ double get_avg_time_n(const double* times, int n);   /* outlier-filtered mean, h
 
 #ifdef __cplusplus
 } /* extern "C" */
+#include <algorithm>
+#include <vector>
+/* handle.h:532-539, cuda/util/handle.cu:556-599: the overloads the reference's drivers call. */
+inline double get_avg_time(std::vector<double> times) {
+  return get_avg_time_n(times.data(), (int)times.size());
+}
+/* Mean of the samples within 10 % of the median; the median itself when none is. */
+inline double get_avg_time_2(std::vector<double> times) {
+  if (times.empty()) return 0.0;
+  std::sort(times.begin(), times.end());
+  const size_t n = times.size();
+  const double med = n % 2 ? times[n / 2] : 0.5 * (times[n / 2 - 1] + times[n / 2]);
+  double sum = 0;
+  size_t kept = 0;
+  for (double t : times)
+    if (t >= 0.9 * med && t <= 1.1 * med) {
+      sum += t;
+      ++kept;
+    }
+  return kept ? sum / (double)kept : med;
+}
 
 /* Source compatibility with the reference's template creator
  * (cuda/format/alphasparse_create_csr.h:6-18). */

@@ -29,6 +29,9 @@ INDEX_I32, INDEX_I64 = 2, 3
 BASE_ZERO, BASE_ONE = 0, 1
 SPMV_ALG_DEFAULT, SPMV_ALG_COO, SPMV_ALG_VECTOR, SPMV_ALG_MERGE = 0, 1, 6, 9
 SPMM_ALG_DEFAULT, SPMM_CSR_ALG1, SPMM_CSR_ALG2, SPMM_CSR_ALG6 = 0, 5, 6, 10
+MG_X_BROADCAST, MG_X_ALLGATHER, MG_X_WINDOW, MG_X_WINDOW_OVERLAP = 0, 1, 2, 3
+MG_INFO_NAMES = ["window_lo", "window_hi", "bytes_received", "interior_begin", "interior_end", "num_sends",
+                 "num_recvs", "mode"]
 STAT_NAMES = ["max_len", "empty_rows", "num_short", "num_medium", "num_long", "group_lanes",
               "merge_items", "merge_tiles", "variant", "identity_short", "nnz_short", "device_error"]
 
@@ -41,9 +44,12 @@ EXPORTS = [
     "alphasparseSpMV_clear", "alphasparseSpMV_clearMat", "alphasparseSpMM",
     "alphasparseSpMM_bufferSize", "alphasparseSpMM_preprocess",
     "alphasparseCsrPartitionRowsByNnz", "alphasparseCsrRebaseRowOffsets", "alphasparseCsrPlanGet",
-    "alphasparseCsrLastVariant", "alphasparseGetLaunchCount", "get_time_us", "get_avg_time_n",
+    "alphasparseCsrLastVariant", "alphasparseCsrLastSpmmVariant", "alphasparseGetLaunchCount", "get_time_us", "get_avg_time_n",
     "alphasparseSpMVCsrNoAlloc", "alphasparseXcoo2csr", "alphasparseCsrColumnRange",
     "alphasparseCreateDnVecWindow", "alphasparseReadMtxCoo", "alphasparseFreeHost", "alphasparseCooOrder",
+    "alphasparseMgCreate", "alphasparseMgDestroy", "alphasparseMgSetShard", "alphasparseMgSpMV",
+    "alphasparseMgExchange", "alphasparseMgOwnView", "alphasparseMgGetInfo", "alphasparseMgExchangePlan",
+    "alphasparseMgGetUniqueId", "alphasparseMgCommInitRank", "alphasparseMgCommDestroy",
 ]
 
 
@@ -67,6 +73,7 @@ def load():
         for name in EXPORTS:
             getattr(lib, name)  # AttributeError if a declared symbol is not exported
         lib.alphasparseCsrLastVariant.restype = C.c_char_p
+        lib.alphasparseCsrLastSpmmVariant.restype = C.c_char_p
         lib.alphasparseGetLaunchCount.restype = C.c_int64
         lib.get_time_us.restype = C.c_double
         lib.get_avg_time_n.restype = C.c_double
@@ -259,6 +266,10 @@ def spmm(handle: Handle, A: CsrMatrix, B: DnMat, Cm: DnMat, alpha=1.0, beta=0.0,
                                   alg, buf), "alphasparseSpMM")
 
 
+def spmm_last_variant(A: CsrMatrix) -> str:
+    return load().alphasparseCsrLastSpmmVariant(A.d).decode()
+
+
 def spmm_preprocess(handle: Handle, A: CsrMatrix, B: DnMat, Cm: DnMat, alg=SPMM_ALG_DEFAULT):
     code = _dtype_code(Cm.t.dtype)
     a, b = _scalar(1.0, code), _scalar(0.0, code)
@@ -354,3 +365,101 @@ def read_mtx(path: str, dtype=torch.float32, ordered: bool = True):
         for p in (ri, ci, v):
             lib.alphasparseFreeHost(p)
     return m.value, n.value, torch.from_numpy(rows_i), torch.from_numpy(cols_i), torch.from_numpy(vals)
+
+
+# ---- multi-GPU SpMV (alphasparseMg*) ------------------------------------------------------
+
+def mg_exchange_plan(own_bounds, windows, rank: int):
+    """alphasparseMgExchangePlan (host only).  ``windows``: one (lo, hi) pair per rank.  Returns
+    (sends, recvs), lists of (peer, begin, end)."""
+    import numpy as np
+    world = len(windows)
+    ob = np.ascontiguousarray(own_bounds, dtype=np.int64)
+    w = np.ascontiguousarray(np.asarray(windows, dtype=np.int64).reshape(-1))
+    sends = np.zeros(3 * world, dtype=np.int64)
+    recvs = np.zeros(3 * world, dtype=np.int64)
+    ns, nr = C.c_int(0), C.c_int(0)
+    _check(load().alphasparseMgExchangePlan(world, rank, ob.ctypes.data_as(C.c_void_p), w.ctypes.data_as(C.c_void_p),
+                                            sends.ctypes.data_as(C.c_void_p), C.byref(ns),
+                                            recvs.ctypes.data_as(C.c_void_p), C.byref(nr)),
+           "alphasparseMgExchangePlan")
+    tri = lambda a, n: [tuple(int(v) for v in a[3 * i:3 * i + 3]) for i in range(n)]
+    return tri(sends, ns.value), tri(recvs, nr.value)
+
+
+class _DevicePointer:
+    """Lets torch view device memory it did not allocate (the window buffer inside the library)."""
+
+    def __init__(self, ptr: int, count: int, dtype: torch.dtype):
+        typestr = {torch.float32: "<f4", torch.float64: "<f8"}[dtype]
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": typestr, "data": (ptr, False),
+                                         "version": 2, "strides": None}
+
+
+class Mg:
+    """alphasparseMgHandle_t: row-sharded SpMV over an NCCL communicator of its own, created from a
+    unique id that rank 0 makes and torch.distributed hands round (any transport would do)."""
+
+    def __init__(self, handle: Handle, rank: int, world: int, group=None):
+        self.lib, self.handle, self.rank, self.world = load(), handle, rank, world
+        self.comm = C.c_void_p()
+        self.mg = C.c_void_p()
+        if world > 1:
+            import torch.distributed as dist
+            ident = (C.c_char * 128)()
+            if rank == 0:
+                _check(self.lib.alphasparseMgGetUniqueId(ident), "alphasparseMgGetUniqueId")
+            box = [bytes(ident.raw)]
+            dist.broadcast_object_list(box, src=0, group=group)
+            ident = (C.c_char * 128).from_buffer_copy(box[0])
+            _check(self.lib.alphasparseMgCommInitRank(C.byref(self.comm), world, ident, rank),
+                   "alphasparseMgCommInitRank")
+        _check(self.lib.alphasparseMgCreate(C.byref(self.mg), handle.h, self.comm, rank, world),
+               "alphasparseMgCreate")
+        self.A = None
+
+    def set_shard(self, A: CsrMatrix, x_bounds=None, mode=MG_X_WINDOW_OVERLAP, root=0):
+        import numpy as np
+        xb = None if x_bounds is None else np.ascontiguousarray(x_bounds, dtype=np.int64)
+        _check(self.lib.alphasparseMgSetShard(self.mg, A.d, None if xb is None else xb.ctypes.data_as(C.c_void_p),
+                                              mode, root), "alphasparseMgSetShard")
+        self.A = A            # keeps the arrays alive
+
+    def _scalars(self, alpha, beta):
+        code = _dtype_code(self.A.val.dtype)
+        return _scalar(alpha, code), _scalar(beta, code)
+
+    def spmv(self, x: torch.Tensor | None, y: torch.Tensor, alpha=1.0, beta=0.0, alg=SPMV_ALG_DEFAULT):
+        a, b = self._scalars(alpha, beta)
+        _check(self.lib.alphasparseMgSpMV(self.mg, C.byref(a), C.c_void_p(x.data_ptr() if x is not None else 0),
+                                          C.byref(b), C.c_void_p(y.data_ptr()), alg), "alphasparseMgSpMV")
+
+    def exchange(self, x: torch.Tensor | None):
+        _check(self.lib.alphasparseMgExchange(self.mg, C.c_void_p(x.data_ptr() if x is not None else 0)),
+               "alphasparseMgExchange")
+
+    def own_view(self) -> torch.Tensor:
+        """This rank's own part of x inside the library's window buffer, as a tensor."""
+        p, first, count = C.c_void_p(), C.c_int64(), C.c_int64()
+        _check(self.lib.alphasparseMgOwnView(self.mg, C.byref(p), C.byref(first), C.byref(count)),
+               "alphasparseMgOwnView")
+        return torch.as_tensor(_DevicePointer(p.value, count.value, self.A.val.dtype), device=self.A.val.device)
+
+    def info(self) -> dict:
+        out = (C.c_int64 * 8)()
+        _check(self.lib.alphasparseMgGetInfo(self.mg, out), "alphasparseMgGetInfo")
+        return {n: int(out[i]) for i, n in enumerate(MG_INFO_NAMES)}
+
+    def close(self):
+        if self.mg:
+            self.lib.alphasparseMgDestroy(self.mg)
+            self.mg = C.c_void_p()
+        if self.comm:
+            self.lib.alphasparseMgCommDestroy(self.comm)
+            self.comm = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -291,7 +291,7 @@ alphasparseStatus_t analyse_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, 
 
   // Per-class row lists, each in ascending row order.
   if (p->rows > 0 && !p->identity_short) {
-    ASP_CUDA(cudaMalloc(&p->bin_rows, sizeof(int32_t) * p->rows));
+    ASP_CUDA(cudaMalloc(&p->bin_rows, sizeof(int32_t) * p->rows));  // owned by the plan: freed with it on any failure
     int* d_num = nullptr;
     ASP_CUDA(cudaMalloc(&d_num, sizeof(int)));
     size_t tmp_bytes = 0;
@@ -407,6 +407,7 @@ alphasparseStatus_t transposed_of(alphasparseHandle_t h, alphasparseSpMatDescr_t
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   }
   Plan* p = plan_of(A);
+  if (p->device != h->device) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
   if (p->transposed) {
     *At = &reinterpret_cast<Transposed*>(p->transposed)->d;
     return ALPHA_SPARSE_STATUS_SUCCESS;
@@ -595,6 +596,10 @@ const char* alphasparseCsrLastVariant(alphasparseSpMatDescr_t A) {
   }
 }
 
+const char* alphasparseCsrLastSpmmVariant(alphasparseSpMatDescr_t A) {
+  return (A && A->info) ? plan_of(A)->last_spmm : "none";
+}
+
 alphasparseStatus_t alphasparseCsrPartitionRowsByNnz(alphasparseHandle_t h, int64_t rows,
                                                      const void* row_offsets,
                                                      alphasparseIndexType_t rowT, int parts,
@@ -604,8 +609,9 @@ alphasparseStatus_t alphasparseCsrPartitionRowsByNnz(alphasparseHandle_t h, int6
   if (rows < 0 || parts < 1 || parts > 4096) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
   if (rowT != ALPHA_SPARSE_INDEXTYPE_I32 && rowT != ALPHA_SPARSE_INDEXTYPE_I64)
     return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
-  int64_t* d = nullptr;
-  ASP_CUDA(cudaMalloc(&d, sizeof(int64_t) * (parts + 1)));
+  // the handle's 1 MB scratch buffer holds the bounds of up to 4096 parts: no allocation per call
+  int64_t* d = reinterpret_cast<int64_t*>(h->buffer);
+  if (!d || h->buffer_size < sizeof(int64_t) * (size_t)(parts + 1)) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
   const int g = (parts + 1 + 127) / 128;
   if (rowT == ALPHA_SPARSE_INDEXTYPE_I32)
     partition_kernel<int32_t><<<g, 128, 0, h->stream>>>((const int32_t*)row_offsets, rows, parts, d);
@@ -615,7 +621,6 @@ alphasparseStatus_t alphasparseCsrPartitionRowsByNnz(alphasparseHandle_t h, int6
   cudaError_t e = cudaMemcpyAsync(bounds, d, sizeof(int64_t) * (parts + 1), cudaMemcpyDeviceToHost,
                                   h->stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
-  cudaFree(d);
   return status_of(e);
 }
 
@@ -683,8 +688,12 @@ extern "C" alphasparseStatus_t alphasparseXcoo2csr(cudaStream_t stream, const in
   const bool o64 = rowOffsetsType == ALPHA_SPARSE_INDEXTYPE_I64;
   if (!o64 && rowOffsetsType != ALPHA_SPARSE_INDEXTYPE_I32) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
   if (!o64 && nnz >= (int64_t(1) << 31)) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
+  int dev = 0, sms = 0;  // no handle on this entry point: ask the device the stream's work will run on
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+    return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
   int64_t g = (m + 1 + 255) / 256;
-  if (g > 148 * 16) g = 148 * 16;
+  if (g > (int64_t)sms * 16) g = (int64_t)sms * 16;
   if (o64) asp::coo2csr_kernel<int64_t><<<(unsigned)g, 256, 0, stream>>>(cooRowInd, nnz, m, (int64_t*)csrRowPtr);
   else asp::coo2csr_kernel<int32_t><<<(unsigned)g, 256, 0, stream>>>(cooRowInd, nnz, m, (int32_t*)csrRowPtr);
   return asp::status_of(cudaGetLastError());

@@ -38,6 +38,9 @@ struct HandleImpl {
   int sm_count = 148;
   int64_t launches = 0;
   size_t smem_optin = 0;
+  // sustained rates estimated from the device's own attributes (clocks, SM count, bus width):
+  // what the tensor-core SpMM's density test weighs MMA work against memory traffic with
+  double bf16_flops = 1.4e15, hbm_bytes = 6.5e12;
 };
 
 // The analysis result attached to a CSR descriptor (matA->info).
@@ -58,6 +61,7 @@ struct Plan {
   int* dev_err = nullptr;             // device flag a kernel raises when a bounded wait expires
   int variant_auto = kVariantBinned;
   int last_variant = -1;
+  const char* last_spmm = "none";   // name of the SpMM kernel family the last call ran
   // SpMM
   int64_t max_block_nnz = 0;          // most entries in an aligned block of kSpmmRowBlock rows
   void* spmm_tc = nullptr;            // plan of the tcgen05 variant (spmm_tc.cu)

@@ -58,6 +58,19 @@ alphasparseStatus_t alphasparseGetHandle(alphasparseHandle_t* handle) {
   h->wavefront_size = prop.warpSize;
   impl(h)->sm_count = prop.multiProcessorCount;
   impl(h)->smem_optin = prop.sharedMemPerBlockOptin;
+  {
+    // dense bf16: 8192 flop per clock per SM on this architecture, of which a long-running kernel
+    // sustains about 0.62 under the power cap; HBM: double data rate over the bus, of which a
+    // streaming kernel sustains about 0.8
+    int sm_khz = 0, mem_khz = 0, bus_bits = 0;
+    if (cudaDeviceGetAttribute(&sm_khz, cudaDevAttrClockRate, h->device) == cudaSuccess &&
+        cudaDeviceGetAttribute(&mem_khz, cudaDevAttrMemoryClockRate, h->device) == cudaSuccess &&
+        cudaDeviceGetAttribute(&bus_bits, cudaDevAttrGlobalMemoryBusWidth, h->device) == cudaSuccess &&
+        sm_khz > 0 && mem_khz > 0 && bus_bits > 0) {
+      impl(h)->bf16_flops = 0.62 * 8192.0 * prop.multiProcessorCount * (double)sm_khz * 1e3;
+      impl(h)->hbm_bytes = 0.8 * 2.0 * (double)mem_khz * 1e3 * (bus_bits / 8.0);
+    }
+  }
   const char* layer = getenv("ALPHA_SPARSE_LAYER");
   h->layer_mode = layer ? (alphasparse_layer_mode_t)atoi(layer) : ALPHA_SPARSE_LAYER_MODE_NONE;
   if (!h->buffer) {

@@ -12,8 +12,8 @@
 //     kernel (hygon/kernel/level3/mm/gemm/gemm_csr_row.hpp:33-56), so fp32/fp64 results are
 //     reproducible and equal to that kernel's;
 //   - indices into B and C are 64-bit (the reference multiplies int32, e.g. :907-914);
-//   - column-major B / C is rejected instead of transposing the caller's buffers in place
-//     (alphasparse_spmm.cu:134-162,274-283).
+//   - column-major B / C run through row-major copies in the caller's buffer; the caller's B and C
+//     keep their layout (the reference transposes them in place, alphasparse_spmm.cu:134-162,274-283).
 #include <climits>
 #include <cstring>
 #include <type_traits>
@@ -351,11 +351,13 @@ alphasparseStatus_t spmm_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, con
   constexpr int VN = 16 / (int)sizeof(T);
   if (A->rows == 0 || n == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
   const bool vec = (n % VN == 0) && (ldb % VN == 0) && (ldc % VN == 0) && aligned(B, 16) && aligned(C, 16);
+  plan_of(A)->last_spmm = "row-block";
   if (!vec) return launch_rb<T, OffT, 32, 1>(h, A, B, ldb, C, ldc, alpha, beta, n);
   const int64_t lanes = n / VN;
   const bool tile_ok = plan_of(A)->max_block_nnz <= (sizeof(T) == 4 ? kSpmmStageCap32 : kSpmmStageCap64) && aligned(A->const_val_data, 16) &&
                        aligned(A->const_col_data, 16) && env_int("ASP_SPMM_TMA", 1);
   if (tile_ok) {
+    plan_of(A)->last_spmm = "tile";
     if constexpr (sizeof(T) == 4) {
       // from N = 128 on a lane keeps two 16-byte packs (half the instructions per entry and column; measured
       // 1.50 -> 1.44 ms at N = 128, but 0.37 -> 0.51 ms at N = 32, where it is not used)
@@ -478,6 +480,7 @@ alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t h, alphasparseOperation_
     s = analyse(h, A);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   }
+  if (plan_of(A)->device != h->device) return ALPHA_SPARSE_STATUS_INVALID_VALUE;  // the plan's arrays live on another GPU
   if (B->order == ALPHASPARSE_ORDER_COL) {
     // Column-major B and C: row-major copies in the caller's buffer (sizes: alphasparseSpMM_bufferSize),
     // the row-major kernel, and C copied back.  B and C themselves keep their layout.
@@ -501,6 +504,7 @@ alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t h, alphasparseOperation_
   if (A->data_type == ALPHA_R_16BF) {
     // bf16 operands exist only for the tensor-core variant.
     if (!spmm_tc_applicable(A, B, C)) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    plan_of(A)->last_spmm = "tcgen05";
     return spmm_tc_run(h, A, B, C, *(const float*)alpha, *(const float*)beta, false);
   }
   if (alg == ALPHASPARSE_SPMM_CSR_ALG6) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;  // needs bf16 operands

@@ -8,13 +8,16 @@
 // and rebuilds it for tcgen05:
 //   * preprocessing (device): for every block of 128 rows, the ascending list of 64-column
 //     chunks that hold at least one entry (a bitmap per row block, a scan, a fill);
-//   * the kernel: one CTA per row block.  For each chunk, the 64 x N slice of B is fetched by
-//     TMA (cp.async.bulk.tensor, 128-byte swizzle, completion on an mbarrier) while the CTA's
-//     128 threads scatter their rows' entries of that chunk into a zeroed 128 x 64 bf16 tile in
-//     shared memory; one thread then issues four tcgen05.mma (M=128, N, K=16) that accumulate
-//     into tensor memory, and tcgen05.commit releases the stage.  Three B stages keep the TMA a
-//     chunk ahead; two A tiles overlap the next chunk's scatter with the current chunk's MMAs.  The epilogue reads the fp32
-//     accumulators with tcgen05.ld and writes alpha*acc + beta*C.
+//   * the kernel (spmm_tc_persistent_kernel, the default): one persistent, warp-specialised CTA per
+//     SM walks row blocks.  Per 64-column chunk a TMA warp fetches the 64 x N slice of B
+//     (cp.async.bulk.tensor, 128-byte swizzle, completion on an mbarrier) into a ring of stages,
+//     builder warps clear a 128 x 64 bf16 tile of A in shared memory and scatter the chunk's
+//     entries into it from a per-chunk scatter list the plan holds, one issuing thread per
+//     accumulator runs four tcgen05.mma (M=128, N, K=16) into tensor memory and tcgen05.commit
+//     hands the stage back; an epilogue warp group reads the fp32 accumulators with tcgen05.ld and
+//     writes alpha*acc + beta*C while the next row block's chunks are already in the ring.
+//     spmm_tc_kernel (one CTA per row block, three B stages, two A tiles) is the simple form kept
+//     for matrices whose blocks hold more chunks than the persistent kernel's staging.
 // Every mbarrier wait is bounded; on expiry the CTA raises *err, frees its tensor memory and
 // leaves.  No TMA load here uses cluster multicast.
 #include <cuda.h>
@@ -31,6 +34,7 @@ namespace asp {
 namespace {
 
 constexpr int TC_M = 128;       // rows per CTA (the MMA's M)
+static_assert(kSpmmRowBlock == TC_M, "Plan::max_block_nnz (per kSpmmRowBlock rows) bounds a row block's scatter offsets");
 #ifndef ASP_TC_KC
 #define ASP_TC_KC 64
 #endif
@@ -1089,8 +1093,8 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
   const int n = (int)C->cols;
   // Dense enough: the MMA work over all non-empty chunks (at the sustained bf16 rate) must stay
   // within three times the time HBM needs for the algorithmic bytes.
-  const double t_mma = (double)tp->total_chunks * TC_M * TC_KC * n * 2.0 / 1.39e15;
-  const double t_hbm = ((double)A->nnz * 6.0 + (double)A->cols * n * 2.0 + (double)A->rows * n * 4.0) / 6.55e12;
+  const double t_mma = (double)tp->total_chunks * TC_M * TC_KC * n * 2.0 / impl(h)->bf16_flops;
+  const double t_hbm = ((double)A->nnz * 6.0 + (double)A->cols * n * 2.0 + (double)A->rows * n * 4.0) / impl(h)->hbm_bytes;
   if (!tp->usable || t_mma > 3.0 * t_hbm) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
   if (preprocess_only || A->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
 

@@ -844,6 +844,7 @@ alphasparseStatus_t alphasparseSpMV(alphasparseHandle_t h, alphasparseOperation_
   }
   Plan* p = plan_of(A);
   if (p->rows != A->rows || p->nnz != A->nnz || p->cols != A->cols) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+  if (p->device != h->device) return ALPHA_SPARSE_STATUS_INVALID_VALUE;  // the plan's arrays live on another GPU
   if (A->data_type == ALPHA_R_16F || A->data_type == ALPHA_R_16BF) {
     // 16-bit operands, fp32 arithmetic: the TMA-staged merge-path kernel when the plan chose merge-path
     // and the arrays can be bulk-copied, else the row-length-binned kernel of spmv_lowp.cu
@@ -970,7 +971,7 @@ extern "C" alphasparseStatus_t alphasparseSpMVCsrNoAlloc(
   // The scratch array is fixed: refuse anything that needs more tiles than it holds.
   if (rows + nnz > (int64_t)ALPHASPARSE_SPMV_NOALLOC_MAX_ITEMS) return ALPHA_SPARSE_STATUS_INVALID_SIZE;
   if (!alpha || !beta || !csrRowOffsets) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
-  if ((nnz > 0 && (!csrColInd || !csrValues)) || (cols > 0 && !x) || (rows > 0 && !y))
+  if ((nnz > 0 && (!csrColInd || !csrValues || !x)) || (rows > 0 && !y))  // x is read only through entries
     return ALPHA_SPARSE_STATUS_INVALID_POINTER;
   const bool o64 = csrRowOffsetsType == ALPHA_SPARSE_INDEXTYPE_I64;
   if (!o64 && csrRowOffsetsType != ALPHA_SPARSE_INDEXTYPE_I32) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;

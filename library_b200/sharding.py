@@ -1,13 +1,16 @@
-"""Row sharding of one CSR matrix across ranks (one process per GPU).
+"""Row sharding of one CSR matrix across ranks (one process per GPU): the harness side.
 
 Rows are split into contiguous ranges of near-equal nnz by the C ABI call
 alphasparseCsrPartitionRowsByNnz (the rule of the reference's CPU partitioner,
 hygon/util/partition.cpp:83-96, in 64-bit).  A shard keeps global column indices, its own
 rebased row offsets (32-bit when the shard's nnz allows) and the matching slices of the column
-and value arrays; y stays sharded by rows.  x is either replicated to every rank (broadcast /
-all-gather of the whole vector) or, when it is sharded like y, exchanged by column window: a rank
-receives only x[min_col, max_col] of its shard (XWindowExchange), which for a banded matrix is its
-own rows plus a halo.
+and value arrays; y stays sharded by rows.
+
+On GPUs the exchange of x and the product run behind the C ABI (alphasparseMg*, api.Mg).  What
+is left here: ``shard_csr`` (cutting one device-resident matrix into this rank's shard), and
+Python twins of the library's host-side planning - ``partition_bounds_host``, ``exchange_plan``,
+``interior_row_range`` and ``XWindowExchange`` over torch.distributed - which the CPU tests run
+on gloo ranks and compare with the library's own answers.
 """
 from __future__ import annotations
 
@@ -154,58 +157,3 @@ def interior_row_range(row_ptr: torch.Tensor, col_idx: torch.Tensor, own_lo: int
     rest = torch.nonzero(~inside[i0:]).flatten()
     i1 = i0 + (int(rest[0]) if rest.numel() else n - i0)
     return i0, i1
-
-
-class OverlappedShardSpMV:
-    """y_local = alpha * A_local * x + beta * y_local with the halo exchange hidden behind the rows that
-    do not need it: the shard is cut into top boundary rows, interior rows and bottom boundary rows
-    (three CSR descriptors over slices of the same arrays); a step copies the rank's own part of x into
-    the window, starts the point-to-point exchange on a side stream, multiplies the interior rows on
-    the compute stream meanwhile, then waits for the halo and multiplies the boundary rows."""
-
-    def __init__(self, handle: api.Handle, shard: api.CsrMatrix, exchange: XWindowExchange, cols: int,
-                 compute_stream: torch.cuda.Stream):
-        self.h, self.ex, self.stream = handle, exchange, compute_stream
-        self.comm = torch.cuda.Stream()
-        o0, o1 = exchange.own_bounds[exchange.rank], exchange.own_bounds[exchange.rank + 1]
-        i0, i1 = interior_row_range(shard.row_ptr, shard.col_idx, o0, o1)
-        self.i0, self.i1, self.rows = i0, i1, shard.rows
-        self.parts = []                       # (row_begin, row_end, CsrMatrix), interior first
-        for (a, b) in ((i0, i1), (0, i0), (i1, shard.rows)):
-            if b <= a:
-                continue
-            k0, k1 = int(shard.row_ptr[a]), int(shard.row_ptr[b])
-            rp = api.rebase_row_offsets(handle, shard.row_ptr, a, b, shard.row_ptr.dtype)
-            m = api.CsrMatrix(b - a, cols, rp, shard.col_idx[k0:k1], shard.val[k0:k1])
-            m.analyse(handle)
-            self.parts.append((a, b, m))
-        self.xd = api.DnVecWindow(exchange.window, cols, exchange.lo)
-
-    def step(self, x_own: torch.Tensor, y: torch.Tensor, alpha=1.0, beta=0.0):
-        import torch.distributed as dist
-        ex = self.ex
-        o0 = ex.own_bounds[ex.rank]
-        in_place = ex._own_in_place(x_own)
-        if in_place:
-            o0 = max(o0, ex.lo)
-        with torch.cuda.stream(self.stream):
-            for p, a, b in ex.recvs:          # the own part first: the interior rows read only this
-                if p == ex.rank and not in_place:
-                    ex.window[a - ex.lo:b - ex.lo].copy_(x_own[a - o0:b - o0])
-        self.comm.wait_stream(self.stream)
-        with torch.cuda.stream(self.comm):
-            ops = [dist.P2POp(dist.irecv, ex.window[a - ex.lo:b - ex.lo], p, group=ex.group)
-                   for p, a, b in ex.recvs if p != ex.rank]
-            ops += [dist.P2POp(dist.isend, x_own[a - o0:b - o0], p, group=ex.group)
-                    for p, a, b in ex.sends if p != ex.rank]
-            if ops:
-                for r in dist.batch_isend_irecv(ops):
-                    r.wait()
-        with torch.cuda.stream(self.stream):
-            first = True
-            for a, b, m in self.parts:
-                if not first or not (a == self.i0 and b == self.i1):
-                    self.stream.wait_stream(self.comm)      # boundary rows need the halo
-                api.spmv(self.h, m, self.xd, api.DnVec(y[a:b]), alpha, beta)
-                first = False
-        x_own.record_stream(self.comm)

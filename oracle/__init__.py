@@ -24,11 +24,17 @@ _oracle = None
 _ref = None
 
 
+def reference_root() -> str:
+    """Where a checkout of the reference project lies: $ALPHASPARSE_REFERENCE, else a directory
+    named ``reference`` beside this repository (it need not exist)."""
+    return os.environ.get("ALPHASPARSE_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
 def build(ref: bool = True) -> None:
     """Compile the restatement and, when the reference tree is present, the reference."""
     subprocess.run(["make", "-s", "-C", _HERE, "oracle"], check=True)
     if ref:
-        subprocess.run(["make", "-s", "-j8", "-C", _HERE, "ref"], check=True)
+        subprocess.run(["make", "-s", "-j8", "-C", _HERE, "ref", "REF=" + reference_root()], check=True)
 
 
 def _p(a: np.ndarray):

@@ -14,10 +14,12 @@ def pytest_configure(config):
 
 
 def pytest_sessionstart(session):
-    """A fresh checkout has no built libraries (they are not in the history): compile the CUDA library
-    and the C oracle once when nvcc / gcc are there.  A prebuilt library is used as it is."""
+    """Built libraries are not in the history: compile the CUDA library and the C oracle when nvcc /
+    gcc are there.  The build is incremental (by modification time), so a source edit can never be
+    tested against an old binary; a machine without nvcc uses the prebuilt library as it is."""
+    import shutil
     from library_b200 import build as lib_build
-    if not os.path.exists(lib_build.LIB):
+    if shutil.which(lib_build._nvcc()) or not os.path.exists(lib_build.LIB):
         lib_build.build()
     import oracle
     oracle.lib()
