@@ -24,11 +24,11 @@ STATUS_NAMES = {
 }
 OP_N, OP_T, OP_C = 0, 1, 2
 ORDER_ROW, ORDER_COL = 0, 1
-R_32F, R_64F, R_16F, R_16BF = 0, 1, 4, 5
+R_32F, R_64F, C_32F, C_64F, R_16F, R_16BF, R_8I, R_32I = 0, 1, 2, 3, 4, 5, 8, 9
 INDEX_I32, INDEX_I64 = 2, 3
 BASE_ZERO, BASE_ONE = 0, 1
 SPMV_ALG_DEFAULT, SPMV_ALG_COO, SPMV_ALG_VECTOR, SPMV_ALG_MERGE = 0, 1, 6, 9
-SPMM_ALG_DEFAULT, SPMM_CSR_ALG1, SPMM_CSR_ALG2, SPMM_CSR_ALG6 = 0, 5, 6, 10
+SPMM_ALG_DEFAULT, SPMM_CSR_ALG1, SPMM_CSR_ALG2, SPMM_CSR_ALG3, SPMM_CSR_ALG4, SPMM_CSR_ALG5, SPMM_CSR_ALG6 = 0, 5, 6, 7, 8, 9, 10
 MG_X_BROADCAST, MG_X_ALLGATHER, MG_X_WINDOW, MG_X_WINDOW_OVERLAP = 0, 1, 2, 3
 MG_INFO_NAMES = ["window_lo", "window_hi", "bytes_received", "interior_begin", "interior_end", "num_sends",
                  "num_recvs", "mode"]
@@ -87,8 +87,8 @@ def _check(st: int, where: str):
 
 
 def _dtype_code(dt: torch.dtype) -> int:
-    return {torch.float32: R_32F, torch.float64: R_64F, torch.bfloat16: R_16BF,
-            torch.float16: R_16F}[dt]
+    return {torch.float32: R_32F, torch.float64: R_64F, torch.bfloat16: R_16BF, torch.float16: R_16F,
+            torch.complex64: C_32F, torch.complex128: C_64F, torch.int8: R_8I, torch.int32: R_32I}[dt]
 
 
 def _spmv_compute_code(dt: torch.dtype) -> int:
@@ -97,6 +97,12 @@ def _spmv_compute_code(dt: torch.dtype) -> int:
 
 
 def _scalar(value, code):
+    if code == C_32F:
+        return (C.c_float * 2)(complex(value).real, complex(value).imag)
+    if code == C_64F:
+        return (C.c_double * 2)(complex(value).real, complex(value).imag)
+    if code == R_32I:
+        return C.c_int32(int(value))
     return C.c_double(value) if code == R_64F else C.c_float(value)
 
 
@@ -238,8 +244,9 @@ def spmv_buffer_size(handle: Handle, A: CsrMatrix, x: DnVec, y: DnVec, alpha=1.0
 
 def spmv(handle: Handle, A: CsrMatrix, x: DnVec, y: DnVec, alpha=1.0, beta=0.0,
          alg=SPMV_ALG_DEFAULT, buffer: torch.Tensor | None = None, op=OP_N):
-    """y = alpha*A*x + beta*y on handle's stream (asynchronous)."""
-    code = _spmv_compute_code(A.val.dtype)
+    """y = alpha*A*x + beta*y on handle's stream (asynchronous).  The compute type is the matrix type,
+    fp32 for 16-bit matrices, and y's type (int32 or fp32) for int8 matrices."""
+    code = _dtype_code(y.t.dtype) if A.val.dtype == torch.int8 else _spmv_compute_code(A.val.dtype)
     a, b = _scalar(alpha, code), _scalar(beta, code)
     buf = C.c_void_p(buffer.data_ptr()) if buffer is not None else C.c_void_p()
     _check(load().alphasparseSpMV(handle.h, op, C.byref(a), A.d, x.d, C.byref(b), y.d, code, alg, buf),

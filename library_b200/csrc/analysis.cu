@@ -392,7 +392,9 @@ void free_plan(Plan* p) {
   cudaFree(p->merge_tile_row);
   cudaFree(p->carry);
   cudaFree(p->dev_err);
+  cudaFree(p->spmm_carry);
   if (p->spmm_tc) free_spmm_tc_plan(p->spmm_tc);
+  if (p->spmm_stage) free_spmm_stage_plan(p->spmm_stage);
   if (p->transposed) free_transposed(p->transposed);
   delete p;
 }

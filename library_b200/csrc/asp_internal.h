@@ -64,7 +64,10 @@ struct Plan {
   const char* last_spmm = "none";   // name of the SpMM kernel family the last call ran
   // SpMM
   int64_t max_block_nnz = 0;          // most entries in an aligned block of kSpmmRowBlock rows
+  void* spmm_carry = nullptr;         // device, carry array of the balanced SpMM when the caller gave no buffer
+  size_t spmm_carry_bytes = 0;
   void* spmm_tc = nullptr;            // plan of the tcgen05 variant (spmm_tc.cu)
+  void* spmm_stage = nullptr;         // chunk lists of the kernel that stages B by TMA (spmm_stage.cu)
   void* transposed = nullptr;         // CSR of the transposed matrix with its own descriptor and plan (analysis.cu)
 };
 
@@ -97,6 +100,10 @@ inline size_t elem_size(alphasparseDataType t) {
     case ALPHA_R_32F: return 4;
     case ALPHA_R_64F: return 8;
     case ALPHA_R_16BF: case ALPHA_R_16F: return 2;
+    case ALPHA_C_32F: return 8;
+    case ALPHA_C_64F: return 16;
+    case ALPHA_R_8I: return 1;
+    case ALPHA_R_32I: return 4;
     default: return 0;
   }
 }
@@ -116,10 +123,29 @@ alphasparseStatus_t transposed_of(alphasparseHandle_t h, alphasparseSpMatDescr_t
 // spmm_tc.cu
 void free_spmm_tc_plan(void* p);
 
+// spmm_balanced.cu: the merge-path SpMM for skewed matrices; carry holds merge_tiles x carry_ld values
+int64_t spmm_balanced_carry_ld(int64_t n, size_t elem);
+template <typename T, typename OffT>
+alphasparseStatus_t spmm_balanced_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, const T* B, int64_t ldb, T* C,
+                                    int64_t ldc, T alpha, T beta, int64_t n, void* carry);
+
+// spmm_stage.cu: the kernel that stages B through shared memory by TMA.  *ran tells whether the product
+// qualified (and, unless prepare_only, was launched); otherwise the caller runs another kernel.
+void free_spmm_stage_plan(void* p);
+template <typename T>
+alphasparseStatus_t spmm_stage_try(alphasparseHandle_t h, alphasparseSpMatDescr_t A, const T* B, int64_t ldb, T* C,
+                                   int64_t ldc, T alpha, T beta, int64_t n, bool prepare_only, bool* ran);
+
 // spmv_lowp.cu: 16-bit A and x with fp32 arithmetic (fp16 -> fp32 y, bf16 -> bf16 y)
 bool spmv_lowp_types(alphasparseDataType a, alphasparseDataType x, alphasparseDataType y,
                      alphasparseDataType compute);
 alphasparseStatus_t spmv_lowp_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A, const Plan* p,
                                   const void* x, void* y, float alpha, float beta);
+
+
+// spmv_types.cu: complex and int8 instances of the reference's SpMV type table
+bool spmv_other_types(alphasparseDataType a, alphasparseDataType x, alphasparseDataType y, alphasparseDataType compute);
+alphasparseStatus_t spmv_other_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A, const Plan* p, const void* x,
+                                   void* y, alphasparseDataType y_type, const void* alpha, const void* beta);
 
 }  // namespace asp

@@ -136,7 +136,8 @@ alphasparseStatus_t alphasparseCreateCsr(alphasparseSpMatDescr_t* out, int64_t r
   if (rowT == ALPHA_SPARSE_INDEXTYPE_I32 && nnz >= (int64_t(1) << 31))
     return ALPHA_SPARSE_STATUS_INVALID_SIZE;
   if (base != ALPHA_SPARSE_INDEX_BASE_ZERO) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
-  if (valueType != ALPHA_R_32F && valueType != ALPHA_R_64F && valueType != ALPHA_R_16BF && valueType != ALPHA_R_16F)
+  if (valueType != ALPHA_R_32F && valueType != ALPHA_R_64F && valueType != ALPHA_R_16BF && valueType != ALPHA_R_16F &&
+      valueType != ALPHA_C_32F && valueType != ALPHA_C_64F && valueType != ALPHA_R_8I)
     return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
   auto* d = new (std::nothrow) _alphasparseSpMatDescr();
   if (!d) return ALPHA_SPARSE_STATUS_ALLOC_FAILED;

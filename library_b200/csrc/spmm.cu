@@ -315,6 +315,7 @@ spmm_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
 }
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+inline size_t round256(size_t b) { return (b + 255) & ~(size_t)255; }
 
 template <typename T, typename OffT, int LN, int VN>
 alphasparseStatus_t launch_rb(alphasparseHandle_t h, alphasparseSpMatDescr_t A, const T* B,
@@ -345,14 +346,73 @@ alphasparseStatus_t launch_tile(alphasparseHandle_t h, alphasparseSpMatDescr_t A
   return status_of(cudaGetLastError());
 }
 
+// Bytes of the balanced kernel's carry array for this matrix and N.
+inline size_t balanced_carry_bytes(alphasparseSpMatDescr_t A, int64_t n) {
+  const size_t es = elem_size(A->data_type);
+  if (es < 4) return 0;
+  const int64_t tiles = (A->rows + A->nnz + kMergeItems - 1) / kMergeItems;
+  return round256((size_t)(tiles > 0 ? tiles : 1) * (size_t)spmm_balanced_carry_ld(n, es) * es);
+}
+
+// Which kernel family a call runs.  ALG1 names the reference's row-balanced algorithm: rows stay
+// whole (tile / row-block kernels, bit-equal to the CPU path).  ALG2, ALG3 and ALG5 name its
+// element-balanced, merge-path and flat algorithms: the merge-path kernel.  Everything else
+// (DEFAULT, ALG4 "adaptive", the COO names) picks from the plan: whole rows while every 128-row
+// block fits the staging buffer - then no row is long and the blocks are even - else merge-path.
+enum SpmmFamily { kSpmmRows = 0, kSpmmBalanced = 1 };
+inline SpmmFamily family_for(const Plan* p, alphasparseSpMMAlg_t alg, bool vec, size_t elem) {
+  const char* f = getenv("ASP_SPMM_VARIANT");
+  if (!vec) return kSpmmRows;  // the balanced kernel moves 16-byte packs
+  if (f && !strcmp(f, "rows")) return kSpmmRows;
+  if (f && !strcmp(f, "balanced")) return kSpmmBalanced;
+  switch (alg) {
+    case ALPHASPARSE_SPMM_CSR_ALG1: return kSpmmRows;
+    case ALPHASPARSE_SPMM_CSR_ALG2:
+    case ALPHASPARSE_SPMM_CSR_ALG3:
+    case ALPHASPARSE_SPMM_CSR_ALG5: return kSpmmBalanced;
+    default: return p->max_block_nnz <= (elem == 4 ? kSpmmStageCap32 : kSpmmStageCap64) ? kSpmmRows : kSpmmBalanced;
+  }
+}
+
 template <typename T, typename OffT>
 alphasparseStatus_t spmm_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, const T* B, int64_t ldb,
-                           T* C, int64_t ldc, T alpha, T beta, int64_t n) {
+                           T* C, int64_t ldc, T alpha, T beta, int64_t n, alphasparseSpMMAlg_t alg, void* ext) {
   constexpr int VN = 16 / (int)sizeof(T);
   if (A->rows == 0 || n == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
   const bool vec = (n % VN == 0) && (ldb % VN == 0) && (ldc % VN == 0) && aligned(B, 16) && aligned(C, 16);
-  plan_of(A)->last_spmm = "row-block";
+  Plan* p = plan_of(A);
+  if (family_for(p, alg, vec, sizeof(T)) == kSpmmBalanced) {
+    // carry array: the caller's buffer (alphasparseSpMM_bufferSize covers it), else one the plan keeps,
+    // allocated when a product of this width is first prepared or run
+    void* carry = ext;
+    if (!carry) {
+      const size_t need = balanced_carry_bytes(A, n);
+      if (p->spmm_carry_bytes < need) {
+        ASP_CUDA(cudaStreamSynchronize(h->stream));
+        cudaFree(p->spmm_carry);
+        p->spmm_carry = nullptr;
+        p->spmm_carry_bytes = 0;
+        ASP_CUDA(cudaMalloc(&p->spmm_carry, need));
+        p->spmm_carry_bytes = need;
+      }
+      carry = p->spmm_carry;
+    }
+    p->last_spmm = "merge-path";
+    return spmm_balanced_t<T, OffT>(h, A, B, ldb, C, ldc, alpha, beta, n, carry);
+  }
+  p->last_spmm = "row-block";
   if (!vec) return launch_rb<T, OffT, 32, 1>(h, A, B, ldb, C, ldc, alpha, beta, n);
+  if (n >= env_int("ASP_SPMM_STAGE_MIN_N", 16) && env_int("ASP_SPMM_STAGE", 0)) {
+    // opt-in (measured slower than the tile kernel, see the profile notes): blocks that touch B in runs take B
+    // through shared memory by TMA, one fetch per 64-row chunk instead of one per entry
+    bool ran = false;
+    const alphasparseStatus_t s = spmm_stage_try<T>(h, A, B, ldb, C, ldc, alpha, beta, n, false, &ran);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    if (ran) {
+      p->last_spmm = "staged";
+      return s;
+    }
+  }
   const int64_t lanes = n / VN;
   const bool tile_ok = plan_of(A)->max_block_nnz <= (sizeof(T) == 4 ? kSpmmStageCap32 : kSpmmStageCap64) && aligned(A->const_val_data, 16) &&
                        aligned(A->const_col_data, 16) && env_int("ASP_SPMM_TMA", 1);
@@ -423,8 +483,6 @@ alphasparseStatus_t transpose_any(alphasparseHandle_t h, const void* src, int64_
   return status_of(cudaGetLastError());
 }
 
-inline size_t round256(size_t b) { return (b + 255) & ~(size_t)255; }
-
 alphasparseStatus_t check_spmm_args(alphasparseHandle_t h, alphasparseOperation_t opA,
                                     alphasparseOperation_t opB, const void* alpha,
                                     alphasparseSpMatDescr_t A, alphasparseDnMatDescr_t B,
@@ -492,11 +550,12 @@ alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t h, alphasparseOperation_
     Bt.ld = Ct.ld = n;
     Bt.values = externalBuffer;
     Ct.values = reinterpret_cast<unsigned char*>(externalBuffer) + round256((size_t)B->rows * n * eb);
+    void* rest = reinterpret_cast<unsigned char*>(Ct.values) + round256((size_t)C->rows * n * ec);  // the carry array's place
     s = transpose_any(h, B->values, B->ld, n, B->rows, Bt.values, n, eb);
     const bool reads_c = computeType == ALPHA_R_64F ? *(const double*)beta != 0.0 : *(const float*)beta != 0.f;
     if (s == ALPHA_SPARSE_STATUS_SUCCESS && reads_c) s = transpose_any(h, C->values, C->ld, n, C->rows, Ct.values, n, ec);
     if (s == ALPHA_SPARSE_STATUS_SUCCESS)
-      s = alphasparseSpMM(h, opA, opB, alpha, A, &Bt, beta, &Ct, computeType, alg, nullptr);
+      s = alphasparseSpMM(h, opA, opB, alpha, A, &Bt, beta, &Ct, computeType, alg, rest);
     if (s == ALPHA_SPARSE_STATUS_SUCCESS) s = transpose_any(h, Ct.values, n, C->rows, n, C->values, C->ld, ec);
     return s;
   }
@@ -511,12 +570,12 @@ alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t h, alphasparseOperation_
   const bool o64 = A->row_type == ALPHA_SPARSE_INDEXTYPE_I64;
   if (A->data_type == ALPHA_R_32F) {
     const float al = *(const float*)alpha, be = *(const float*)beta;
-    return o64 ? spmm_t<float, int64_t>(h, A, (const float*)B->values, B->ld, (float*)C->values, C->ld, al, be, n)
-               : spmm_t<float, int32_t>(h, A, (const float*)B->values, B->ld, (float*)C->values, C->ld, al, be, n);
+    return o64 ? spmm_t<float, int64_t>(h, A, (const float*)B->values, B->ld, (float*)C->values, C->ld, al, be, n, alg, externalBuffer)
+               : spmm_t<float, int32_t>(h, A, (const float*)B->values, B->ld, (float*)C->values, C->ld, al, be, n, alg, externalBuffer);
   }
   const double al = *(const double*)alpha, be = *(const double*)beta;
-  return o64 ? spmm_t<double, int64_t>(h, A, (const double*)B->values, B->ld, (double*)C->values, C->ld, al, be, n)
-             : spmm_t<double, int32_t>(h, A, (const double*)B->values, B->ld, (double*)C->values, C->ld, al, be, n);
+  return o64 ? spmm_t<double, int64_t>(h, A, (const double*)B->values, B->ld, (double*)C->values, C->ld, al, be, n, alg, externalBuffer)
+             : spmm_t<double, int32_t>(h, A, (const double*)B->values, B->ld, (double*)C->values, C->ld, al, be, n, alg, externalBuffer);
 }
 
 alphasparseStatus_t alphasparseSpMM_bufferSize(alphasparseHandle_t h, alphasparseOperation_t opA,
@@ -528,10 +587,19 @@ alphasparseStatus_t alphasparseSpMM_bufferSize(alphasparseHandle_t h, alphaspars
   if (!bufferSize) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
   alphasparseStatus_t s = check_spmm_args(h, opA, opB, alpha, A, B, beta, C, computeType);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-  *bufferSize = 256;  // no row-major kernel needs caller scratch; non-zero so cudaMalloc returns a pointer
-  if (B->order == ALPHASPARSE_ORDER_COL)  // row-major copies of B and C
-    *bufferSize = round256((size_t)B->rows * B->cols * elem_size(B->data_type)) +
-                  round256((size_t)C->rows * C->cols * elem_size(C->data_type));
+  // the carry array of the merge-path kernel (whichever kernel the call then runs), never zero so
+  // that cudaMalloc returns a pointer; with column-major operands the row-major copies of B and C first
+  const alphasparseSpMatDescr_t Aop = A;
+  size_t carry = balanced_carry_bytes(Aop, C->cols);
+  if (opA != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) {  // the product runs on the transposed matrix: cols + nnz items
+    const size_t es = elem_size(A->data_type);
+    const int64_t tiles = (A->cols + A->nnz + kMergeItems - 1) / kMergeItems;
+    if (es >= 4) carry = round256((size_t)(tiles > 0 ? tiles : 1) * (size_t)spmm_balanced_carry_ld(C->cols, es) * es);
+  }
+  *bufferSize = carry > 256 ? carry : 256;
+  if (B->order == ALPHASPARSE_ORDER_COL)
+    *bufferSize += round256((size_t)B->rows * B->cols * elem_size(B->data_type)) +
+                   round256((size_t)C->rows * C->cols * elem_size(C->data_type));
   return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
@@ -540,7 +608,7 @@ alphasparseStatus_t alphasparseSpMM_preprocess(alphasparseHandle_t h, alphaspars
                                                alphasparseSpMatDescr_t A, alphasparseDnMatDescr_t B,
                                                const void* beta, alphasparseDnMatDescr_t C,
                                                alphasparseDataType computeType,
-                                               alphasparseSpMMAlg_t, size_t* bufferSize) {
+                                               alphasparseSpMMAlg_t alg, size_t* bufferSize) {
   alphasparseStatus_t s = check_spmm_args(h, opA, opB, alpha, A, B, beta, C, computeType);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   if (opA != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) {
@@ -548,13 +616,14 @@ alphasparseStatus_t alphasparseSpMM_preprocess(alphasparseHandle_t h, alphaspars
     s = transposed_of(h, A, &At);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     return alphasparseSpMM_preprocess(h, ALPHA_SPARSE_OPERATION_NON_TRANSPOSE, opB, alpha, At, B, beta, C, computeType,
-                                      ALPHASPARSE_SPMM_ALG_DEFAULT, bufferSize);
+                                      alg, bufferSize);
   }
   if (bufferSize) {
-    *bufferSize = 256;
+    const size_t carry = balanced_carry_bytes(A, C->cols);
+    *bufferSize = carry > 256 ? carry : 256;
     if (B->order == ALPHASPARSE_ORDER_COL)
-      *bufferSize = round256((size_t)B->rows * B->cols * elem_size(B->data_type)) +
-                    round256((size_t)C->rows * C->cols * elem_size(C->data_type));
+      *bufferSize += round256((size_t)B->rows * B->cols * elem_size(B->data_type)) +
+                     round256((size_t)C->rows * C->cols * elem_size(C->data_type));
   }
   if (!A->info) {
     s = analyse(h, A);
@@ -569,6 +638,34 @@ alphasparseStatus_t alphasparseSpMM_preprocess(alphasparseHandle_t h, alphaspars
     }
     if (!spmm_tc_applicable(A, &Bt, &Ct)) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
     return spmm_tc_run(h, A, &Bt, &Ct, 0.f, 0.f, true);
+  }
+  // The merge-path kernel's carry array, so that a later alphasparseSpMM without an external buffer
+  // allocates nothing.  (Operand alignment is judged on the descriptors as they are now.)
+  {
+    Plan* p = plan_of(A);
+    const size_t es = elem_size(A->data_type);
+    const int64_t n = C->cols, vn = 16 / (int64_t)es;
+    const bool row = B->order == ALPHASPARSE_ORDER_ROW;
+    const bool vec = !row || ((n % vn == 0) && (B->ld % vn == 0) && (C->ld % vn == 0) && aligned(B->values, 16) &&
+                              aligned(C->values, 16));
+    if (row && vec && n > 0 && A->rows > 0 && family_for(p, alg, vec, es) == kSpmmRows &&
+        n >= env_int("ASP_SPMM_STAGE_MIN_N", 16) && env_int("ASP_SPMM_STAGE", 0)) {
+      bool would_run = false;  // builds the chunk lists of the staged kernel now
+      s = es == 4 ? spmm_stage_try<float>(h, A, (const float*)B->values, B->ld, (float*)C->values, C->ld, 0.f, 0.f, n, true, &would_run)
+                  : spmm_stage_try<double>(h, A, (const double*)B->values, B->ld, (double*)C->values, C->ld, 0.0, 0.0, n, true, &would_run);
+      if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    }
+    if (row && n > 0 && A->rows > 0 && family_for(p, alg, vec, es) == kSpmmBalanced) {
+      const size_t need = balanced_carry_bytes(A, n);
+      if (p->spmm_carry_bytes < need) {
+        ASP_CUDA(cudaStreamSynchronize(h->stream));
+        cudaFree(p->spmm_carry);
+        p->spmm_carry = nullptr;
+        p->spmm_carry_bytes = 0;
+        ASP_CUDA(cudaMalloc(&p->spmm_carry, need));
+        p->spmm_carry_bytes = need;
+      }
+    }
   }
   return ALPHA_SPARSE_STATUS_SUCCESS;
 }

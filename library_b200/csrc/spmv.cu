@@ -807,7 +807,11 @@ alphasparseStatus_t check_spmv_args(alphasparseHandle_t h, alphasparseOperation_
   alphasparseStatus_t s = validate_csr(A);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   if (!x->init || !y->init) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
-  if (!spmv_lowp_types(A->data_type, x->data_type, y->data_type, computeType)) {
+  // the complex and int8 instances exist for opA = N only (no transposed copy is built for them)
+  if (tr && (A->data_type == ALPHA_C_32F || A->data_type == ALPHA_C_64F || A->data_type == ALPHA_R_8I))
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  if (!spmv_lowp_types(A->data_type, x->data_type, y->data_type, computeType) &&
+      !spmv_other_types(A->data_type, x->data_type, y->data_type, computeType)) {
     if (A->data_type != ALPHA_R_32F && A->data_type != ALPHA_R_64F) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
     if (x->data_type != A->data_type || y->data_type != A->data_type || computeType != A->data_type)
       return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
@@ -845,6 +849,10 @@ alphasparseStatus_t alphasparseSpMV(alphasparseHandle_t h, alphasparseOperation_
   Plan* p = plan_of(A);
   if (p->rows != A->rows || p->nnz != A->nnz || p->cols != A->cols) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
   if (p->device != h->device) return ALPHA_SPARSE_STATUS_INVALID_VALUE;  // the plan's arrays live on another GPU
+  if (A->data_type == ALPHA_C_32F || A->data_type == ALPHA_C_64F || A->data_type == ALPHA_R_8I) {
+    p->last_variant = kVariantBinned;  // complex and int8 instances: the row-length-binned kernel of spmv_types.cu
+    return spmv_other_run(h, A, p, x->values, y->values, y->data_type, alpha, beta);
+  }
   if (A->data_type == ALPHA_R_16F || A->data_type == ALPHA_R_16BF) {
     // 16-bit operands, fp32 arithmetic: the TMA-staged merge-path kernel when the plan chose merge-path
     // and the arrays can be bulk-copied, else the row-length-binned kernel of spmv_lowp.cu
@@ -886,7 +894,8 @@ alphasparseStatus_t alphasparseSpMV_bufferSize(alphasparseHandle_t h, alphaspars
   // One carry slot per merge-path tile, in 64-bit arithmetic (the reference adds rows+nnz in
   // int, cuda/kernel/level2/alphasparse_spmv.cu:357).
   const int64_t tiles = ((A->rows > A->cols ? A->rows : A->cols) + A->nnz + kMergeItems - 1) / kMergeItems;  // either op
-  const size_t slot = elem_size(A->data_type) < 4 ? 4 : elem_size(A->data_type);  // 16-bit matrices carry in fp32
+  const size_t es_ = elem_size(A->data_type);
+  const size_t slot = es_ < 4 ? 4 : (es_ > 8 ? 8 : es_);  // 16-bit matrices carry in fp32; complex / int8 use no carries
   size_t bytes = (size_t)(tiles > 0 ? tiles : 1) * slot;
   *bufferSize = (bytes + 255) & ~(size_t)255;
   return ALPHA_SPARSE_STATUS_SUCCESS;

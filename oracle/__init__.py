@@ -91,6 +91,42 @@ def spmv(row_ptr, col_idx, val, x, alpha, beta, y0=None):
     return y
 
 
+def spmv_complex(row_ptr, col_idx, val, x, alpha, beta, y0=None):
+    """Complex y = alpha*A*x + beta*y0 (numpy complex64 / complex128 arrays, Python complex scalars)."""
+    rows = row_ptr.shape[0] - 1
+    row_ptr = np.ascontiguousarray(row_ptr)
+    col_idx = np.ascontiguousarray(col_idx, dtype=np.int32)
+    val = np.ascontiguousarray(val)
+    x = np.ascontiguousarray(x, dtype=val.dtype)
+    y = np.zeros(rows, dtype=val.dtype) if y0 is None else np.array(y0, dtype=val.dtype, copy=True)
+    tn, rt = {np.dtype(np.complex64): ("c32", np.float32), np.dtype(np.complex128): ("c64", np.float64)}[val.dtype]
+    a = np.array([complex(alpha).real, complex(alpha).imag], dtype=rt)
+    b = np.array([complex(beta).real, complex(beta).imag], dtype=rt)
+    fn = getattr(lib(), f"oracle_spmv_{tn}_" + _off_suffix(row_ptr))
+    fn.restype = None
+    fn(C.c_int64(rows), _p(row_ptr), _p(col_idx), _p(val), _p(x), _p(a), _p(b), _p(y))
+    return y
+
+
+def spmv_int8(row_ptr, col_idx, val, x, alpha, beta, y0):
+    """int8 A and x; y0's dtype (int32 or float32) selects the instance (int32 or float arithmetic)."""
+    rows = row_ptr.shape[0] - 1
+    row_ptr = np.ascontiguousarray(row_ptr)
+    col_idx = np.ascontiguousarray(col_idx, dtype=np.int32)
+    val = np.ascontiguousarray(val, dtype=np.int8)
+    x = np.ascontiguousarray(x, dtype=np.int8)
+    y = np.array(y0, copy=True)
+    if y.dtype == np.int32:
+        fn, ct = getattr(lib(), "oracle_spmv_i8_i32_" + _off_suffix(row_ptr)), C.c_int32
+    elif y.dtype == np.float32:
+        fn, ct = getattr(lib(), "oracle_spmv_i8_f32_" + _off_suffix(row_ptr)), C.c_float
+    else:
+        raise TypeError(y.dtype)
+    fn.restype = None
+    fn(C.c_int64(rows), _p(row_ptr), _p(col_idx), _p(val), _p(x), ct(alpha), ct(beta), _p(y))
+    return y
+
+
 def spmm(row_ptr, col_idx, val, X, alpha, beta, Y0=None):
     """Row-major Y = alpha*A*X + beta*Y0.  ``val``/``X`` of dtype uint16 are bf16 bit patterns
     (fp32 accumulation and fp32 Y)."""
@@ -166,6 +202,25 @@ def ref_spmv(row_ptr, col_idx, val, x, alpha, beta, y0=None, cols=None, repeats=
     if st != 0:
         raise RuntimeError(f"reference mv returned status {st}")
     return y, times
+
+
+def ref_spmv_complex(row_ptr, col_idx, val, x, alpha, beta, y0=None, cols=None):
+    """The reference's alphasparse_{c,z}_mv."""
+    rows = row_ptr.shape[0] - 1
+    cols = int(x.shape[0]) if cols is None else cols
+    row_ptr = np.ascontiguousarray(row_ptr, dtype=np.int32)
+    col_idx = np.ascontiguousarray(col_idx, dtype=np.int32)
+    val = np.ascontiguousarray(val)
+    x = np.ascontiguousarray(x, dtype=val.dtype)
+    y = np.zeros(rows, dtype=val.dtype) if y0 is None else np.array(y0, dtype=val.dtype, copy=True)
+    fn, rt = (ref_lib().ref_c_mv, np.float32) if val.dtype == np.complex64 else (ref_lib().ref_z_mv, np.float64)
+    a = np.array([complex(alpha).real, complex(alpha).imag], dtype=rt)
+    b = np.array([complex(beta).real, complex(beta).imag], dtype=rt)
+    fn.restype = C.c_int
+    st = fn(C.c_int(rows), C.c_int(cols), _p(row_ptr), _p(col_idx), _p(val), _p(x), _p(a), _p(b), _p(y))
+    if st != 0:
+        raise RuntimeError(f"reference complex mv returned status {st}")
+    return y
 
 
 def ref_spmm(row_ptr, col_idx, val, X, alpha, beta, Y0=None, repeats=1):

@@ -81,6 +81,55 @@ DEF_SPMV_F64(oracle_spmv_f64_i64, int64_t)
 DEF_SPMV_F32(oracle_spmv_f32_i32, int32_t)
 DEF_SPMV_F32(oracle_spmv_f32_i64, int64_t)
 
+/* Complex SpMV (interleaved re, im).  The reference's CPU kernels for it are assembly
+ * (hygon/kernel/level2/mv/gemv/gemv_csr.hpp:80-139 -> csrmv/gemv_csr_serial_fma_c8_u2.S,
+ * gemv_csr_serial_fma_c16_u1.S); this restatement keeps their structure - per row a sum over the
+ * entries in storage order, then y = alpha*sum + beta*y - with fused multiply-adds on the real and
+ * imaginary parts, and is checked against the compiled reference within rounding (its unrolled
+ * partial sums make the last bits differ), not bit for bit. */
+#define DEF_SPMV_CPLX(NAME, T, OFF_T, FMA)                                                 \
+  void NAME(int64_t rows, const OFF_T* row_ptr, const int32_t* col, const T* val,          \
+            const T* x, const T* alpha, const T* beta, T* y) {                             \
+    _Pragma("omp parallel for schedule(static)")                                           \
+    for (int64_t i = 0; i < rows; ++i) {                                                   \
+      T sr = 0, si = 0;                                                                    \
+      for (int64_t k = (int64_t)row_ptr[i]; k < (int64_t)row_ptr[i + 1]; ++k) {            \
+        const T ar = val[2 * k], ai = val[2 * k + 1];                                      \
+        const T xr = x[2 * (int64_t)col[k]], xi = x[2 * (int64_t)col[k] + 1];              \
+        sr = FMA(-ai, xi, FMA(ar, xr, sr));                                                \
+        si = FMA(ai, xr, FMA(ar, xi, si));                                                 \
+      }                                                                                    \
+      const T yr = y[2 * i], yi = y[2 * i + 1];                                            \
+      const T tr = FMA(-alpha[1], si, alpha[0] * sr), ti = FMA(alpha[1], sr, alpha[0] * si); \
+      const T ur = FMA(-beta[1], yi, beta[0] * yr), ui = FMA(beta[1], yr, beta[0] * yi);   \
+      y[2 * i] = tr + ur;                                                                  \
+      y[2 * i + 1] = ti + ui;                                                              \
+    }                                                                                      \
+  }
+DEF_SPMV_CPLX(oracle_spmv_c32_i32, float, int32_t, fmaf)
+DEF_SPMV_CPLX(oracle_spmv_c32_i64, float, int64_t, fmaf)
+DEF_SPMV_CPLX(oracle_spmv_c64_i32, double, int32_t, fma)
+DEF_SPMV_CPLX(oracle_spmv_c64_i64, double, int64_t, fma)
+
+/* int8 A and x.  The reference has no CPU path for these instances (its hygon backend knows s, d, c, z
+ * only), so nothing pins them beyond the arithmetic its CUDA dispatcher instantiates
+ * (cuda/kernel/level2/alphasparse_spmv.cu:276-287): int32 products and sums with int32 alpha / beta
+ * and y, or values widened to float with float alpha / beta and y.  Parity unpinned for these two. */
+#define DEF_SPMV_I8(NAME, OFF_T, TY, ACC)                                                  \
+  void NAME(int64_t rows, const OFF_T* row_ptr, const int32_t* col, const int8_t* val,     \
+            const int8_t* x, TY alpha, TY beta, TY* y) {                                   \
+    _Pragma("omp parallel for schedule(static)")                                           \
+    for (int64_t i = 0; i < rows; ++i) {                                                   \
+      TY s = 0;                                                                            \
+      for (int64_t k = (int64_t)row_ptr[i]; k < (int64_t)row_ptr[i + 1]; ++k) ACC;         \
+      y[i] = alpha * s + beta * y[i];                                                      \
+    }                                                                                      \
+  }
+DEF_SPMV_I8(oracle_spmv_i8_i32_i32, int32_t, int32_t, s += (int32_t)val[k] * (int32_t)x[col[k]])
+DEF_SPMV_I8(oracle_spmv_i8_i32_i64, int64_t, int32_t, s += (int32_t)val[k] * (int32_t)x[col[k]])
+DEF_SPMV_I8(oracle_spmv_i8_f32_i32, int32_t, float, s = fmaf((float)val[k], (float)x[col[k]], s))
+DEF_SPMV_I8(oracle_spmv_i8_f32_i64, int64_t, float, s = fmaf((float)val[k], (float)x[col[k]], s))
+
 /* Row-major SpMM, X is cols x n with leading dimension ldx, Y is rows x n with ldy. */
 #define DEF_SPMM(NAME, T, OFF_T, FMA)                                                      \
   void NAME(int64_t rows, const OFF_T* row_ptr, const int32_t* col, const T* val,          \

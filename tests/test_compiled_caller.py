@@ -99,4 +99,6 @@ def test_spmm_caller_result_equals_the_oracle(tmp_path):
     assert r.returncode == 0, r.stderr
     got = np.fromfile(tmp_path / "out.bin", dtype=np.float32).reshape(A.rows, n)
     want = oracle.spmm(rp, ci, v, B, 2.0, 0.5, C0)
-    assert np.array_equal(got, want)
+    # the caller passes CSR_ALG2 as the reference's driver does: the merge-path kernel, equal within rounding
+    from conftest import rel_l2
+    assert got.shape == want.shape and rel_l2(got, want) <= 1e-5

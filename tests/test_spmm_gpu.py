@@ -3,6 +3,8 @@
 The SIMT kernel accumulates every C element in the same order and with the same fma as the
 reference's CPU kernel, so fp32 / fp64 results are compared bit for bit as well as within the
 stated tolerance (relative L2 1e-5 fp32, 1e-12 fp64)."""
+import functools
+
 import numpy as np
 import pytest
 import torch
@@ -17,7 +19,8 @@ TOL = {np.dtype(np.float32): 1e-5, np.dtype(np.float64): 1e-12}
 MM_CASES = sorted(k for k, c in load_golden().items() if c["kind"] == "mm")
 
 
-def run_spmm(handle, rp, ci, v, X, alpha, beta, Y0, cols, ldx=None, ldy=None):
+def run_spmm(handle, rp, ci, v, X, alpha, beta, Y0, cols, ldx=None, ldy=None, alg=api.SPMM_ALG_DEFAULT,
+             use_buffer=False, want_variant=None):
     dev = "cuda"
     A = api.CsrMatrix(len(rp) - 1, cols, torch.from_numpy(rp).to(dev), torch.from_numpy(ci).to(dev),
                       torch.from_numpy(v).to(dev))
@@ -33,8 +36,15 @@ def run_spmm(handle, rp, ci, v, X, alpha, beta, Y0, cols, ldx=None, ldy=None):
         buf[:, :n] = Yt
         Yt = buf[:, :n]
     handle.use_torch_stream()
-    api.spmm(handle, A, api.DnMat(Xt), api.DnMat(Yt), alpha, beta)
+    Bd, Cd = api.DnMat(Xt), api.DnMat(Yt)
+    ext = None
+    if use_buffer:
+        ext = torch.empty(api.spmm_buffer_size(handle, A, Bd, Cd, alg), dtype=torch.uint8, device=dev)
+    api.spmm(handle, A, Bd, Cd, alpha, beta, alg=alg, buffer=ext)
     torch.cuda.synchronize()
+    if want_variant:
+        assert api.spmm_last_variant(A) == want_variant
+    assert A.plan(handle)[0]["device_error"] == 0
     if ldy:
         assert bool((buf[:, n:] == 7.0).all())  # padding untouched
     return Yt.cpu().numpy()
@@ -72,8 +82,94 @@ def test_skewed_and_long_rows(handle, n):
     X = G.uniform((A.cols, n), -1, 1, seed=72).numpy()
     Y0 = G.uniform((A.rows, n), -1, 1, seed=73).numpy()
     want = oracle.spmm(rp, ci, v, X, 1.0, 1.0, Y0)
-    got = run_spmm(handle, rp, ci, v, X, 1.0, 1.0, Y0, A.cols)
+    # ALG1 = the reference's row-balanced algorithm: rows stay whole, so the result is the oracle's bit for bit
+    got = run_spmm(handle, rp, ci, v, X, 1.0, 1.0, Y0, A.cols, alg=api.SPMM_CSR_ALG1, want_variant="row-block")
     assert np.array_equal(got, want)
+
+
+@functools.lru_cache(maxsize=None)
+def _skewed_cases():
+    rng = np.random.default_rng(5)
+    out = {"rmat": G.rmat(14, 16, seed=71)}
+    # one 30,000-entry row (15 merge-path tiles) between runs of empty rows, short rows after it
+    lens = np.concatenate([np.zeros(200, np.int64), [30000], np.zeros(3000, np.int64), rng.integers(0, 9, size=5000),
+                           [5000], np.zeros(10, np.int64)])
+    cols = 40000
+    rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    ci = np.concatenate([np.sort(rng.choice(cols, size=int(l), replace=False)) for l in lens if l]).astype(np.int32)
+    out["one_long_row"] = G.Csr(len(lens), cols, torch.from_numpy(rp), torch.from_numpy(ci),
+                                torch.from_numpy(rng.normal(size=ci.size).astype(np.float32)))
+    out["no_entries"] = G.Csr(300, 50, torch.zeros(301, dtype=torch.int32), torch.zeros(0, dtype=torch.int32),
+                              torch.zeros(0, dtype=torch.float32))
+    return out
+
+
+@pytest.mark.parametrize("case", ["rmat", "one_long_row", "no_entries"])
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("n", [4, 8, 32, 64, 128, 160])
+def test_merge_path_spmm_on_skewed_rows(handle, case, dtype, n):
+    """The load-balanced kernel (the reference's ALG2 / ALG3 / ALG5, and the default for matrices whose row
+    blocks do not fit the row kernels' staging): rows are split over lane groups and tiles, so the result
+    matches the oracle within the tolerance, not bit for bit."""
+    A = _skewed_cases()[case]
+    rp, ci, v = A.numpy()
+    v = v.astype(dtype)
+    t = torch.float32 if dtype == np.float32 else torch.float64
+    X = G.uniform((A.cols, n), -1, 1, dtype=t, seed=74).numpy()
+    Y0 = G.uniform((A.rows, n), -1, 1, dtype=t, seed=75).numpy()
+    for (alpha, beta), alg, use_buffer in (((1.0, 0.0), api.SPMM_CSR_ALG2, True), ((1.5, -0.5), api.SPMM_ALG_DEFAULT, False),
+                                           ((2.0, 1.0), api.SPMM_CSR_ALG3, False)):
+        want = oracle.spmm(rp, ci, v, X, alpha, beta, Y0)
+        variant = None if (alg == api.SPMM_ALG_DEFAULT and case == "no_entries") else "merge-path"
+        got = run_spmm(handle, rp, ci, v, X, alpha, beta, Y0, A.cols, alg=alg, use_buffer=use_buffer, want_variant=variant)
+        assert rel_l2(got, want) <= TOL[np.dtype(dtype)], (case, n, alg)
+    if n == 32:     # 64-bit row offsets and padded leading dimensions
+        want = oracle.spmm(rp, ci, v, X, 1.0, 0.0, Y0)
+        got = run_spmm(handle, rp.astype(np.int64), ci, v, X, 1.0, 0.0, Y0, A.cols, ldx=n + 4, ldy=n + 8,
+                       alg=api.SPMM_CSR_ALG5, want_variant="merge-path")
+        assert rel_l2(got, want) <= TOL[np.dtype(dtype)]
+
+
+def test_merge_path_spmm_is_reproducible(handle):
+    A = G.rmat(14, 16, seed=71)
+    rp, ci, v = A.numpy()
+    X = G.uniform((A.cols, 32), -1, 1, seed=76).numpy()
+    Y0 = np.zeros((A.rows, 32), np.float32)
+    a = run_spmm(handle, rp, ci, v, X, 1.0, 0.0, Y0, A.cols, alg=api.SPMM_CSR_ALG2)
+    b = run_spmm(handle, rp, ci, v, X, 1.0, 0.0, Y0, A.cols, alg=api.SPMM_CSR_ALG2)
+    assert np.array_equal(a, b)      # no atomics: the same bits every run
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("n", [16, 32, 48, 64, 128, 192])
+def test_staged_kernel_on_a_stencil(handle, dtype, n, monkeypatch):
+    """B through shared memory by TMA (opt-in with ASP_SPMM_STAGE=1, for blocks that touch B in runs): the same
+    bits as the oracle and as the kernel that reads B from global memory, with padded leading dimensions and
+    beta != 0."""
+    monkeypatch.setenv("ASP_SPMM_STAGE", "1")
+    t = torch.float32 if dtype == np.float32 else torch.float64
+    A = G.stencil_3d_27pt(20, seed=9, dtype=t)        # 8,000 rows: 63 row blocks, the last one partial
+    rp, ci, v = A.numpy()
+    X = G.uniform((A.cols, n), -1, 1, dtype=t, seed=91).numpy()
+    Y0 = G.uniform((A.rows, n), -1, 1, dtype=t, seed=92).numpy()
+    want = oracle.spmm(rp, ci, v, X, 1.25, 0.5, Y0)
+    # (16-byte fp64 entries: a 256-row block of this stencil does not fit the staging buffer, the tile kernel runs)
+    got = run_spmm(handle, rp, ci, v, X, 1.25, 0.5, Y0, A.cols, ldx=n + 8, ldy=n + 4,
+                   want_variant="staged" if dtype == np.float32 else None)
+    assert np.array_equal(got, want)
+    monkeypatch.setenv("ASP_SPMM_STAGE", "0")
+    plain = run_spmm(handle, rp, ci, v, X, 1.25, 0.5, Y0, A.cols, ldx=n + 8, ldy=n + 4, want_variant="tile")
+    assert np.array_equal(plain, want)
+
+
+def test_staged_kernel_is_not_chosen_for_scattered_columns(handle, monkeypatch):
+    monkeypatch.setenv("ASP_SPMM_STAGE", "1")
+    A = G.poisson_random(5000, 5000, mean_len=12, seed=93)      # a chunk of 64 rows of B per entry would be waste
+    rp, ci, v = A.numpy()
+    X = G.uniform((A.cols, 32), -1, 1, seed=94).numpy()
+    Y0 = np.zeros((A.rows, 32), np.float32)
+    got = run_spmm(handle, rp, ci, v, X, 1.0, 0.0, Y0, A.cols, want_variant="tile")
+    assert np.array_equal(got, oracle.spmm(rp, ci, v, X, 1.0, 0.0, Y0))
 
 
 def test_leading_dimensions_and_i64_offsets(handle):
