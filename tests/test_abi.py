@@ -75,7 +75,9 @@ def test_descriptor_argument_checks():
     assert csr(3, 3, 2 ** 31, dummy, dummy, dummy) == 10           # does not fit 32-bit offsets
     assert csr(3, 3, 2 ** 31, dummy, dummy, dummy, rt=api.INDEX_I64) == 0
     lib.alphasparseDestroySpMat(d)
-    assert csr(3, 3, 2, dummy, dummy, dummy, dt=2) == 6            # complex
+    assert csr(3, 3, 2, dummy, dummy, dummy, dt=6) == 6            # half-precision complex: no instance
+    assert csr(3, 3, 2, dummy, dummy, dummy, dt=api.C_32F) == 0    # complex float has an SpMV instance
+    lib.alphasparseDestroySpMat(d)
     assert csr(3, 3, 0, dummy, None, None) == 0                    # empty matrix needs no arrays
     lib.alphasparseDestroySpMat(d)
 
