@@ -617,6 +617,18 @@ def run_ours(args):
         xd_loc, yd_loc = api.DnVec(x_full), api.DnVec(y)
         extras["spmv_only_ms"] = max_over_ranks(time_steps(
             lambda: api.spmv(h, Am, xd_loc, yd_loc, w["alpha"], w["beta"]), stream, 20, 3, barrier))
+        # the exchanged x gives the same y as the whole x resident on the rank (max over ranks of the relative error)
+        y_a = torch.zeros_like(y)
+        y_b = torch.zeros_like(y)
+        with torch.cuda.stream(stream):
+            mg.spmv(x_in, y_a, w["alpha"], 0.0)
+            api.spmv(h, Am, xd_loc, api.DnVec(y_b), w["alpha"], 0.0)
+        torch.cuda.synchronize()
+        den = float(y_b.double().norm())
+        rel = float((y_a.double() - y_b.double()).norm()) / (den if den > 0 else 1.0)
+        extras["exchange_check_rel_l2"] = max_over_ranks(rel)
+        extras["exchange_check_ok"] = extras["exchange_check_rel_l2"] <= (1e-12 if w["dtype"] == torch.float64 else 1e-5)
+        del y_a, y_b
         extras["x_bytes_received_per_rank"] = info["bytes_received"]
         extras["interior_rows"] = [info["interior_begin"], info["interior_end"]]
         extras["window"] = [info["window_lo"], info["window_hi"]]

@@ -455,9 +455,16 @@ alphasparseStatus_t alphasparseMgCommDestroy(void* ncclComm);
  * for pattern entries, and for symmetric / Hermitian / skew-symmetric files each off-diagonal
  * entry followed by its mirror image with the same value, as the reference's reader does.
  * valueType R_32F or R_64F.  Status instead of exit(): INVALID_VALUE for a missing or malformed
- * file or an index outside the announced size, NOT_SUPPORTED for array or complex files.  The
- * reference's ".bin" dump format is not read. */
+ * file or an index outside the announced size, NOT_SUPPORTED for array or complex files. */
 alphasparseStatus_t alphasparseReadMtxCoo(const char* file, int64_t* rows, int64_t* cols, int64_t* nnz,
+                                          int32_t** row_index, int32_t** col_index, void** values,
+                                          alphasparseDataType valueType);
+/* The binary dump format of the reference's drivers (header: cuda/test/include/io.h:41-50; records:
+ * cuda/test/io.cu:596-725): eight int64 (rows, cols, records, entries after mirroring, value fields
+ * per record, number type, symmetry, reserved), then per record int32 row, int32 column (one-based)
+ * and 0, 1 or 2 doubles.  Same outputs and conventions as alphasparseReadMtxCoo (pattern -> 1, the
+ * real part of a complex value, symmetric files mirrored). */
+alphasparseStatus_t alphasparseReadBinCoo(const char* file, int64_t* rows, int64_t* cols, int64_t* nnz,
                                           int32_t** row_index, int32_t** col_index, void** values,
                                           alphasparseDataType valueType);
 void alphasparseFreeHost(void* p);

@@ -46,7 +46,7 @@ EXPORTS = [
     "alphasparseCsrPartitionRowsByNnz", "alphasparseCsrRebaseRowOffsets", "alphasparseCsrPlanGet",
     "alphasparseCsrLastVariant", "alphasparseCsrLastSpmmVariant", "alphasparseGetLaunchCount", "get_time_us", "get_avg_time_n",
     "alphasparseSpMVCsrNoAlloc", "alphasparseXcoo2csr", "alphasparseCsrColumnRange",
-    "alphasparseCreateDnVecWindow", "alphasparseReadMtxCoo", "alphasparseFreeHost", "alphasparseCooOrder",
+    "alphasparseCreateDnVecWindow", "alphasparseReadMtxCoo", "alphasparseReadBinCoo", "alphasparseFreeHost", "alphasparseCooOrder",
     "alphasparseMgCreate", "alphasparseMgDestroy", "alphasparseMgSetShard", "alphasparseMgSpMV",
     "alphasparseMgExchange", "alphasparseMgOwnView", "alphasparseMgGetInfo", "alphasparseMgExchangePlan",
     "alphasparseMgGetUniqueId", "alphasparseMgCommInitRank", "alphasparseMgCommDestroy",
@@ -348,7 +348,8 @@ def coo2csr(coo_row: torch.Tensor, rows: int, out_dtype=torch.int32, stream=None
 
 
 def read_mtx(path: str, dtype=torch.float32, ordered: bool = True):
-    """MatrixMarket coordinate file -> (rows, cols, row_index, col_index, values) as host tensors,
+    """MatrixMarket coordinate file (or, for a name ending in .bin, the reference drivers' binary dump) ->
+    (rows, cols, row_index, col_index, values) as host tensors,
     sorted by (row, column) when ``ordered`` (what coo2csr needs)."""
     import numpy as np
     lib = load()
@@ -356,8 +357,9 @@ def read_mtx(path: str, dtype=torch.float32, ordered: bool = True):
     code = _dtype_code(dtype)
     m, n, nnz = C.c_int64(), C.c_int64(), C.c_int64()
     ri, ci, v = C.c_void_p(), C.c_void_p(), C.c_void_p()
-    _check(lib.alphasparseReadMtxCoo(path.encode(), C.byref(m), C.byref(n), C.byref(nnz), C.byref(ri), C.byref(ci),
-                                     C.byref(v), code), "alphasparseReadMtxCoo")
+    reader = lib.alphasparseReadBinCoo if path.endswith(".bin") else lib.alphasparseReadMtxCoo
+    _check(reader(path.encode(), C.byref(m), C.byref(n), C.byref(nnz), C.byref(ri), C.byref(ci),
+                  C.byref(v), code), "alphasparseReadBinCoo" if path.endswith(".bin") else "alphasparseReadMtxCoo")
     try:
         k = nnz.value
         if ordered:

@@ -6,7 +6,8 @@
 // value 1; for symmetric, Hermitian and skew-symmetric files every off-diagonal entry is followed by
 // its mirror image WITH THE SAME VALUE (the reference does not negate for skew-symmetric files).
 // Differences: errors are returned as status codes (the reference prints and calls exit), 64-bit
-// counts, bounds of every index are checked, and the reference's private ".bin" dump format is not read.
+// counts, bounds of every index are checked.  alphasparseReadBinCoo reads the binary dump format of the
+// reference's drivers (bin_header, cuda/test/include/io.h:41-50; records, cuda/test/io.cu:596-725).
 #include <algorithm>
 #include <cctype>
 #include <cstdio>
@@ -166,6 +167,75 @@ alphasparseStatus_t alphasparseReadMtxCoo(const char* file, int64_t* rows, int64
     *cols = n;
   }
   return st;
+}
+
+// The reference's binary matrix dump: a header of eight int64 (rows, cols, records, entries after
+// mirroring, value fields per record - 0 pattern, 1 real, 2 complex -, number type, symmetry - 0
+// general -, reserved), then one record per stored entry: int32 row and column (one-based) followed
+// by that many doubles.  As in the reference's reader (cuda/test/io.cu:603-725) a pattern entry gets
+// the value 1, a complex entry contributes its real part, and for a symmetric file every
+// off-diagonal record is followed by its mirror image with the same value.
+alphasparseStatus_t alphasparseReadBinCoo(const char* file, int64_t* rows, int64_t* cols, int64_t* nnz,
+                                          int32_t** row_index, int32_t** col_index, void** values,
+                                          alphasparseDataType valueType) {
+  if (!file || !rows || !cols || !nnz || !row_index || !col_index || !values) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+  if (valueType != ALPHA_R_32F && valueType != ALPHA_R_64F) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  *row_index = *col_index = nullptr;
+  *values = nullptr;
+  FILE* fp = fopen(file, "rb");
+  if (!fp) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+  int64_t hdr[8];
+  if (fread(hdr, sizeof(int64_t), 8, fp) != 8) {
+    fclose(fp);
+    return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+  }
+  const int64_t m = hdr[0], n = hdr[1], records = hdr[2], fields = hdr[4];
+  const bool mirror = hdr[6] != 0;
+  if (m < 0 || n < 0 || records < 0 || m >= (int64_t(1) << 31) || n >= (int64_t(1) << 31) || fields < 0 || fields > 2) {
+    fclose(fp);
+    return fields > 2 ? ALPHA_SPARSE_STATUS_NOT_SUPPORTED : ALPHA_SPARSE_STATUS_INVALID_VALUE;
+  }
+  const size_t es = valueType == ALPHA_R_64F ? 8 : 4;
+  const int64_t cap = mirror ? 2 * records : records;
+  int32_t* ri = (int32_t*)malloc(sizeof(int32_t) * (size_t)(cap > 0 ? cap : 1));
+  int32_t* ci = (int32_t*)malloc(sizeof(int32_t) * (size_t)(cap > 0 ? cap : 1));
+  void* v = malloc(es * (size_t)(cap > 0 ? cap : 1));
+  alphasparseStatus_t st = (ri && ci && v) ? ALPHA_SPARSE_STATUS_SUCCESS : ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+  int64_t k = 0;
+  for (int64_t i = 0; i < records && st == ALPHA_SPARSE_STATUS_SUCCESS; ++i) {
+    int32_t rc[2];
+    double f[2] = {1.0, 0.0};
+    if (fread(rc, sizeof(int32_t), 2, fp) != 2 || (fields > 0 && fread(f, sizeof(double), (size_t)fields, fp) != (size_t)fields)) {
+      st = ALPHA_SPARSE_STATUS_INVALID_VALUE;  // the file ends before the announced records do
+      break;
+    }
+    const int64_t r = (int64_t)rc[0] - 1, c = (int64_t)rc[1] - 1;
+    if (r < 0 || r >= m || c < 0 || c >= n) {
+      st = ALPHA_SPARSE_STATUS_INVALID_VALUE;
+      break;
+    }
+    for (int copy = 0; copy < ((mirror && r != c) ? 2 : 1); ++copy) {
+      ri[k] = (int32_t)(copy ? c : r);
+      ci[k] = (int32_t)(copy ? r : c);
+      if (es == 8) ((double*)v)[k] = f[0];
+      else ((float*)v)[k] = (float)f[0];
+      ++k;
+    }
+  }
+  fclose(fp);
+  if (st != ALPHA_SPARSE_STATUS_SUCCESS) {
+    free(ri);
+    free(ci);
+    free(v);
+    return st;
+  }
+  *rows = m;
+  *cols = n;
+  *nnz = k;
+  *row_index = ri;
+  *col_index = ci;
+  *values = v;
+  return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
 alphasparseStatus_t alphasparseCooOrder(int64_t nnz, int32_t* row_index, int32_t* col_index, void* values,

@@ -246,6 +246,7 @@ def _check_slabs(handle, A, x, tol, name, slab=1 << 22):
 
 
 def test_config5a_laplacian_512_cubed_slabs_against_the_oracle(handle):
+    torch.cuda.empty_cache()
     if torch.cuda.mem_get_info()[0] < 60e9:
         pytest.skip("needs about 40 GB of free device memory")
     A = G.laplacian_3d_7pt(512, dtype=torch.float64, device="cuda", index64=True)
@@ -254,7 +255,10 @@ def test_config5a_laplacian_512_cubed_slabs_against_the_oracle(handle):
 
 
 def test_config5b_rmat26_slabs_against_the_oracle(handle):
-    if torch.cuda.mem_get_info()[0] < 150e9:
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()          # blocks the earlier tests freed are still in torch's cache
+    if torch.cuda.mem_get_info()[0] < 120e9:
         pytest.skip("building R-MAT scale 26 needs most of a 180 GB device")
     A = G.rmat(26, 32, device="cuda", seed=5, index64=True)
     assert A.row_ptr.dtype == torch.int64 and A.rows == 1 << 26

@@ -106,3 +106,52 @@ def test_file_to_spmv(handle, tmp_path):
     api.spmv(handle, Am, api.DnVec(x.cuda()), api.DnVec(y), 1.0, 0.0)
     torch.cuda.synchronize()
     assert rel_l2(y.cpu().numpy(), oracle.spmv(rp, ci, v, x.numpy(), 1.0, 0.0)) <= 1e-12
+
+
+def _write_bin(path, rows, cols, recs, fields, sym):
+    """The reference drivers' dump format: eight int64, then int32 row, int32 column (one-based), `fields` doubles."""
+    mirrored = sum(2 if (sym and r != c) else 1 for r, c, *_ in recs)
+    with open(path, "wb") as f:
+        np.array([rows, cols, len(recs), mirrored, fields, 0, sym, 0], dtype=np.int64).tofile(f)
+        for r, c, *vals in recs:
+            np.array([r, c], dtype=np.int32).tofile(f)
+            np.array(vals[:fields], dtype=np.float64).tofile(f)
+
+
+def test_binary_dump_general_symmetric_pattern_and_complex(tmp_path):
+    p = str(tmp_path / "g.bin")
+    _write_bin(p, 3, 4, [(3, 1, 2.5), (1, 4, -1e-2), (1, 2, 7.0)], 1, 0)
+    m, n, r, c, v = api.read_mtx(p, torch.float64, ordered=False)
+    assert (m, n) == (3, 4) and r.tolist() == [2, 0, 0] and c.tolist() == [0, 3, 1] and v.tolist() == [2.5, -1e-2, 7.0]
+    m, n, r, c, v = api.read_mtx(p, torch.float32)                           # ordered by (row, column)
+    assert r.tolist() == [0, 0, 2] and c.tolist() == [1, 3, 0]
+    p = str(tmp_path / "s.bin")
+    _write_bin(p, 3, 3, [(1, 1, 4.0), (3, 1, -1.0)], 1, 1)                   # symmetric: the mirror follows the entry
+    _, _, r, c, v = api.read_mtx(p, torch.float64, ordered=False)
+    assert r.tolist() == [0, 2, 0] and c.tolist() == [0, 0, 2] and v.tolist() == [4.0, -1.0, -1.0]
+    p = str(tmp_path / "p.bin")
+    _write_bin(p, 2, 2, [(1, 2), (2, 2)], 0, 0)                              # pattern: value 1
+    _, _, r, c, v = api.read_mtx(p, torch.float32, ordered=False)
+    assert r.tolist() == [0, 1] and c.tolist() == [1, 1] and v.tolist() == [1.0, 1.0]
+    p = str(tmp_path / "z.bin")
+    _write_bin(p, 2, 2, [(1, 1, 3.0, 9.0)], 2, 0)                            # complex: the real part, as the reference
+    _, _, r, c, v = api.read_mtx(p, torch.float64, ordered=False)
+    assert v.tolist() == [3.0]
+
+
+def test_binary_dump_errors(tmp_path):
+    lib = api.load()
+    out = [C.c_int64() for _ in range(3)]
+    ptrs = [C.c_void_p() for _ in range(3)]
+
+    def read(path):
+        return lib.alphasparseReadBinCoo(path.encode(), *[C.byref(o) for o in out], *[C.byref(p) for p in ptrs], api.R_32F)
+    assert read(str(tmp_path / "missing.bin")) == 3
+    p = str(tmp_path / "short.bin")
+    _write_bin(p, 3, 3, [(1, 1, 1.0)], 1, 0)
+    with open(p, "r+b") as f:
+        f.truncate(64 + 8 + 4)                                               # the record is cut off
+    assert read(p) == 3
+    p = str(tmp_path / "range.bin")
+    _write_bin(p, 3, 3, [(4, 1, 1.0)], 1, 0)                                 # row outside the announced size
+    assert read(p) == 3

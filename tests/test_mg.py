@@ -162,6 +162,8 @@ def _gpu_worker(rank, world, port, out_dir):
                 assert (info["interior_begin"], info["interior_end"]) == (i0, i1)
                 if name == "lap3d_f64":
                     assert i1 > i0 and (i0 > 0 or i1 < Aloc.rows)       # a slab's first or last grid plane reaches out
+                    if 0 < rank < world - 1:
+                        assert i0 > 0 and i1 < Aloc.rows                # a middle rank: halo rows on both sides
                     # x kept inside the window: only the halo moves, same y
                     xv = mg.own_view()
                     assert xv.numel() == r1 - r0
@@ -179,13 +181,15 @@ def _gpu_worker(rank, world, port, out_dir):
 
 
 @pytest.mark.gpu
-def test_every_mode_on_two_gpus_against_the_oracle(tmp_path):
-    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
-        pytest.skip("needs two CUDA devices")
+@pytest.mark.parametrize("world", [2, 4])
+def test_every_mode_on_several_gpus_against_the_oracle(tmp_path, world):
+    """Two ranks: each has one neighbour.  Four ranks: the middle ranks have two, so their shard is cut into
+    top boundary rows, interior rows and bottom boundary rows."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} CUDA devices")
     import oracle
     from conftest import rel_l2
     from library_b200 import generators as G
-    world = 2
     mp.spawn(_gpu_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     for name, (make, dt, tol, (xlo, xhi)) in _cases().items():
         A = make()
@@ -204,4 +208,4 @@ def test_every_mode_on_two_gpus_against_the_oracle(tmp_path):
                 recv = [int(np.load(tmp_path / f"{name}_m{mode}_recv{r}.npy")[0]) for r in range(world)]
                 assert 0 < max(recv) <= (48 * 48 + 32) * 8          # one grid plane (plus alignment slack)
             recv = [int(np.load(tmp_path / f"{name}_m1_recv{r}.npy")[0]) for r in range(world)]
-            assert max(recv) >= (A.cols // 2 - 48 * 48) * 8         # all-gather: the other rank's whole part
+            assert max(recv) >= (A.cols * (world - 1) // world - 48 * 48) * 8     # all-gather: everybody else's part
