@@ -319,8 +319,14 @@ alphasparseStatus_t analyse_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, 
   p->merge_tiles = (p->rows + p->nnz + kMergeItems - 1) / kMergeItems;
   ASP_CUDA(cudaMalloc(&p->merge_tile_row, sizeof(int32_t) * (p->merge_tiles + 1)));
   ASP_CUDA(cudaMalloc(&p->carry, sizeof(double) * (p->merge_tiles > 0 ? p->merge_tiles : 1)));
-  ASP_CUDA(cudaMalloc(&p->dev_err, sizeof(int)));
-  ASP_CUDA(cudaMemsetAsync(p->dev_err, 0, sizeof(int), st));
+  ASP_CUDA(cudaHostAlloc((void**)&p->dev_err, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable));
+  *p->dev_err = 0;
+  {
+    int polls = env_int("ASP_WAIT_POLLS", 1 << 22);
+    if (polls < 1) polls = 1;
+    p->wait_cfg = (uint32_t)polls & ~kWaitDropCopy;
+    if (env_int("ASP_TEST_DROP_COPY", 0)) p->wait_cfg |= kWaitDropCopy;
+  }
   merge_tile_kernel<OffT><<<(int)((p->merge_tiles + 1 + 255) / 256), 256, 0, st>>>(
       rp, p->rows, p->nnz, p->merge_tiles, kMergeItems, p->merge_tile_row);
   impl(h)->launches++;
@@ -391,7 +397,7 @@ void free_plan(Plan* p) {
   cudaFree(p->bin_rows);
   cudaFree(p->merge_tile_row);
   cudaFree(p->carry);
-  cudaFree(p->dev_err);
+  cudaFreeHost(p->dev_err);
   cudaFree(p->spmm_carry);
   if (p->spmm_tc) free_spmm_tc_plan(p->spmm_tc);
   if (p->spmm_stage) free_spmm_stage_plan(p->spmm_stage);
@@ -572,9 +578,7 @@ alphasparseStatus_t alphasparseCsrPlanGet(alphasparseHandle_t h, alphasparseSpMa
     stats[ASP_STAT_VARIANT] = p->variant_auto;
     stats[ASP_STAT_IDENTITY_SHORT] = p->identity_short ? 1 : 0;
     stats[ASP_STAT_NNZ_SHORT] = p->nnz_short;
-    int e = 0;
-    if (p->dev_err) ASP_CUDA(cudaMemcpy(&e, p->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
-    stats[ASP_STAT_DEVICE_ERROR] = e;
+    stats[ASP_STAT_DEVICE_ERROR] = p->dev_err ? *(volatile int*)p->dev_err : 0;  // the stream was synchronised above
   }
   if (bin_rows && p->rows > 0) {
     if (p->identity_short) {

@@ -58,7 +58,13 @@ struct Plan {
   int64_t merge_tiles = 0;
   int32_t* merge_tile_row = nullptr;  // device, merge_tiles + 1
   void* carry = nullptr;              // device, merge_tiles * 8 bytes (used when no external buffer)
-  int* dev_err = nullptr;             // device flag a kernel raises when a bounded wait expires
+  // Flag a kernel raises when a bounded wait expires: one int in pinned host memory mapped into the
+  // device's address space, so that only a failing CTA ever touches it and the host can look at it
+  // without a synchronisation (the next call on the plan does, and refuses).
+  int* dev_err = nullptr;
+  // Polls a bounded device-side wait may take (bit 31: testing only - the copy the wait is for is not
+  // issued, so the wait does run out).  Read from ASP_WAIT_POLLS / ASP_TEST_DROP_COPY at analysis.
+  uint32_t wait_cfg = 1u << 22;
   int variant_auto = kVariantBinned;
   int last_variant = -1;
   const char* last_spmm = "none";   // name of the SpMM kernel family the last call ran
@@ -107,6 +113,8 @@ inline size_t elem_size(alphasparseDataType t) {
     default: return 0;
   }
 }
+
+constexpr uint32_t kWaitDropCopy = 1u << 31;
 
 inline int env_int(const char* name, int dflt) {
   const char* s = getenv(name);

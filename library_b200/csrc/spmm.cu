@@ -178,7 +178,7 @@ template <typename T, typename OffT, int LN, int VN>
 __global__ void __launch_bounds__(kThreads, ASP_SPMM_MIN_CTAS)
 spmm_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const T* __restrict__ val,
                  const T* __restrict__ B, int64_t ldb, T* __restrict__ C, int64_t ldc, T alpha, T beta,
-                 int64_t rows, int64_t n, int64_t nnz, int* __restrict__ err) {
+                 int64_t rows, int64_t n, int64_t nnz, int* __restrict__ err, uint32_t wait_cfg) {
   constexpr int NG = kThreads / LN;
   constexpr int RB = kSpmmRowBlock;
   constexpr int RPG = RB >= NG ? RB / NG : 1;  // with one lane per row half the groups of a CTA idle
@@ -215,7 +215,7 @@ spmm_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&s_bar)),
                  "r"(cnt * (uint32_t)(sizeof(T) + sizeof(int)))
                  : "memory");
-    if (cnt) {
+    if (cnt && !(wait_cfg & kWaitDropCopy)) {
       bulk_g2s(s_val, val + a0, cnt * (uint32_t)sizeof(T), &s_bar);
       bulk_g2s(s_col, col + a0, cnt * (uint32_t)sizeof(int), &s_bar);
     }
@@ -230,7 +230,7 @@ spmm_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   {
     uint32_t tries = 0;
     while (!mbar_try_wait0(&s_bar)) {
-      if (++tries > (1u << 22)) {
+      if (++tries > (wait_cfg & ~kWaitDropCopy)) {
         failed = true;
         break;
       }
@@ -341,7 +341,7 @@ alphasparseStatus_t launch_tile(alphasparseHandle_t h, alphasparseSpMatDescr_t A
   spmm_tile_kernel<T, OffT, LN, VN><<<dim3((unsigned)gx, (unsigned)gy), kThreads, 0, h->stream>>>(
       reinterpret_cast<const OffT*>(A->row_offsets), A->const_col_data,
       reinterpret_cast<const T*>(A->const_val_data), B, ldb, C, ldc, alpha, beta, A->rows, n, A->nnz,
-      plan_of(A)->dev_err);
+      plan_of(A)->dev_err, plan_of(A)->wait_cfg);
   impl(h)->launches++;
   return status_of(cudaGetLastError());
 }
@@ -539,6 +539,7 @@ alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t h, alphasparseOperation_
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   }
   if (plan_of(A)->device != h->device) return ALPHA_SPARSE_STATUS_INVALID_VALUE;  // the plan's arrays live on another GPU
+  if (plan_of(A)->dev_err && *(volatile int*)plan_of(A)->dev_err) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
   if (B->order == ALPHASPARSE_ORDER_COL) {
     // Column-major B and C: row-major copies in the caller's buffer (sizes: alphasparseSpMM_bufferSize),
     // the row-major kernel, and C copied back.  B and C themselves keep their layout.

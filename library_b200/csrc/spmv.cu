@@ -440,7 +440,6 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 
 constexpr int kTileSlot = kMergeItems + 16;    // entries per staged array (widening adds < 16)
 constexpr int kTileShortSeg = ASP_TILE_SHORT_SEG;
-constexpr uint32_t kTileMaxTries = 1u << 22;
 
 // Storage <-> arithmetic conversions of the mixed-precision instances (TA = __half or __nv_bfloat16
 // for A and x, arithmetic in T = float); identity for the fp32 / fp64 instances.
@@ -461,7 +460,7 @@ __global__ void __launch_bounds__(kThreads, (sizeof(TA) < 4 ? ASP_TILE_MIN_CTAS_
 spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const TA* __restrict__ val,
                  const TA* __restrict__ x, TY* __restrict__ y, T alpha, T beta, int64_t rows,
                  int64_t nnz, const int32_t* __restrict__ tile_row, T* __restrict__ carry,
-                 int* __restrict__ err) {
+                 int* __restrict__ err, uint32_t wait_cfg) {
   constexpr int ITEMS = kMergeItems;
   constexpr int IPT = kMergeIpt;
   constexpr bool kSame = std::is_same<TA, T>::value;
@@ -498,7 +497,7 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
     if (a1 < a0) a1 = a0;
     const uint32_t cnt = (uint32_t)(a1 - a0);
     mbar_expect_tx(&s_bar, cnt * (uint32_t)(sizeof(TA) + sizeof(int)));
-    if (cnt) {
+    if (cnt && !(wait_cfg & kWaitDropCopy)) {
       bulk_g2s(s_val, val + a0, cnt * (uint32_t)sizeof(TA), &s_bar);
       bulk_g2s(s_col, col + a0, cnt * (uint32_t)sizeof(int), &s_bar);
     }
@@ -525,7 +524,7 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   {
     uint32_t tries = 0;
     while (!mbar_try_wait(&s_bar, 0)) {
-      if (++tries > kTileMaxTries) {
+      if (++tries > (wait_cfg & ~kWaitDropCopy)) {
         failed = true;
         break;
       }
@@ -734,7 +733,7 @@ alphasparseStatus_t spmv_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, Pla
   const dim3 grid((unsigned)p->merge_tiles), block(kMergeThreads);
   if (vl && env_int("ASP_MERGE_TMA", 1)) {
     spmv_tile_kernel<T, OffT><<<grid, kThreads, 0, h->stream>>>(rp, col, val, x, y, alpha, beta, p->rows, p->nnz,
-                                                              p->merge_tile_row, carry, p->dev_err);
+                                                              p->merge_tile_row, carry, p->dev_err, p->wait_cfg);
     spmv_merge_fixup_kernel<T><<<(unsigned)((p->merge_tiles + 255) / 256), 256, 0, h->stream>>>(
         p->merge_tile_row, carry, p->merge_tiles, p->rows, y, alpha);
     impl(h)->launches += 2;
@@ -759,7 +758,7 @@ alphasparseStatus_t spmv_lowp_tile(alphasparseHandle_t h, alphasparseSpMatDescr_
   spmv_tile_kernel<float, OffT, TA, TY><<<(unsigned)p->merge_tiles, kThreads, 0, h->stream>>>(
       reinterpret_cast<const OffT*>(A->row_offsets), A->const_col_data, reinterpret_cast<const TA*>(A->const_val_data),
       reinterpret_cast<const TA*>(x), reinterpret_cast<TY*>(y), alpha, beta, p->rows, p->nnz, p->merge_tile_row,
-      carry, p->dev_err);
+      carry, p->dev_err, p->wait_cfg);
   spmv_merge_fixup_kernel<float, TY><<<(unsigned)((p->merge_tiles + 255) / 256), 256, 0, h->stream>>>(
       p->merge_tile_row, carry, p->merge_tiles, p->rows, reinterpret_cast<TY*>(y), alpha);
   impl(h)->launches += 2;
@@ -849,6 +848,8 @@ alphasparseStatus_t alphasparseSpMV(alphasparseHandle_t h, alphasparseOperation_
   Plan* p = plan_of(A);
   if (p->rows != A->rows || p->nnz != A->nnz || p->cols != A->cols) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
   if (p->device != h->device) return ALPHA_SPARSE_STATUS_INVALID_VALUE;  // the plan's arrays live on another GPU
+  // a kernel of an earlier call on this matrix gave up on a bounded wait: its result was incomplete
+  if (p->dev_err && *(volatile int*)p->dev_err) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
   if (A->data_type == ALPHA_C_32F || A->data_type == ALPHA_C_64F || A->data_type == ALPHA_R_8I) {
     p->last_variant = kVariantBinned;  // complex and int8 instances: the row-length-binned kernel of spmv_types.cu
     return spmv_other_run(h, A, p, x->values, y->values, y->data_type, alpha, beta);

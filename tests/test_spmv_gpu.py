@@ -370,3 +370,34 @@ def test_transposed_without_entries(handle):
     api.spmv(handle, Am, api.DnVec(torch.ones(rows, device="cuda")), api.DnVec(y), 1.0, 3.0, op=api.OP_T)
     torch.cuda.synchronize()
     assert torch.equal(y, 3.0 * y0)
+
+
+def test_a_wait_that_runs_out_is_reported_as_a_status(handle, monkeypatch):
+    """Failure detection without a fault: with ASP_TEST_DROP_COPY the tile kernel announces its bulk copies to
+    the mbarrier but never issues them, so every CTA's bounded wait runs out after ASP_WAIT_POLLS polls; the
+    CTAs raise the plan's flag and return, the context stays usable, the flag shows in the plan statistics and
+    the next call on the matrix is refused with EXECUTION_FAILED.  A fresh analysis clears it."""
+    A = G.poisson_random(20000, 20000, mean_len=16, seed=301).to("cuda")
+    x = G.uniform((A.cols,), -1, 1, device="cuda", seed=302)
+    y = torch.zeros(A.rows, device="cuda")
+    handle.use_torch_stream()
+    monkeypatch.setenv("ASP_SPMV_VARIANT", "merge")
+    monkeypatch.setenv("ASP_TEST_DROP_COPY", "1")
+    monkeypatch.setenv("ASP_WAIT_POLLS", "2")
+    Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr, A.col_idx, A.val)
+    Am.analyse(handle)                                 # the plan takes the wait settings from the environment
+    monkeypatch.delenv("ASP_TEST_DROP_COPY")
+    monkeypatch.delenv("ASP_WAIT_POLLS")
+    api.spmv(handle, Am, api.DnVec(x), api.DnVec(y), 1.0, 0.0)      # launches; every CTA gives up and leaves
+    torch.cuda.synchronize()                                         # no error from the runtime: nothing faulted
+    assert Am.plan(handle)[0]["device_error"] == 1
+    with pytest.raises(api.AlphaSparseError) as ei:
+        api.spmv(handle, Am, api.DnVec(x), api.DnVec(y), 1.0, 0.0)
+    assert ei.value.status == 4                                      # ALPHA_SPARSE_STATUS_EXECUTION_FAILED
+    Am.analyse(handle)                                               # new plan, normal waits
+    api.spmv(handle, Am, api.DnVec(x), api.DnVec(y), 1.0, 0.0)
+    torch.cuda.synchronize()
+    assert Am.plan(handle)[0]["device_error"] == 0
+    import oracle
+    want = oracle.spmv(*A.numpy(), x.cpu().numpy(), 1.0, 0.0)
+    assert rel_l2(y.cpu().numpy(), want) <= 1e-5
