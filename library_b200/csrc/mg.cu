@@ -307,7 +307,9 @@ alphasparseStatus_t alphasparseMgCreate(alphasparseMgHandle_t* out, alphasparseH
   int lo_prio = 0, hi_prio = 0;
   cudaError_t e = cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio);
   // the few CTAs of a halo exchange must not queue behind a product that fills the GPU
-  if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&m->comm_stream, cudaStreamNonBlocking, hi_prio);
+  if (e == cudaSuccess)
+    e = cudaStreamCreateWithPriority(&m->comm_stream, cudaStreamNonBlocking,
+                                     env_int("ASP_MG_COMM_PRIORITY", 1) ? hi_prio : lo_prio);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&m->ev_ready, cudaEventDisableTiming);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&m->ev_halo, cudaEventDisableTiming);
   if (e != cudaSuccess) {
@@ -460,6 +462,48 @@ alphasparseStatus_t alphasparseMgSetShard(alphasparseMgHandle_t m, alphasparseSp
   }
   cudaFree(d_out);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  // The interior and bottom parts are slices of the shard's arrays: move the two cuts to rows whose
+  // first entry sits on a 16-byte boundary of both arrays (a multiple of four entries), or those
+  // parts lose the bulk-copy kernels.  Rows that leave the interior this way simply count as
+  // boundary rows.
+  if (i1 > i0) {
+    constexpr int kLook = 4096;  // far enough to get past a run of even-length rows that starts on an odd entry
+    auto align_cut = [&](int64_t from, int dir, int64_t* cut) -> alphasparseStatus_t {
+      int64_t a = dir > 0 ? from : from - kLook + 1;
+      if (a < 0) a = 0;
+      int64_t b = dir > 0 ? from + kLook : from + 1;  // offsets of rows [a, b)
+      if (b > A->rows + 1) b = A->rows + 1;
+      std::vector<int64_t> host((size_t)kLook);
+      const int64_t cnt = b - a;
+      if (o64) {
+        ASP_CUDA(cudaMemcpyAsync(host.data(), (const int64_t*)A->row_offsets + a, sizeof(int64_t) * cnt, cudaMemcpyDeviceToHost, st));
+        ASP_CUDA(cudaStreamSynchronize(st));
+      } else {
+        std::vector<int32_t> h32((size_t)kLook);
+        ASP_CUDA(cudaMemcpyAsync(h32.data(), (const int32_t*)A->row_offsets + a, sizeof(int32_t) * cnt, cudaMemcpyDeviceToHost, st));
+        ASP_CUDA(cudaStreamSynchronize(st));
+        for (int64_t j = 0; j < cnt; ++j) host[j] = h32[j];
+      }
+      *cut = -1;
+      if (dir > 0) {
+        for (int64_t j = 0; j < cnt; ++j)
+          if (host[j] % 4 == 0) { *cut = a + j; break; }
+      } else {
+        for (int64_t j = cnt - 1; j >= 0; --j)
+          if (host[j] % 4 == 0) { *cut = a + j; break; }
+      }
+      return ALPHA_SPARSE_STATUS_SUCCESS;
+    };
+    int64_t c0 = i0, c1 = i1;
+    if (i0 > 0) s = align_cut(i0, +1, &c0);
+    if (s == ALPHA_SPARSE_STATUS_SUCCESS && i1 < A->rows) s = align_cut(i1, -1, &c1);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    if (c0 < 0 || c1 < 0 || c1 <= c0) i0 = i1 = 0;  // no aligned cut nearby: run as WINDOW
+    else {
+      i0 = c0;
+      i1 = c1;
+    }
+  }
   m->i0 = i0;
   m->i1 = i1;
   if (i1 <= i0) return ALPHA_SPARSE_STATUS_SUCCESS;  // no interior: the overlapped mode runs as WINDOW
@@ -596,17 +640,26 @@ alphasparseStatus_t alphasparseMgSpMV(alphasparseMgHandle_t m, const void* alpha
     // previous step's boundary rows no longer read the halo that is about to be overwritten
     ASP_CUDA(cudaEventRecord(m->ev_ready, st));
     ASP_CUDA(cudaStreamWaitEvent(m->comm_stream, m->ev_ready, 0));
-    s = enqueue_exchange(m, nc, xo, o0, m->comm_stream);
-    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-    ASP_CUDA(cudaEventRecord(m->ev_halo, m->comm_stream));
-    bool first = true;
+    // the interior rows are enqueued before the exchange: the host's time inside NCCL then passes
+    // while the GPU already multiplies
+    bool exchanged = false;
     for (const Part& p : m->parts) {
       const bool interior = p.a == m->i0 && p.b == m->i1;
-      if (!(first && interior)) ASP_CUDA(cudaStreamWaitEvent(st, m->ev_halo, 0));
+      if (!interior && !exchanged) {
+        s = enqueue_exchange(m, nc, xo, o0, m->comm_stream);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        ASP_CUDA(cudaEventRecord(m->ev_halo, m->comm_stream));
+        exchanged = true;
+      }
+      if (!interior) ASP_CUDA(cudaStreamWaitEvent(st, m->ev_halo, 0));  // boundary rows need the halo
       _alphasparse_dnvec_descr yp{true, p.b - p.a, (char*)y + (size_t)p.a * m->es, dt};
       s = alphasparseSpMV(h, ALPHA_SPARSE_OPERATION_NON_TRANSPOSE, alpha, p.d, m->xd, beta, &yp, dt, alg, nullptr);
       if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-      first = false;
+    }
+    if (!exchanged) {  // a shard without boundary rows still owes its peers their halos
+      s = enqueue_exchange(m, nc, xo, o0, m->comm_stream);
+      if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+      ASP_CUDA(cudaEventRecord(m->ev_halo, m->comm_stream));
     }
     // whatever the caller enqueues next on its stream (e.g. an update of x) comes after the sends
     ASP_CUDA(cudaStreamWaitEvent(st, m->ev_halo, 0));

@@ -137,11 +137,14 @@ class XWindowExchange:
         return self.window
 
 
-def interior_row_range(row_ptr: torch.Tensor, col_idx: torch.Tensor, own_lo: int, own_hi: int):
+def interior_row_range(row_ptr: torch.Tensor, col_idx: torch.Tensor, own_lo: int, own_hi: int, align: int = 1):
     """Rows [i0, i1) of a shard (local CSR, ascending global columns inside a row) all of whose
     columns lie in [own_lo, own_hi): they need nothing from other ranks.  The largest such range that
-    is one contiguous run starting at the first interior row; (0, 0) when there is none.  Works on
-    host or device tensors."""
+    is one contiguous run starting at the first interior row; (0, 0) when there is none.  With
+    ``align`` > 1 (the library uses 4) a cut that is not the shard's first or last row moves inwards,
+    by at most 4095 rows, to a row whose first entry's index is a multiple of ``align`` - the slices of
+    the entry arrays then start on a 16-byte boundary; (0, 0) if there is no such row.  Works on host
+    or device tensors."""
     n = row_ptr.numel() - 1
     if n <= 0 or col_idx.numel() == 0:
         return 0, 0
@@ -156,4 +159,19 @@ def interior_row_range(row_ptr: torch.Tensor, col_idx: torch.Tensor, own_lo: int
     i0 = int(idx[0])
     rest = torch.nonzero(~inside[i0:]).flatten()
     i1 = i0 + (int(rest[0]) if rest.numel() else n - i0)
+    if align > 1 and i1 > i0:
+        look = 4096
+        c0, c1 = i0, i1
+        if i0 > 0:
+            w = rp[i0:min(i0 + look, n + 1)] % align == 0
+            hit = torch.nonzero(w).flatten()
+            c0 = i0 + int(hit[0]) if hit.numel() else -1
+        if i1 < n:
+            a = max(i1 - look + 1, 0)
+            w = rp[a:i1 + 1] % align == 0
+            hit = torch.nonzero(w).flatten()
+            c1 = a + int(hit[-1]) if hit.numel() else -1
+        if c0 < 0 or c1 < 0 or c1 <= c0:
+            return 0, 0
+        i0, i1 = c0, c1
     return i0, i1
