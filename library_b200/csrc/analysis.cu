@@ -319,8 +319,8 @@ alphasparseStatus_t analyse_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, 
   p->merge_tiles = (p->rows + p->nnz + kMergeItems - 1) / kMergeItems;
   ASP_CUDA(cudaMalloc(&p->merge_tile_row, sizeof(int32_t) * (p->merge_tiles + 1)));
   ASP_CUDA(cudaMalloc(&p->carry, sizeof(double) * (p->merge_tiles > 0 ? p->merge_tiles : 1)));
-  ASP_CUDA(cudaHostAlloc((void**)&p->dev_err, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable));
-  *p->dev_err = 0;
+  ASP_CUDA(cudaMalloc(&p->dev_err, sizeof(int)));
+  ASP_CUDA(cudaMemsetAsync(p->dev_err, 0, sizeof(int), st));
   {
     int polls = env_int("ASP_WAIT_POLLS", 1 << 22);
     if (polls < 1) polls = 1;
@@ -397,7 +397,7 @@ void free_plan(Plan* p) {
   cudaFree(p->bin_rows);
   cudaFree(p->merge_tile_row);
   cudaFree(p->carry);
-  cudaFreeHost(p->dev_err);
+  cudaFree(p->dev_err);
   cudaFree(p->spmm_carry);
   if (p->spmm_tc) free_spmm_tc_plan(p->spmm_tc);
   if (p->spmm_stage) free_spmm_stage_plan(p->spmm_stage);
@@ -578,7 +578,9 @@ alphasparseStatus_t alphasparseCsrPlanGet(alphasparseHandle_t h, alphasparseSpMa
     stats[ASP_STAT_VARIANT] = p->variant_auto;
     stats[ASP_STAT_IDENTITY_SHORT] = p->identity_short ? 1 : 0;
     stats[ASP_STAT_NNZ_SHORT] = p->nnz_short;
-    stats[ASP_STAT_DEVICE_ERROR] = p->dev_err ? *(volatile int*)p->dev_err : 0;  // the stream was synchronised above
+    int e = 0;
+    if (p->dev_err) ASP_CUDA(cudaMemcpy(&e, p->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
+    stats[ASP_STAT_DEVICE_ERROR] = e;
   }
   if (bin_rows && p->rows > 0) {
     if (p->identity_short) {

@@ -58,9 +58,8 @@ struct Plan {
   int64_t merge_tiles = 0;
   int32_t* merge_tile_row = nullptr;  // device, merge_tiles + 1
   void* carry = nullptr;              // device, merge_tiles * 8 bytes (used when no external buffer)
-  // Flag a kernel raises when a bounded wait expires: one int in pinned host memory mapped into the
-  // device's address space, so that only a failing CTA ever touches it and the host can look at it
-  // without a synchronisation (the next call on the plan does, and refuses).
+  // Device flag a kernel raises when a bounded wait expires (read back, after a synchronisation, by
+  // alphasparseCsrPlanGet).
   int* dev_err = nullptr;
   // Polls a bounded device-side wait may take (bit 31: testing only - the copy the wait is for is not
   // issued, so the wait does run out).  Read from ASP_WAIT_POLLS / ASP_TEST_DROP_COPY at analysis.

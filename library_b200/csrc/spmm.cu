@@ -539,7 +539,6 @@ alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t h, alphasparseOperation_
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   }
   if (plan_of(A)->device != h->device) return ALPHA_SPARSE_STATUS_INVALID_VALUE;  // the plan's arrays live on another GPU
-  if (plan_of(A)->dev_err && *(volatile int*)plan_of(A)->dev_err) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
   if (B->order == ALPHASPARSE_ORDER_COL) {
     // Column-major B and C: row-major copies in the caller's buffer (sizes: alphasparseSpMM_bufferSize),
     // the row-major kernel, and C copied back.  B and C themselves keep their layout.

@@ -848,8 +848,6 @@ alphasparseStatus_t alphasparseSpMV(alphasparseHandle_t h, alphasparseOperation_
   Plan* p = plan_of(A);
   if (p->rows != A->rows || p->nnz != A->nnz || p->cols != A->cols) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
   if (p->device != h->device) return ALPHA_SPARSE_STATUS_INVALID_VALUE;  // the plan's arrays live on another GPU
-  // a kernel of an earlier call on this matrix gave up on a bounded wait: its result was incomplete
-  if (p->dev_err && *(volatile int*)p->dev_err) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
   if (A->data_type == ALPHA_C_32F || A->data_type == ALPHA_C_64F || A->data_type == ALPHA_R_8I) {
     p->last_variant = kVariantBinned;  // complex and int8 instances: the row-length-binned kernel of spmv_types.cu
     return spmv_other_run(h, A, p, x->values, y->values, y->data_type, alpha, beta);
