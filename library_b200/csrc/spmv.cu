@@ -474,6 +474,7 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   __shared__ T s_wval[kThreads / 32];
   __shared__ int s_wflag[kThreads / 32];
   __shared__ int s_wcnt[kThreads / 32];
+  __shared__ int s_vote[2];  // [0]: some thread's wait ran out, [1]: some row segment is long
   static_assert(IPT == 8, "a thread's row-end bytes are read as one 8-byte word");
 
   const int tid = threadIdx.x;
@@ -489,6 +490,7 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   const int lo = (int)(nz_s - a0);
 
   if (tid == 0) {
+    s_vote[0] = s_vote[1] = 0;
     mbar_init(&s_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     const int64_t nnz4 = nnz & ~(int64_t)(GA - 1);
@@ -530,8 +532,12 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
       }
     }
   }
-  const int vote = __syncthreads_or((long_seg ? 1 : 0) | (failed ? 2 : 0));
-  if (vote & 2) {
+  // two CTA-wide votes behind one barrier (__syncthreads_or could carry only one: it tells whether any
+  // thread's value was non-zero, not the values' bitwise OR)
+  if (failed) s_vote[0] = 1;
+  if (long_seg) s_vote[1] = 1;
+  __syncthreads();
+  if (s_vote[0]) {
     if (tid == 0) atomicExch(err, 1);
     __nanosleep(1000000);  // let a copy still in flight land before the CTA's memory is released
     return;
@@ -539,7 +545,7 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   const TA* sv = s_val + lo;
   const int* sc = s_col + lo;
 
-  if (!(vote & 1)) {
+  if (!s_vote[1]) {
     // (3a) one thread per row segment, four entries in flight at a time
     for (int i = tid; i <= tile_rows; i += kThreads) {
       int b, e;
