@@ -488,6 +488,7 @@ enum {
   ASP_STAT_NUM_LONG = 4, ASP_STAT_GROUP_LANES = 5, ASP_STAT_MERGE_ITEMS = 6,
   ASP_STAT_MERGE_TILES = 7, ASP_STAT_VARIANT = 8, ASP_STAT_IDENTITY_SHORT = 9,
   ASP_STAT_NNZ_SHORT = 10, ASP_STAT_DEVICE_ERROR = 11 /* 1 if a kernel's bounded wait ever expired */,
+  ASP_STAT_COL_STEP = 12 /* mean |first column of row r+1 - first column of row r|, rounded */,
   ASP_STAT_COUNT = 16
 };
 alphasparseStatus_t alphasparseCsrPlanGet(alphasparseHandle_t handle,

@@ -33,7 +33,7 @@ MG_X_BROADCAST, MG_X_ALLGATHER, MG_X_WINDOW, MG_X_WINDOW_OVERLAP = 0, 1, 2, 3
 MG_INFO_NAMES = ["window_lo", "window_hi", "bytes_received", "interior_begin", "interior_end", "num_sends",
                  "num_recvs", "mode"]
 STAT_NAMES = ["max_len", "empty_rows", "num_short", "num_medium", "num_long", "group_lanes",
-              "merge_items", "merge_tiles", "variant", "identity_short", "nnz_short", "device_error"]
+              "merge_items", "merge_tiles", "variant", "identity_short", "nnz_short", "device_error", "col_step"]
 
 EXPORTS = [
     "initHandle", "alphasparseGetHandle", "alphasparse_destory_handle", "alphasparseSetStream",

@@ -76,6 +76,31 @@ __global__ void __launch_bounds__(256) col_check_kernel(const int32_t* __restric
   if (__any_sync(0xffffffffu, b) && (threadIdx.x & 31) == 0) atomicMax(bad, 1ull);
 }
 
+// How far the first column moves from one row to the next, summed over neighbouring non-empty rows
+// (out[0]) with the number of such pairs (out[1]).  Small for banded matrices and stencils, where
+// the rows of a tile gather neighbouring parts of x; about cols / 3 for uniformly random columns.
+template <typename OffT>
+__global__ void __launch_bounds__(256) col_step_kernel(const OffT* __restrict__ rp, const int32_t* __restrict__ col,
+                                                       int64_t rows, unsigned long long* __restrict__ out) {
+  unsigned long long sum = 0, cnt = 0;
+  for (int64_t r = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; r + 1 < rows; r += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t a = (int64_t)rp[r], b = (int64_t)rp[r + 1], c = (int64_t)rp[r + 2];
+    if (b > a && c > b) {
+      const int64_t d = (int64_t)col[b] - (int64_t)col[a];
+      sum += (unsigned long long)(d < 0 ? -d : d);
+      ++cnt;
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  }
+  if ((threadIdx.x & 31) == 0 && cnt) {
+    atomicAdd(&out[0], sum);
+    atomicAdd(&out[1], cnt);
+  }
+}
+
 template <typename OffT>
 struct RowClassIs {
   const OffT* rp;
@@ -266,6 +291,17 @@ alphasparseStatus_t analyse_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, 
       return fail(status_of(cudaGetLastError()));
     if (ctr[C_COUNT]) return fail(ALPHA_SPARSE_STATUS_INVALID_VALUE);
   }
+  // column locality of neighbouring rows (the offsets and columns were just validated)
+  if (p->rows > 1 && p->nnz > 0) {
+    unsigned long long step[2] = {0, 0};
+    if (cudaMemsetAsync(d_ctr, 0, sizeof(unsigned long long) * 2, st) != cudaSuccess) return fail(ALPHA_SPARSE_STATUS_INTERNAL_ERROR);
+    col_step_kernel<OffT><<<grid_for(p->rows, sms), 256, 0, st>>>(rp, A->const_col_data, p->rows, d_ctr);
+    impl(h)->launches++;
+    if (cudaMemcpyAsync(step, d_ctr, sizeof step, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess)
+      return fail(status_of(cudaGetLastError()));
+    p->col_step = step[1] ? (double)step[0] / (double)step[1] : 0.0;
+  }
   cudaFree(d_ctr);
   d_ctr = nullptr;
 
@@ -324,8 +360,13 @@ alphasparseStatus_t analyse_t(alphasparseHandle_t h, alphasparseSpMatDescr_t A, 
   {
     int polls = env_int("ASP_WAIT_POLLS", 1 << 22);
     if (polls < 1) polls = 1;
-    p->wait_cfg = (uint32_t)polls & ~kWaitDropCopy;
+    p->wait_cfg = (uint32_t)polls & kWaitPollMask;
     if (env_int("ASP_TEST_DROP_COPY", 0)) p->wait_cfg |= kWaitDropCopy;
+    // A's bulk copies carry an L2 evict-first policy where the rows of a tile gather from all over x
+    // (measured +2 % to +5 % on random and power-law columns: x keeps its place in L2), not where
+    // neighbouring rows read neighbouring columns (measured -1 % on stencils).  ASP_TILE_L2_HINT forces it.
+    const int hint = env_int("ASP_TILE_L2_HINT", -1);
+    if (hint == 0 || (hint < 0 && p->col_step < 64.0)) p->wait_cfg |= kWaitNoL2Hint;
   }
   merge_tile_kernel<OffT><<<(int)((p->merge_tiles + 1 + 255) / 256), 256, 0, st>>>(
       rp, p->rows, p->nnz, p->merge_tiles, kMergeItems, p->merge_tile_row);
@@ -578,6 +619,7 @@ alphasparseStatus_t alphasparseCsrPlanGet(alphasparseHandle_t h, alphasparseSpMa
     stats[ASP_STAT_VARIANT] = p->variant_auto;
     stats[ASP_STAT_IDENTITY_SHORT] = p->identity_short ? 1 : 0;
     stats[ASP_STAT_NNZ_SHORT] = p->nnz_short;
+    stats[ASP_STAT_COL_STEP] = (int64_t)(p->col_step + 0.5);
     int e = 0;
     if (p->dev_err) ASP_CUDA(cudaMemcpy(&e, p->dev_err, sizeof(int), cudaMemcpyDeviceToHost));
     stats[ASP_STAT_DEVICE_ERROR] = e;

@@ -50,6 +50,7 @@ struct Plan {
   bool off64 = false;
   // statistics
   int64_t max_len = 0, empty_rows = 0;
+  double col_step = 0;  // mean |first column of row r+1 - first column of row r| over neighbouring non-empty rows
   int64_t n_short = 0, n_medium = 0, n_long = 0, nnz_short = 0;
   int group_lanes = 4;
   bool identity_short = false;      // every row is short: no row list is needed
@@ -62,7 +63,8 @@ struct Plan {
   // alphasparseCsrPlanGet).
   int* dev_err = nullptr;
   // Polls a bounded device-side wait may take (bit 31: testing only - the copy the wait is for is not
-  // issued, so the wait does run out).  Read from ASP_WAIT_POLLS / ASP_TEST_DROP_COPY at analysis.
+  // issued, so the wait does run out; bit 30: testing only - no L2 policy on the copies of A).  Read from
+  // ASP_WAIT_POLLS / ASP_TEST_DROP_COPY / ASP_TILE_L2_HINT at analysis.
   uint32_t wait_cfg = 1u << 22;
   int variant_auto = kVariantBinned;
   int last_variant = -1;
@@ -114,6 +116,8 @@ inline size_t elem_size(alphasparseDataType t) {
 }
 
 constexpr uint32_t kWaitDropCopy = 1u << 31;
+constexpr uint32_t kWaitNoL2Hint = 1u << 30;  // testing: bulk copies of A without the L2 evict-first policy
+constexpr uint32_t kWaitPollMask = (1u << 30) - 1;
 
 inline int env_int(const char* name, int dflt) {
   const char* s = getenv(name);

@@ -230,7 +230,7 @@ spmm_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   {
     uint32_t tries = 0;
     while (!mbar_try_wait0(&s_bar)) {
-      if (++tries > (wait_cfg & ~kWaitDropCopy)) {
+      if (++tries > (wait_cfg & kWaitPollMask)) {
         failed = true;
         break;
       }

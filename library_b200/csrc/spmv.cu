@@ -438,6 +438,18 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
       : "memory");
 }
 
+// The same copy with an L2 evict-first policy: A is read once, so its lines should be the first to
+// leave L2 and x, which is gathered over and over, should stay.
+__device__ __forceinline__ void bulk_g2s_stream(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
+      : "memory");
+}
+
 constexpr int kTileSlot = kMergeItems + 16;    // entries per staged array (widening adds < 16)
 constexpr int kTileShortSeg = ASP_TILE_SHORT_SEG;
 
@@ -474,7 +486,6 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   __shared__ T s_wval[kThreads / 32];
   __shared__ int s_wflag[kThreads / 32];
   __shared__ int s_wcnt[kThreads / 32];
-  __shared__ int s_vote[2];  // [0]: some thread's wait ran out, [1]: some row segment is long
   static_assert(IPT == 8, "a thread's row-end bytes are read as one 8-byte word");
 
   const int tid = threadIdx.x;
@@ -490,7 +501,6 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   const int lo = (int)(nz_s - a0);
 
   if (tid == 0) {
-    s_vote[0] = s_vote[1] = 0;
     mbar_init(&s_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     const int64_t nnz4 = nnz & ~(int64_t)(GA - 1);
@@ -500,8 +510,13 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
     const uint32_t cnt = (uint32_t)(a1 - a0);
     mbar_expect_tx(&s_bar, cnt * (uint32_t)(sizeof(TA) + sizeof(int)));
     if (cnt && !(wait_cfg & kWaitDropCopy)) {
-      bulk_g2s(s_val, val + a0, cnt * (uint32_t)sizeof(TA), &s_bar);
-      bulk_g2s(s_col, col + a0, cnt * (uint32_t)sizeof(int), &s_bar);
+      if (wait_cfg & kWaitNoL2Hint) {
+        bulk_g2s(s_val, val + a0, cnt * (uint32_t)sizeof(TA), &s_bar);
+        bulk_g2s(s_col, col + a0, cnt * (uint32_t)sizeof(int), &s_bar);
+      } else {
+        bulk_g2s_stream(s_val, val + a0, cnt * (uint32_t)sizeof(TA), &s_bar);
+        bulk_g2s_stream(s_col, col + a0, cnt * (uint32_t)sizeof(int), &s_bar);
+      }
     }
     for (int64_t e = a1 > nz_s ? a1 : nz_s; e < nz_e; ++e) {  // past the last full group of entries
       s_val[e - a0] = val[e];
@@ -526,18 +541,17 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   {
     uint32_t tries = 0;
     while (!mbar_try_wait(&s_bar, 0)) {
-      if (++tries > (wait_cfg & ~kWaitDropCopy)) {
+      if (++tries > (wait_cfg & kWaitPollMask)) {
         failed = true;
         break;
       }
     }
   }
-  // two CTA-wide votes behind one barrier (__syncthreads_or could carry only one: it tells whether any
-  // thread's value was non-zero, not the values' bitwise OR)
-  if (failed) s_vote[0] = 1;
-  if (long_seg) s_vote[1] = 1;
-  __syncthreads();
-  if (s_vote[0]) {
+  // Two CTA-wide votes.  __syncthreads_or tells whether any thread's value was non-zero (not the values'
+  // bitwise OR), so the common case - no long segment, no wait that ran out - takes one barrier, and only
+  // a tile that has either takes a second one to tell them apart.
+  const int any_long_or_failed = __syncthreads_or((long_seg || failed) ? 1 : 0);
+  if (any_long_or_failed && __syncthreads_or(failed ? 1 : 0)) {
     if (tid == 0) atomicExch(err, 1);
     __nanosleep(1000000);  // let a copy still in flight land before the CTA's memory is released
     return;
@@ -545,7 +559,7 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   const TA* sv = s_val + lo;
   const int* sc = s_col + lo;
 
-  if (!s_vote[1]) {
+  if (!any_long_or_failed) {
     // (3a) one thread per row segment, four entries in flight at a time
     for (int i = tid; i <= tile_rows; i += kThreads) {
       int b, e;

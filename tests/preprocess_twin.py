@@ -28,7 +28,20 @@ def merge_path_row(row_end, nnz, diag):
     return lo
 
 
-def plan(row_ptr, val_bytes):
+def col_step(row_ptr, col_idx):
+    """Mean |first column of row r+1 - first column of row r| over neighbouring non-empty rows, rounded
+    half up (the statistic that decides the L2 policy of the bulk copies of A)."""
+    row_ptr = np.asarray(row_ptr, dtype=np.int64)
+    col_idx = np.asarray(col_idx, dtype=np.int64)
+    a, b, c = row_ptr[:-2], row_ptr[1:-1], row_ptr[2:]
+    ok = (b > a) & (c > b)
+    if not ok.any():
+        return 0
+    d = np.abs(col_idx[b[ok]] - col_idx[a[ok]])
+    return int(int(d.sum()) / int(ok.sum()) + 0.5)
+
+
+def plan(row_ptr, val_bytes, col_idx=None):
     row_ptr = np.asarray(row_ptr, dtype=np.int64)
     rows = len(row_ptr) - 1
     nnz = int(row_ptr[-1]) if rows >= 0 and len(row_ptr) else 0
@@ -54,4 +67,6 @@ def plan(row_ptr, val_bytes):
     stats = dict(max_len=max_len, empty_rows=empty, num_short=n_short, num_medium=n_medium,
                  num_long=n_long, group_lanes=g, merge_items=MERGE_ITEMS, merge_tiles=tiles,
                  variant=variant, identity_short=int(n_short == rows), nnz_short=nnz_short, device_error=0)
+    if col_idx is not None:
+        stats["col_step"] = col_step(row_ptr, col_idx)
     return stats, bins, tile_row

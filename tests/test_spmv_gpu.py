@@ -180,8 +180,8 @@ def test_preprocessing_bit_exact(handle, kind):
     Am = api.CsrMatrix.from_csr(A)
     Am.analyse(handle)
     stats, bins, tiles = Am.plan(handle)
-    rp, _, _ = A.numpy()
-    want_stats, want_bins, want_tiles = twin.plan(rp, 4)
+    rp, ci, _ = A.numpy()
+    want_stats, want_bins, want_tiles = twin.plan(rp, 4, ci)
     assert stats == want_stats
     assert np.array_equal(bins, want_bins)
     assert np.array_equal(tiles, want_tiles)
@@ -194,7 +194,7 @@ def test_preprocessing_skewed_bit_exact(handle):
                        torch.from_numpy(v).to(dev))
     Am.analyse(handle)
     stats, bins, tiles = Am.plan(handle)
-    want_stats, want_bins, want_tiles = twin.plan(rp, 8)
+    want_stats, want_bins, want_tiles = twin.plan(rp, 8, ci)
     assert stats == want_stats and np.array_equal(bins, want_bins) and np.array_equal(tiles, want_tiles)
     assert stats["num_long"] == 3 and stats["num_medium"] == 1 and stats["variant"] == 0
 
