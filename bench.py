@@ -409,12 +409,23 @@ def cpu_baseline_subprocess(args):
 # our arm
 # ------------------------------------------------------------------------------------------------
 
+def align_ranks(stream):
+    """A device-side meeting point on the timing stream: the ranks leave the host barrier up to milliseconds
+    apart, and without this the first step's exchange would absorb that skew into the timed region."""
+    import torch
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        with torch.cuda.stream(stream):
+            dist.all_reduce(torch.zeros(1, device="cuda"))
+
+
 def time_steps(fn, stream, steps, warmup, barrier):
     import torch
     for _ in range(warmup):
         fn()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    align_ranks(stream)
     e0.record(stream)
     for _ in range(steps):
         fn()
@@ -585,9 +596,12 @@ def run_ours(args):
     l0 = h.launches
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
+        align_ranks(stream)
         ev0.record(stream)
+        t_host = time.perf_counter()
         for _ in range(args.steps):
             step()
+        t_host = (time.perf_counter() - t_host) / args.steps * 1e3   # host time to enqueue a step (no synchronisation inside)
         ev1.record(stream)
         barrier()
     ms = ev0.elapsed_time(ev1)
@@ -693,6 +707,7 @@ def run_ours(args):
             e2e_step(i)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        align_ranks(s_in)
         e0.record(s_in)
         for i in range(e_steps):
             e2e_step(i)
@@ -761,7 +776,10 @@ def run_ours(args):
                                      "broadcast": "whole on rank 0, broadcast before the product"}[args.exchange]
                                     if spmv else "replicated by NCCL broadcast inside the step")
                                  + "; the exchange is inside the timed region"),
-                    "step_parts_ms": extras or None},
+                    "step_parts_ms": extras or None,
+                    "timing": "CUDA events on the launching stream around the K steps, max over ranks"
+                              + ("; the ranks meet in a device-side all-reduce on that stream right before the first event "
+                                 "(they leave the host barrier up to milliseconds apart)" if world > 1 else "")},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                          "peak_source": peak_src,
                          "traffic": (TRAFFIC_RATIO[args.workload] * nbytes / world) if args.workload in TRAFFIC_RATIO else None,
@@ -769,6 +787,7 @@ def run_ours(args):
                          "note": "achieved = this GPU's share of the algorithmic bytes (x counted once over all GPUs) / "
                                  "time of a whole step" + (", exchange included" if world > 1 else "")},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk.summary(),
+            "host_enqueue_ms_per_step": t_host,
         }
         if per_config is not None:
             line["per_config"] = per_config
