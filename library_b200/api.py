@@ -148,8 +148,12 @@ class DnVec:
                "alphasparseCreateDnVec")
 
     def __del__(self):
-        if getattr(self, "d", None):
-            load().alphasparseDestroyDnVec(self.d)
+        # at interpreter shutdown module globals may already be gone: then the process's exit frees the descriptor
+        if getattr(self, "d", None) and load is not None:
+            try:
+                load().alphasparseDestroyDnVec(self.d)
+            except Exception:
+                pass
 
 
 class DnVecWindow(DnVec):
@@ -182,8 +186,12 @@ class DnMat:
                                              self.order), "alphasparseCreateDnMat")
 
     def __del__(self):
-        if getattr(self, "d", None):
-            load().alphasparseDestroyDnMat(self.d)
+        # at interpreter shutdown module globals may already be gone: then the process's exit frees the descriptor
+        if getattr(self, "d", None) and load is not None:
+            try:
+                load().alphasparseDestroyDnMat(self.d)
+            except Exception:
+                pass
 
 
 class CsrMatrix:
@@ -228,8 +236,12 @@ class CsrMatrix:
         return load().alphasparseCsrLastVariant(self.d).decode()
 
     def __del__(self):
-        if getattr(self, "d", None):
-            load().alphasparseDestroySpMat(self.d)
+        # at interpreter shutdown module globals may already be gone: then the process's exit frees the descriptor
+        if getattr(self, "d", None) and load is not None:
+            try:
+                load().alphasparseDestroySpMat(self.d)
+            except Exception:
+                pass
 
 
 def spmv_buffer_size(handle: Handle, A: CsrMatrix, x: DnVec, y: DnVec, alpha=1.0, beta=0.0,
