@@ -25,6 +25,7 @@
 #include <cub/device/device_reduce.cuh>
 #include <cub/device/device_scan.cuh>
 
+#include <cstdio>
 #include <new>
 
 #include "asp_internal.h"
@@ -60,6 +61,11 @@ struct TcPlan {
   // order), so that a tile is filled by independent threads instead of one serial walk per row:
   int32_t* chunk_ent = nullptr;   // device, parallel to chunk_list: first position in `scatter` of the chunk's entries
   uint32_t* scatter = nullptr;    // device, nnz words: where the entry comes from and where it goes
+  // For the kernel that keeps A in tensor memory (a thread builds its own row of a chunk):
+  uint32_t* runs = nullptr;       // device, 128 words per chunk slot: (first entry of the row's run in the chunk,
+                                  // counted from the block's first entry rounded down to 16) << 7 | entries in the run
+  uint8_t* kcol = nullptr;        // device, nnz bytes: the entry's column modulo 64 (its position in the chunk)
+  bool runs_tried = false;
 };
 
 // ---- preprocessing -------------------------------------------------------------------------
@@ -189,6 +195,37 @@ __global__ void __launch_bounds__(128) tc_scatter_kernel(const int32_t* __restri
     }
     if (!FILL) counts[j0 + j] = n;
   }
+}
+
+// One CTA per row block, one thread per chunk of the block: for every row the run of its (ascending)
+// columns inside the chunk, as (offset of the run's first entry from the block's first entry rounded
+// down to a multiple of 16) << 7 | length.  Rows past the matrix keep the zero the array was cleared to.
+__global__ void __launch_bounds__(128) tc_runs_kernel(const int32_t* __restrict__ rp, const int32_t* __restrict__ col,
+                                                      int64_t rows, const int32_t* __restrict__ chunk_off,
+                                                      const int32_t* __restrict__ chunk_cnt,
+                                                      const int32_t* __restrict__ chunk_list,
+                                                      uint32_t* __restrict__ runs) {
+  __shared__ int s_rp[TC_M + 1];
+  const int64_t r0 = (int64_t)blockIdx.x * TC_M;
+  const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
+  for (int i = threadIdx.x; i <= nr; i += 128) s_rp[i] = rp[r0 + i];
+  __syncthreads();
+  const int j0 = chunk_off[blockIdx.x], nch = chunk_cnt[blockIdx.x];
+  const int a0 = s_rp[0] & ~15;
+  for (int j = threadIdx.x; j < nch; j += 128) {
+    const int cbeg = chunk_list[j0 + j] * TC_KC, cend = cbeg + TC_KC;
+    uint32_t* out = runs + (size_t)(j0 + j) * TC_M;
+    for (int r = 0; r < nr; ++r) {
+      const int lo = lower_bound_col(col, s_rp[r], s_rp[r + 1], cbeg);
+      const int hi = lower_bound_col(col, lo, s_rp[r + 1], cend);
+      out[r] = ((uint32_t)(lo - a0) << 7) | (uint32_t)(hi - lo);
+    }
+  }
+}
+__global__ void __launch_bounds__(256) tc_kcol_kernel(const int32_t* __restrict__ col, int64_t nnz,
+                                                      uint8_t* __restrict__ kcol) {
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < nnz; i += (int64_t)gridDim.x * 256)
+    kcol[i] = (uint8_t)(col[i] % TC_KC);
 }
 
 // ---- PTX helpers ---------------------------------------------------------------------------
@@ -560,6 +597,34 @@ __device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
+// One lane of the (converged) warp: unlike `lane == 0`, elect.sync tells the compiler that exactly
+// one thread runs the guarded code, so that the operands of the instructions that take them from
+// uniform registers (tcgen05.mma, tcgen05.commit, the TMA and bulk copies) need no per-lane
+// serialisation.  Every lane named in the mask has to execute it.
+__device__ __forceinline__ bool elect_one(uint32_t mask = 0xffffffffu) {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, %1;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred)
+      : "r"(mask));
+  return pred != 0;
+}
+
+// One non-blocking test of a barrier's phase.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -571,7 +636,8 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
                           int64_t nnz, int n, int nblocks, int sb,
                           const int32_t* __restrict__ chunk_off, const int32_t* __restrict__ chunk_cnt,
                           const int32_t* __restrict__ chunk_list, const int32_t* __restrict__ chunk_ent,
-                          const uint32_t* __restrict__ scatter, int one_box, int* __restrict__ err) {
+                          const uint32_t* __restrict__ scatter, int one_box, int issuers_max,
+                          int* __restrict__ err) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int nblk = n / 64;
@@ -594,13 +660,15 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(st_empty + sb);
   volatile int* s_fail = reinterpret_cast<volatile int*>(s_tmem + 1);
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // the warp number through a shuffle: provably the same in every lane, so that what derives from
+  // it (roles, ring stages, descriptors) can live in uniform registers
+  const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
   const uint32_t acc_cols = n <= 64 ? 64u : (n <= 128 ? 128u : 256u);
   // Two threads issue MMAs when tensor memory holds four accumulators (N <= 128): chunks with an
   // even running number go to one, odd ones to the other, each into an accumulator of its own
   // (the epilogue adds them).  One thread's stream of wait / 4 x tcgen05.mma / commit costs about
   // twice the 256 cycles the tensor core needs for a chunk, so a single issuer halves its rate.
-  const int issuers = acc_cols <= 128u ? 2 : 1;
+  const int issuers = (acc_cols <= 128u && issuers_max >= 2) ? 2 : 1;
 
   for (int i = tid; i < sb * TC_A_BYTES / 16; i += TCP_THREADS)
     reinterpret_cast<uint4*>(sA)[i] = make_uint4(0, 0, 0, 0);
@@ -698,8 +766,11 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
     }
   } else if (warp >= TCP_BWARPS + 5) {
     // ---------------- MMA issuers ----------------
+    // The whole warp walks the loop (every lane polls, votes keep the lanes together) and one
+    // elected lane issues: with a lone thread behind `lane == 0` the stream of a chunk - wait,
+    // four MMAs, commit - took about twice the tensor core's time for it.
     const int w = warp - (TCP_BWARPS + 5);
-    if (lane == 0 && w < issuers) {
+    if (w < issuers) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(n >> 3) << 17) |
                              ((uint32_t)(TC_M >> 4) << 24);
       bool ok = true;
@@ -710,9 +781,8 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
         ph ^= 1u;
       }
       uint32_t cnum0 = 0, mine = (uint32_t)w;  // running numbers: the block's first chunk, this issuer's next chunk
-      // The issuing thread's instruction stream is the pipeline's clock: keep it short.  A stage's
-      // descriptors differ from stage 0's only in the low word (the 14-bit address field), so the
-      // loop adds small constants instead of rebuilding 64-bit descriptors.
+      // A stage's descriptors differ from stage 0's only in the low word (the 14-bit address
+      // field), so the loop adds small constants instead of rebuilding 64-bit descriptors.
       const uint64_t ad0 = umma_desc(smem_u32(sA), 2048, 128, 0);
       const uint64_t bd0 = umma_desc(smem_u32(sB), TC_BBLK, 1024, 2);
       const uint32_t a_hi = (uint32_t)(ad0 >> 32), b_hi = (uint32_t)(bd0 >> 32);
@@ -723,7 +793,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
         const int acc = (i & 1) * issuers + w;
         const int nch = nch_next;  // fetched one block ahead: no global latency between blocks
         if (i + 1 < n_my) nch_next = chunk_cnt[first + (i + 1) * stride];
-        if (!mbar_wait(&acc_empty[i & 1], (uint32_t)(((i >> 1) & 1) ^ 1))) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&acc_empty[i & 1], (uint32_t)(((i >> 1) & 1) ^ 1)))) {
           ok = false;
           break;
         }
@@ -731,7 +801,7 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
         const uint32_t d = tmem + (uint32_t)acc * acc_cols;
         uint32_t first_acc = 0u;  // the issuer's first MMA of the block overwrites its accumulator
         for (int j = (int)(mine - cnum0); j < nch; j += issuers, mine += (uint32_t)issuers) {
-          if (!mbar_spin(&st_full[st], ph)) {
+          if (!__all_sync(0xffffffffu, mbar_spin(&st_full[st], ph))) {
             ok = false;
             break;
           }
@@ -739,12 +809,15 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
           // the builders' stores (made visible to the async proxy by their fence.proxy.async); a
           // fence in this loop would make the issuing thread wait for the previous chunk's MMAs
           const uint32_t a_lo = a_lo0 + (uint32_t)st * a_step, b_lo = b_lo0 + (uint32_t)st * b_step;
-          umma_bf16_lohi(d, a_lo, a_hi, b_lo, b_hi, idesc, first_acc);
+          if (elect_one()) {
+            umma_bf16_lohi(d, a_lo, a_hi, b_lo, b_hi, idesc, first_acc);
 #pragma unroll
-          for (uint32_t kk = 1; kk < TC_KC / 16; ++kk)
-            umma_bf16_lohi(d, a_lo + kk * 256u, a_hi, b_lo + kk * 128u, b_hi, idesc, 1u);
+            for (uint32_t kk = 1; kk < TC_KC / 16; ++kk)
+              umma_bf16_lohi(d, a_lo + kk * 256u, a_hi, b_lo + kk * 128u, b_hi, idesc, 1u);
+            umma_commit(&st_empty[st]);
+          }
+          __syncwarp();
           first_acc = 1u;
-          umma_commit(&st_empty[st]);
           st += issuers;
           while (st >= sb) {
             st -= sb;
@@ -752,7 +825,9 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
           }
         }
         cnum0 += (uint32_t)nch;
-        if (ok) umma_commit(&acc_full[i & 1]);  // also with no chunk of its own: the barrier counts the issuers
+        // also with no chunk of its own: the barrier counts the issuers
+        if (ok && elect_one()) umma_commit(&acc_full[i & 1]);
+        __syncwarp();
       }
       if (!ok) *s_fail = 1;
     }
@@ -813,10 +888,11 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
             // the slice's latency runs under the build, and four groups issue side by side
             // (one instruction for the whole slice when the map is the three-dimensional view
             // [column block][row][64 columns]: issuing a copy costs the warp some 300 cycles)
-            if (lane == 0) {
+            if (elect_one(__activemask())) {
               mbar_expect_tx(&st_full[sa], (uint32_t)b_stage_bytes);
               if (one_box) tma_load_3d(sB + (size_t)sa * b_stage_bytes, &tmB, 0, brow, 0, &st_full[sa]);
             }
+            __syncwarp();
             if (!one_box && lane < nblk)
               tma_load_2d(sB + (size_t)sa * b_stage_bytes + lane * TC_BBLK, &tmB, lane * 64, brow, &st_full[sa]);
           }
@@ -930,6 +1006,582 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
   }
   if (warp == TCP_BWARPS + 5)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2u * (uint32_t)issuers * acc_cols) : "memory");
+}
+
+// ------------------------------------------------------------------------------------------
+// The same pipeline with A in tensor memory (N <= 128).  tcgen05.mma takes its A operand from
+// tensor memory as well as from shared memory: lane = row, a 32-bit column = two consecutive bf16
+// of the row.  A builder thread then owns one row of the chunk: it drops the row's few entries
+// into a private 128-byte line of shared memory (no other thread touches it: no barrier, no
+// async-proxy fence, no clear of a 16 KB tile), reads the line back as 32 registers, zeroes what
+// it wrote and hands the registers to tensor memory with one tcgen05.st.  What that frees:
+//   * the A tiles' shared memory goes to B slices: six ring stages at N = 128 instead of four;
+//   * the MMAs read half as much shared memory (B only);
+//   * one warp issues (all lanes walk the loop, one elected lane issues: its stream keeps up with
+//     the tensor core), so two accumulators are enough and tensor memory has room for the A stages:
+//     columns [0, 2 acc) accumulators of two row blocks, then 32 columns per ring stage.
+//   warps 0-11  builders : three groups of 128 threads (thread = row = tensor-memory lane) take
+//                          chunks in turn; a group owns ring stages g and g + 3
+//   warps 12-15 epilogue, warp 16 producer (values, column bytes and chunk ids of the next row
+//   block by bulk copies), warp 17 MMA.
+// The plan holds, per chunk and row, where the row's run of entries inside the chunk starts and
+// how long it is (tc_runs_kernel), and per entry its column modulo 64 as a byte.
+// ------------------------------------------------------------------------------------------
+constexpr int TCT_GROUPS = 3;
+constexpr int TCT_BWARPS = TCT_GROUPS * 4;
+constexpr int TCT_STAGES = 2 * TCT_GROUPS;
+constexpr int TCT_THREADS = (TCT_BWARPS + 6 + TCT_GROUPS + 1) * 32;
+constexpr int TCT_MMA2 = TCT_BWARPS + 6 + TCT_GROUPS;   // the second issuing warp
+constexpr int TCT_CSR = 2;
+constexpr int TCT_CAPB = TC_CAP + 16;      // staged entries of a row block (slice widened to multiples of 16)
+constexpr int TCT_RUNCH = 32;              // chunks of a row block whose run words are staged (the rest: global loads)
+constexpr int TCT_PRIV = TC_M * 128;       // a group's private lines: 128 rows x 64 bf16
+constexpr uint32_t TCT_TMEM_COLS = 512;
+constexpr int TCT_TRLD = 36;               // floats per row of an epilogue warp's transposition tile
+constexpr int TCT_TRBYTES = 5120;          // an epilogue warp's tile: 32 x TCT_TRLD floats, or 32 x 128 bytes for a TMA store
+#ifndef ASP_TCT_TRACE_ON
+#define ASP_TCT_TRACE_ON 0
+#endif
+#ifndef ASP_TCT_ISSUE_FENCE
+#define ASP_TCT_ISSUE_FENCE 0
+#endif
+static_assert(TC_KC == 64, "a row of a chunk is one 128-byte line / 32 tensor-memory columns");
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+// A from tensor memory, B through a shared-memory descriptor given as (low, high) words.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi,
+                                             uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// A load that stays where it is written: the compiler is free to sink a plain load of read-only
+// data to its first use, which puts the whole global latency back into the chunk's chain.
+__device__ __forceinline__ uint32_t ldg_here_u32(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Generic loads (shared or global memory) that stay where they are written.
+__device__ __forceinline__ uint32_t ld_here_u8(const void* p) {
+  uint32_t v;
+  asm volatile("ld.u8 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_here_u16(const void* p) {
+  uint32_t v;
+  asm volatile("ld.u16 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts_b32(uint32_t saddr, uint32_t v) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(saddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sts_b16(uint32_t saddr, uint16_t v) {
+  asm volatile("st.shared.b16 [%0], %1;" ::"r"(saddr), "h"(v) : "memory");
+}
+// The load happens only where `on` is set; elsewhere the registers keep what they hold.
+__device__ __forceinline__ void lds_v4_if(uint32_t on, uint32_t saddr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "@p ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n\t}"
+      : "+r"(a), "+r"(b), "+r"(c), "+r"(d)
+      : "r"(saddr), "r"(on)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(TCT_THREADS, 1)
+spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC, int c_by_tma,
+                    const int32_t* __restrict__ rp,
+                    const __nv_bfloat16* __restrict__ val, float* __restrict__ C, int64_t ldc, float alpha,
+                    float beta, int64_t rows, int64_t nnz, int n, int nblocks,
+                    const int32_t* __restrict__ chunk_off, const int32_t* __restrict__ chunk_cnt,
+                    const int32_t* __restrict__ chunk_list, const uint32_t* __restrict__ runs,
+                    const uint8_t* __restrict__ kcol, int one_box, int issuers_max, int dbg, long long* __restrict__ trace,
+                    int* __restrict__ err) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const int nblk = n / 64;
+  const int b_stage_bytes = nblk * TC_BBLK;
+  unsigned char* sB = smem;                                                   // TCT_STAGES x b_stage_bytes
+  unsigned char* sP = sB + (size_t)TCT_STAGES * b_stage_bytes;                // TCT_GROUPS x 16 KB private lines
+  float* s_tr = reinterpret_cast<float*>(sP + TCT_GROUPS * TCT_PRIV);                    // 4 x TCT_TRBYTES, 1,024-byte aligned
+  __nv_bfloat16* s_val = reinterpret_cast<__nv_bfloat16*>(s_tr + 4 * (TCT_TRBYTES / 4)); // TCT_CSR x TCT_CAPB
+  uint8_t* s_k = reinterpret_cast<uint8_t*>(s_val + TCT_CSR * TCT_CAPB);                 // TCT_CSR x TCT_CAPB
+  uint32_t* s_runs = reinterpret_cast<uint32_t*>(s_k + TCT_CSR * TCT_CAPB);              // TCT_CSR x TCT_RUNCH x 128
+  int* s_hdr = reinterpret_cast<int*>(s_runs + TCT_CSR * TCT_RUNCH * TC_M);              // TCT_CSR x 4: e0, e1, chunks, first slot
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_hdr + TCT_CSR * 4);
+  uint64_t* csr_full = bars;            // [TCT_CSR]
+  uint64_t* csr_empty = bars + 4;       // [TCT_CSR]
+  uint64_t* acc_full = bars + 8;        // [2]
+  uint64_t* acc_empty = bars + 10;      // [2]
+  uint64_t* st_full = bars + 12;        // [TCT_STAGES] A stage stored (4 builder warps) and B slice landed
+  uint64_t* st_empty = st_full + TCT_STAGES;  // [TCT_STAGES] the chunk's MMAs retired
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(st_empty + TCT_STAGES);
+  volatile int* s_fail = reinterpret_cast<volatile int*>(s_tmem + 1);
+
+  const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
+  const uint32_t acc_cols = n <= 64 ? 64u : 128u;
+  const uint32_t a_col0 = 2u * acc_cols;
+  // The tensor core's queue is short: what an issuing warp does between two chunks (the wait for the
+  // next stage, votes, the loop) is time the core idles.  At N = 128 two warps therefore issue, each
+  // the MMAs of one 64-column half of every chunk (same A, its own half of the B slice and of the
+  // accumulator): one warp's bookkeeping runs under the other's MMAs.
+  const int issuers = (n == 128 && issuers_max >= 2) ? 2 : 1;
+
+  for (int i = tid; i < TCT_GROUPS * TCT_PRIV / 16; i += TCT_THREADS)
+    reinterpret_cast<uint4*>(sP)[i] = make_uint4(0, 0, 0, 0);
+  if (tid == 0) {
+    for (int i = 0; i < TCT_CSR; ++i) {
+      mbar_init(&csr_full[i], 1);
+      mbar_init(&csr_empty[i], TCT_BWARPS);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], (uint32_t)issuers);
+      mbar_init(&acc_empty[i], 4);
+    }
+    for (int i = 0; i < TCT_STAGES; ++i) {
+      mbar_init(&st_full[i], 4 + 1);   // the group's warps and the thread that announces the B slice's bytes
+      mbar_init(&st_empty[i], (uint32_t)issuers);
+    }
+    *s_fail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == TCT_BWARPS + 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
+                 "r"(TCT_TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *s_tmem;
+
+  const int first = blockIdx.x, stride = gridDim.x;
+  const int n_my = first < nblocks ? (nblocks - first + stride - 1) / stride : 0;
+
+  if (warp == TCT_BWARPS + 4) {
+    // ---------------- producer: the next row block's values, column bytes and chunk ids ----------------
+    int p_e0 = 0, p_e1 = 0, p_j0 = 0, p_nch = 0;
+    auto prefetch = [&](int i) {
+      const int b = first + i * stride;
+      const int64_t r0 = (int64_t)b * TC_M;
+      const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
+      p_e0 = rp[r0];
+      p_e1 = rp[r0 + nr];
+      p_j0 = chunk_off[b];
+      p_nch = chunk_cnt[b];
+    };
+    auto stage_csr = [&](int i) -> bool {
+      const int cs = i % TCT_CSR;
+      if (!__all_sync(0xffffffffu, mbar_wait(&csr_empty[cs], (uint32_t)(((i / TCT_CSR) & 1) ^ 1)))) return false;
+      const int e0 = p_e0, e1 = p_e1, j0 = p_j0, nch = p_nch;
+      if (i + 1 < n_my) prefetch(i + 1);
+      if (elect_one()) {
+        // the block's scalars travel with its data: the builders load nothing from global memory
+        int* hdr = s_hdr + cs * 4;
+        hdr[0] = e0;
+        hdr[1] = e1;
+        hdr[2] = nch;
+        hdr[3] = j0;
+        const int a0 = e0 & ~15;
+        const bool staged = (e1 - a0) <= TC_CAP;
+        __nv_bfloat16* dv = s_val + cs * TCT_CAPB;
+        uint8_t* dk = s_k + cs * TCT_CAPB;
+        uint32_t cnt = 0;
+        if (staged) {
+          int a1 = (e1 + 15) & ~15;
+          const int nnz16 = (int)(nnz & ~(int64_t)15);
+          if (a1 > nnz16) a1 = nnz16;
+          if (a1 < a0) a1 = a0;
+          cnt = (uint32_t)(a1 - a0);
+          for (int e = a1 > e0 ? a1 : e0; e < e1; ++e) {  // past the arrays' last full group of 16
+            dv[e - a0] = val[e];
+            dk[e - a0] = kcol[e];
+          }
+        }
+        const uint32_t nrun = (uint32_t)(nch < TCT_RUNCH ? nch : TCT_RUNCH);
+        mbar_expect_tx(&csr_full[cs], cnt * 3u + nrun * (TC_M * 4u));
+        if (cnt) {
+          bulk_g2s(dv, val + a0, cnt * 2u, &csr_full[cs]);
+          bulk_g2s(dk, kcol + a0, cnt, &csr_full[cs]);
+        }
+        if (nrun) bulk_g2s(s_runs + cs * (TCT_RUNCH * TC_M), runs + (size_t)j0 * TC_M, nrun * (TC_M * 4u), &csr_full[cs]);
+      }
+      __syncwarp();
+      return true;
+    };
+    bool ok = true;
+    if (n_my > 0) {
+      prefetch(0);
+      ok = stage_csr(0);
+    }
+    for (int i = 0; i < n_my && ok; ++i)
+      if (i + 1 < n_my) ok = stage_csr(i + 1);
+    if (!ok) *s_fail = 1;
+  } else if (warp == TCT_BWARPS + 5 || warp == TCT_MMA2) {
+    // ---------------- MMA: the whole warp walks the loop, one elected lane issues ----------------
+    const int half = warp == TCT_MMA2 ? 1 : 0;
+    const int n_mma = n / issuers;   // columns of an MMA
+    if (half < issuers) {
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(n_mma >> 3) << 17) |
+                           ((uint32_t)(TC_M >> 4) << 24);
+    bool ok = true, ready = false;
+    int st = 0, tn = 0;
+    uint32_t ph = 0;
+    const uint64_t bd0 = umma_desc(smem_u32(sB), TC_BBLK, 1024, 2);
+    const uint32_t b_hi = (uint32_t)(bd0 >> 32), b_lo0 = (uint32_t)bd0 + (uint32_t)half * (TC_BBLK >> 4);
+    const uint32_t b_step = (uint32_t)b_stage_bytes >> 4;
+    int nch_next = n_my > 0 ? chunk_cnt[first] : 0;
+    for (int i = 0; i < n_my && ok; ++i) {
+      const int nch = nch_next;  // fetched one block ahead: no global latency between blocks
+      if (i + 1 < n_my) nch_next = chunk_cnt[first + (i + 1) * stride];
+      if (!__all_sync(0xffffffffu, mbar_wait(&acc_empty[i & 1], (uint32_t)(((i >> 1) & 1) ^ 1)))) {
+        ok = false;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t d = tmem + (uint32_t)(i & 1) * acc_cols + (uint32_t)(half * n_mma);
+      uint32_t first_acc = 0u;  // the block's first MMA overwrites the accumulator
+      for (int j = 0; j < nch; ++j) {
+        const bool TR = ASP_TCT_TRACE_ON && trace && blockIdx.x == 0 && lane == 0 && tn < 144;
+        if (TR) trace[512 + tn * 4 + 0] = clock64();
+        if (!ready && !__all_sync(0xffffffffu, (dbg & 64) ? mbar_wait(&st_full[st], ph) : mbar_spin(&st_full[st], ph))) {
+          ok = false;
+          break;
+        }
+        if (TR) trace[512 + tn * 4 + 1] = clock64();
+        // No tcgen05.fence::after_thread_sync here (it changed nothing in the measured time, and the
+        // kernel that reads A from shared memory has none either): the builders' tcgen05.st have
+        // completed (their wait::st) before they arrive on the barrier, and the MMAs are issued
+        // after the wait on it has returned.
+#if ASP_TCT_ISSUE_FENCE
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#endif
+        const uint32_t a_t = tmem + a_col0 + (uint32_t)st * 32u, b_lo = b_lo0 + (uint32_t)st * b_step;
+        // The tensor core takes the next MMA while it works on one, but its queue is short: what the
+        // warp does between a chunk's last MMA and the next chunk's first one is time the core
+        // idles.  So the next stage's barrier is tested before this chunk's MMAs go out, the vote on
+        // the answer sits before the last MMA, and only the commit and the loop's branch follow it.
+        const int st_n = st + 1 == TCT_STAGES ? 0 : st + 1;
+        const uint32_t ph_n = st + 1 == TCT_STAGES ? ph ^ 1u : ph;
+        const bool early = mbar_test(&st_full[st_n], ph_n);
+        if (elect_one() && !(dbg & 8)) {
+          umma_bf16_ts(d, a_t, b_lo, b_hi, idesc, first_acc);
+          umma_bf16_ts(d, a_t + 8u, b_lo + 128u, b_hi, idesc, 1u);
+          umma_bf16_ts(d, a_t + 16u, b_lo + 256u, b_hi, idesc, 1u);
+        }
+        ready = __all_sync(0xffffffffu, early);
+        if (elect_one()) {
+          if (!(dbg & 8)) umma_bf16_ts(d, a_t + 24u, b_lo + 384u, b_hi, idesc, 1u);
+          umma_commit(&st_empty[st]);
+        }
+        if (TR) trace[512 + tn * 4 + 2] = clock64();
+        ++tn;
+        first_acc = 1u;
+        st = st_n;
+        ph = ph_n;
+      }
+      if (ok && elect_one()) umma_commit(&acc_full[i & 1]);
+      __syncwarp();
+    }
+    if (!ok) *s_fail = 1;
+    }
+  } else if (warp >= TCT_BWARPS + 6) {
+    // ---------------- B loaders: warp g asks for the slices of the chunks g modulo TCT_GROUPS ----------------
+    // (into ring stages g and g + TCT_GROUPS, as soon as the stage is free: issuing a copy keeps a
+    // warp busy for some hundred cycles, which the builders' chain of a chunk should not carry).
+    // Chunk ids come from global memory, one chunk of the warp ahead of their use.
+    const int g = warp - (TCT_BWARPS + 6);
+    bool ok = true;
+    int sa = g;
+    uint32_t ph = 0;
+    uint32_t cnum0 = 0, mine = (uint32_t)g;
+    int n_nch = 0, n_j0 = 0;
+    auto fetch = [&](int i) {
+      const int b = first + i * stride;
+      n_nch = chunk_cnt[b];
+      n_j0 = chunk_off[b];
+    };
+    if (n_my > 0) fetch(0);
+    int id_next = 0;
+    bool have_next = false;
+    for (int i = 0; i < n_my && ok; ++i) {
+      const int nch = n_nch, j0 = n_j0;
+      if (i + 1 < n_my) fetch(i + 1);
+      for (int j = (int)(mine - cnum0); j < nch; j += TCT_GROUPS, mine += (uint32_t)TCT_GROUPS) {
+        const int id = have_next ? id_next : (int)ldg_here_u32(chunk_list + j0 + j);
+        have_next = false;
+        {
+          const int j2 = j + TCT_GROUPS;
+          if (j2 < nch) {
+            id_next = (int)ldg_here_u32(chunk_list + j0 + j2);
+            have_next = true;
+          } else if (i + 1 < n_my && j2 - nch < n_nch) {
+            id_next = (int)ldg_here_u32(chunk_list + n_j0 + j2 - nch);
+            have_next = true;
+          }
+        }
+        const int brow = id * TC_KC;
+        // (a warp that polls flat out costs shared-memory bandwidth, which is what bounds this kernel)
+        if (!__all_sync(0xffffffffu, (dbg & 32) ? mbar_spin(&st_empty[sa], ph ^ 1u) : mbar_wait_backoff(&st_empty[sa], ph ^ 1u))) {
+          ok = false;
+          break;
+        }
+        if (elect_one()) {
+          if (dbg & 4) {
+            mbar_arrive(&st_full[sa]);
+          } else {
+            mbar_expect_tx(&st_full[sa], (uint32_t)b_stage_bytes);
+            if (one_box) {
+              tma_load_3d(sB + (size_t)sa * b_stage_bytes, &tmB, 0, brow, 0, &st_full[sa]);
+            } else {
+              for (int q = 0; q < nblk; ++q)
+                tma_load_2d(sB + (size_t)sa * b_stage_bytes + q * TC_BBLK, &tmB, q * 64, brow, &st_full[sa]);
+            }
+          }
+        }
+        __syncwarp();
+        sa += TCT_GROUPS;
+        if (sa >= TCT_STAGES) {
+          sa -= TCT_STAGES;
+          ph ^= 1u;
+        }
+      }
+      cnum0 += (uint32_t)nch;
+    }
+    if (!ok) *s_fail = 1;
+  } else if (warp < TCT_BWARPS) {
+    // ---------------- builders ----------------
+    // Group g takes the chunks whose running number (over all row blocks of this CTA) is g modulo
+    // TCT_GROUPS, into ring stages g and g + TCT_GROUPS in turn.  Votes keep a warp's lanes
+    // together (tcgen05.st is a warp-wide instruction); a warp whose wait ran out keeps walking the
+    // loop without waiting or storing.
+    bool ok = true;
+    const int grp = warp >> 2;
+    const int gt = tid - grp * 128;            // row of the block = tensor-memory lane
+    const uint32_t priv = smem_u32(sP + grp * TCT_PRIV + gt * 128);
+    const uint32_t swz = (uint32_t)(gt & 7);   // 16-byte pieces of a line are permuted by the row: lines of
+                                               // eight neighbouring rows read as one conflict-free access
+    const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + a_col0;
+    int sa = grp;
+    uint32_t ph = 0;
+    uint32_t cnum0 = 0;              // running number of the block's first chunk
+    uint32_t mine = (uint32_t)grp;   // running number of the group's next chunk
+    int tn = 0;
+    for (int i = 0; i < n_my; ++i) {
+      const int cs = i % TCT_CSR;
+      ok = __all_sync(0xffffffffu, mbar_wait_backoff(&csr_full[cs], (uint32_t)((i / TCT_CSR) & 1)));
+      if (!ok) break;   // the other roles then run into their own limits
+      const int* hdr = s_hdr + cs * 4;
+      const int e0 = hdr[0], e1 = hdr[1], nch = hdr[2], j0 = hdr[3];
+      const int a0 = e0 & ~15;
+      const bool staged = (e1 - a0) <= TC_CAP;
+      const __nv_bfloat16* __restrict__ pv = staged ? s_val + cs * TCT_CAPB : val + a0;   // by offset in the slice
+      const uint8_t* __restrict__ pk = staged ? s_k + cs * TCT_CAPB : kcol + a0;
+      const uint32_t* prun = s_runs + cs * (TCT_RUNCH * TC_M) + gt;
+      for (int j = (int)(mine - cnum0); j < nch; j += TCT_GROUPS, mine += (uint32_t)TCT_GROUPS) {
+        const uint32_t word = j < TCT_RUNCH ? prun[j * TC_M] : ldg_here_u32(runs + (size_t)(j0 + j) * TC_M + gt);
+        const bool TR = ASP_TCT_TRACE_ON && trace && blockIdx.x == 0 && tid == 0 && tn < 48;
+        if (TR) trace[tn * 8 + 0] = clock64();
+        ok = __all_sync(0xffffffffu, (dbg & 128) ? mbar_wait(&st_empty[sa], ph ^ 1u) : mbar_wait_backoff(&st_empty[sa], ph ^ 1u));
+        if (TR) trace[tn * 8 + 1] = clock64();
+        if (!ok) break;
+        {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (TR) trace[tn * 8 + 6] = clock64();
+          // The first four entries of the run are read side by side (all loads issued before the first
+          // store: a run of a stencil matrix has at most three), longer runs go on in a loop.
+          const int start = (int)(word >> 7), cnt = (dbg & 1) ? 0 : (int)(word & 127u);
+          uint32_t off[4];
+          uint16_t vv[4];
+          uint32_t touched = 0u;   // the 16-byte pieces of the line that hold an entry: only those are read back
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t k = e < cnt ? pk[start + e] : 0u;
+            vv[e] = e < cnt ? __bfloat16_as_ushort(pv[start + e]) : (uint16_t)0;
+            off[e] = priv + (((k >> 3) ^ swz) << 4) + ((k & 7u) << 1);
+            if (e < cnt) touched |= 1u << (k >> 3);
+          }
+          if (TR) trace[tn * 8 + 2] = clock64();
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (e < cnt) sts_b16(off[e], vv[e]);
+          for (int e = 4; e < cnt; ++e) {
+            const uint32_t k = pk[start + e];
+            touched |= 1u << (k >> 3);
+            sts_b16(priv + (((k >> 3) ^ swz) << 4) + ((k & 7u) << 1), __bfloat16_as_ushort(pv[start + e]));
+          }
+          uint32_t a[32];
+#pragma unroll
+          for (int q = 0; q < 32; ++q) a[q] = 0u;
+#pragma unroll
+          for (uint32_t q = 0; q < 8; ++q)
+            lds_v4_if(touched & (1u << q), priv + ((q ^ swz) << 4), a[4 * q], a[4 * q + 1], a[4 * q + 2], a[4 * q + 3]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (e < cnt) sts_b16(off[e], (uint16_t)0);
+          for (int e = 4; e < cnt; ++e) {
+            const uint32_t k = pk[start + e];
+            sts_b16(priv + (((k >> 3) ^ swz) << 4) + ((k & 7u) << 1), (uint16_t)0);
+          }
+          __syncwarp();
+          if (TR) trace[tn * 8 + 3] = clock64() + (a[0] & 0u);
+          if (!(dbg & 2)) {
+          tmem_st32(t_lane + (uint32_t)sa * 32u, a);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          }
+          if (TR) trace[tn * 8 + 4] = clock64();
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&st_full[sa]);
+          if (TR) trace[tn * 8 + 5] = clock64();
+          ++tn;
+        }
+        sa += TCT_GROUPS;
+        if (sa >= TCT_STAGES) {
+          sa -= TCT_STAGES;
+          ph ^= 1u;
+        }
+      }
+      if (!ok) break;
+      cnum0 += (uint32_t)nch;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&csr_empty[cs]);
+    }
+    if (!ok) *s_fail = 1;
+  } else {
+    // ---------------- epilogue: warps 12-15 read tensor-memory lanes 32 * (warp mod 4) .. ----------------
+    bool ok = true;
+    int nch_next = n_my > 0 ? chunk_cnt[first] : 0;
+    for (int i = 0; i < n_my && ok; ++i) {
+      const int acc = i & 1;
+      const int b = first + i * stride;
+      const int64_t r0 = (int64_t)b * TC_M;
+      const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
+      const int nch = nch_next;
+      if (i + 1 < n_my) nch_next = chunk_cnt[first + (i + 1) * stride];
+      const bool TR = ASP_TCT_TRACE_ON && trace && blockIdx.x == 0 && tid == TCT_BWARPS * 32 && i < 8;
+      if (TR) trace[1200 + i * 4 + 0] = clock64();
+      if (!__all_sync(0xffffffffu, mbar_wait_backoff(&acc_full[acc], (uint32_t)((i >> 1) & 1)))) {
+        ok = false;
+        break;
+      }
+      if (TR) trace[1200 + i * 4 + 1] = clock64();
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // tcgen05.ld hands lane l the 32 columns of row l; a per-warp 32 x 36 shared-memory tile turns
+      // that around (16-byte accesses both ways, free of bank conflicts) so that a store instruction
+      // writes four whole 128-byte rows of C.
+      float* tr = s_tr + (warp - TCT_BWARPS) * (TCT_TRBYTES / 4);
+      const int wrow0 = (warp - TCT_BWARPS) * 32;
+      if (c_by_tma) {
+        // beta = 0: the tile goes out by one TMA store per 32 x 32 block of C (128-byte swizzle: lane
+        // l writes the 16-byte piece q of its row at position q ^ (l mod 8), free of bank conflicts;
+        // rows past the matrix are clipped by the copy)
+        const uint32_t trow = smem_u32(tr) + (uint32_t)lane * 128u;
+        for (int cb = 0; cb < n; cb += 32) {
+          uint32_t a[32];
+          if (nch > 0) {
+            tmem_ld32(tmem + ((uint32_t)wrow0 << 16) + (uint32_t)acc * acc_cols + (uint32_t)cb, a);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          } else {
+#pragma unroll
+            for (int q = 0; q < 32; ++q) a[q] = 0u;
+          }
+          // the copy that read the tile last has to be through with it
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __syncwarp();
+#pragma unroll
+          for (uint32_t q = 0; q < 8; ++q)
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(trow + ((q ^ (uint32_t)(lane & 7)) << 4)),
+                         "f"(alpha * __uint_as_float(a[4 * q])), "f"(alpha * __uint_as_float(a[4 * q + 1])),
+                         "f"(alpha * __uint_as_float(a[4 * q + 2])), "f"(alpha * __uint_as_float(a[4 * q + 3]))
+                         : "memory");
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0 && wrow0 < nr && !(dbg & 16)) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&tmC),
+                         "r"(cb), "r"((int)(r0 + wrow0)), "r"(smem_u32(tr))
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (TR) trace[1200 + i * 4 + 2] = clock64();
+        continue;
+      }
+      const int rmax = (dbg & 16) ? 0 : (nr - wrow0 < 32 ? nr - wrow0 : 32);
+      const int rsub = lane >> 3, c4 = (lane & 7) * 4;
+      for (int cb = 0; cb < n; cb += 32) {
+        uint32_t a[32];
+        if (nch > 0) {
+          tmem_ld32(tmem + ((uint32_t)wrow0 << 16) + (uint32_t)acc * acc_cols + (uint32_t)cb, a);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
+#pragma unroll
+          for (int q = 0; q < 32; ++q) a[q] = 0u;
+        }
+        if (TR) trace[1300 + i * 16 + (cb >> 5) * 4 + 0] = clock64() + (a[0] & 0u);
+#pragma unroll
+        for (int q = 0; q < 32; q += 4)
+          *reinterpret_cast<float4*>(tr + lane * TCT_TRLD + q) =
+              make_float4(alpha * __uint_as_float(a[q]), alpha * __uint_as_float(a[q + 1]),
+                          alpha * __uint_as_float(a[q + 2]), alpha * __uint_as_float(a[q + 3]));
+        __syncwarp();
+        if (TR) trace[1300 + i * 16 + (cb >> 5) * 4 + 1] = clock64();
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int rr = it * 4 + rsub;
+          if (rr < rmax) {
+            float4 o = *reinterpret_cast<const float4*>(tr + rr * TCT_TRLD + c4);
+            float4* cp = reinterpret_cast<float4*>(C + (r0 + wrow0 + rr) * ldc + cb + c4);
+            if (beta != 0.f) {
+              const float4 c0 = *cp;
+              o.x = fmaf(beta, c0.x, o.x);
+              o.y = fmaf(beta, c0.y, o.y);
+              o.z = fmaf(beta, c0.z, o.z);
+              o.w = fmaf(beta, c0.w, o.w);
+            }
+            *cp = o;
+          }
+        }
+        __syncwarp();
+        if (TR) trace[1300 + i * 16 + (cb >> 5) * 4 + 2] = clock64();
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (TR) trace[1200 + i * 4 + 2] = clock64();
+    }
+    if (c_by_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (!ok) *s_fail = 1;
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (*s_fail) {
+    if (tid == 0) atomicExch(err, 1);
+    __nanosleep(1000000);  // let copies and MMAs still in flight retire before the memory goes away
+  }
+  if (warp == TCT_BWARPS + 5)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TCT_TMEM_COLS) : "memory");
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1053,6 +1705,38 @@ alphasparseStatus_t build_plan(alphasparseHandle_t h, alphasparseSpMatDescr_t A,
   return status_of(e);
 }
 
+// The per-row run list and the column bytes of the kernel that keeps A in tensor memory.  Left
+// out (runs stays null, the shared-memory kernel runs) when the device memory is not there.
+alphasparseStatus_t build_runs(alphasparseHandle_t h, alphasparseSpMatDescr_t A, TcPlan* tp) {
+  tp->runs_tried = true;
+  if (!tp->usable || !tp->chunk_list || A->nnz == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+  cudaStream_t st = h->stream;
+  const int nb = (int)tp->blocks;
+  int32_t total_padded = 0;
+  cudaError_t e = cudaMemcpyAsync(&total_padded, tp->chunk_off + nb, sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return status_of(e);
+  const size_t words = (size_t)total_padded * TC_M;
+  if (cudaMalloc(&tp->runs, words * sizeof(uint32_t)) != cudaSuccess ||
+      cudaMalloc(&tp->kcol, (size_t)A->nnz + 16) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(tp->runs);
+    cudaFree(tp->kcol);
+    tp->runs = nullptr;
+    tp->kcol = nullptr;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+  }
+  cudaMemsetAsync(tp->runs, 0, words * sizeof(uint32_t), st);
+  tc_runs_kernel<<<(unsigned)nb, 128, 0, st>>>(A->const_row_data, A->const_col_data, A->rows, tp->chunk_off,
+                                               tp->chunk_cnt, tp->chunk_list, tp->runs);
+  int64_t g = (A->nnz + 255) / 256;
+  const int64_t gmax = (int64_t)impl(h)->sm_count * 16;
+  if (g > gmax) g = gmax;
+  tc_kcol_kernel<<<(unsigned)g, 256, 0, st>>>(A->const_col_data, A->nnz, tp->kcol);
+  impl(h)->launches += 2;
+  return status_of(cudaStreamSynchronize(st));
+}
+
 }  // namespace
 
 void free_spmm_tc_plan(void* p) {
@@ -1063,6 +1747,8 @@ void free_spmm_tc_plan(void* p) {
   cudaFree(tp->chunk_list);
   cudaFree(tp->chunk_ent);
   cudaFree(tp->scatter);
+  cudaFree(tp->runs);
+  cudaFree(tp->kcol);
   delete tp;
 }
 
@@ -1096,6 +1782,12 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
   const double t_mma = (double)tp->total_chunks * TC_M * TC_KC * n * 2.0 / impl(h)->bf16_flops;
   const double t_hbm = ((double)A->nnz * 6.0 + (double)A->cols * n * 2.0 + (double)A->rows * n * 4.0) / impl(h)->hbm_bytes;
   if (!tp->usable || t_mma > 3.0 * t_hbm) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  const bool want_tmem = n <= 128 && env_int("ASP_TC_A_TMEM", 1) && env_int("ASP_TC_PERSISTENT", 1) &&
+                         p->max_block_nnz + 16 < (int64_t(1) << 25);
+  if (want_tmem && !tp->runs_tried) {
+    alphasparseStatus_t s = build_runs(h, A, tp);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  }
   if (preprocess_only || A->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
 
   EncodeTiledFn enc = encode_fn();
@@ -1111,6 +1803,64 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
     return ALPHA_SPARSE_STATUS_INVALID_VALUE;
 
   const size_t b_stage = (size_t)(n / 64) * TC_BBLK;
+  if (want_tmem && tp->runs && tp->kcol) {
+    const size_t smem = 1024 + TCT_STAGES * b_stage + TCT_GROUPS * (size_t)TCT_PRIV + TCT_CSR * (size_t)TCT_CAPB * 3 +
+                        TCT_CSR * (size_t)TCT_RUNCH * TC_M * 4 + TCT_CSR * 16 + 4 * TCT_TRBYTES +
+                        (12 + 2 * TCT_STAGES) * 8 + 16;
+    const size_t smem_max = impl(h)->smem_optin ? impl(h)->smem_optin : 232448;
+    if (smem <= smem_max) {
+      static size_t attr_t[64] = {0};
+      size_t& set_t = attr_t[h->device & 63];
+      if (smem > set_t) {
+        ASP_CUDA(cudaFuncSetAttribute(spmm_tc_tmem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        set_t = smem;
+      }
+      int64_t g = impl(h)->sm_count;
+      if (g > tp->blocks) g = tp->blocks;
+      CUtensorMap tm3;
+      const cuuint64_t dims3[3] = {64, (cuuint64_t)B->rows, (cuuint64_t)(n / 64)};
+      const cuuint64_t strides3[2] = {(cuuint64_t)B->ld * 2, 128};
+      const cuuint32_t box3[3] = {64, (cuuint32_t)TC_KC, (cuuint32_t)(n / 64)};
+      const cuuint32_t estr3[3] = {1, 1, 1};
+      const int one_box = n > 64 &&
+                          enc(&tm3, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, B->values, dims3, strides3, box3, estr3,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+      // C leaves by TMA stores of 32 x 32 blocks when it is only written (beta = 0)
+      CUtensorMap tmc = tm;
+      const cuuint64_t dimsc[2] = {(cuuint64_t)n, (cuuint64_t)A->rows};
+      const cuuint64_t stridesc[1] = {(cuuint64_t)C->ld * 4};
+      const cuuint32_t boxc[2] = {32, 32};
+      const int c_by_tma = beta == 0.f && env_int("ASP_TC_C_TMA", 1) &&
+                           enc(&tmc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, C->values, dimsc, stridesc, boxc, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+      static long long* g_trace = nullptr;
+      const char* tpath = getenv("ASP_TCT_TRACE");
+      if (tpath && !g_trace) {
+        cudaMalloc(&g_trace, 2048 * sizeof(long long));
+        cudaMemset(g_trace, 0, 2048 * sizeof(long long));
+      }
+      spmm_tc_tmem_kernel<<<(unsigned)g, TCT_THREADS, smem, h->stream>>>(
+          one_box ? tm3 : tm, tmc, c_by_tma, A->const_row_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
+          reinterpret_cast<float*>(C->values), C->ld, alpha, beta, A->rows, A->nnz, n, (int)tp->blocks,
+          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, tp->runs, tp->kcol, one_box, env_int("ASP_TCT_ISSUERS", 1),
+          env_int("ASP_TCT_DBG", 0), g_trace, p->dev_err);
+      p->last_spmm = "tcgen05";
+      impl(h)->launches++;
+      if (tpath) {
+        static long long host[2048];
+        cudaStreamSynchronize(h->stream);
+        cudaMemcpy(host, g_trace, sizeof host, cudaMemcpyDeviceToHost);
+        FILE* f = fopen(tpath, "w");
+        if (f) {
+          for (int i = 0; i < 2048; ++i) fprintf(f, "%lld\n", host[i]);
+          fclose(f);
+        }
+      }
+      return status_of(cudaGetLastError());
+    }
+  }
   if (env_int("ASP_TC_PERSISTENT", 1) && tp->max_chunks <= TC_MAXCH && tp->scatter &&
       p->max_block_nnz + 8 < (int64_t)(1u << (32 - TC_SRC_SHIFT))) {
     // one CTA per SM; whatever shared memory the fixed parts leave goes to B stages
@@ -1147,7 +1897,9 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
       spmm_tc_persistent_kernel<<<(unsigned)g, TCP_THREADS, smem, h->stream>>>(
           one_box ? tm3 : tm, A->const_row_data, A->const_col_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
           reinterpret_cast<float*>(C->values), C->ld, alpha, beta, A->rows, A->nnz, n, (int)tp->blocks, sb,
-          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, tp->chunk_ent, tp->scatter, one_box, p->dev_err);
+          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, tp->chunk_ent, tp->scatter, one_box,
+          env_int("ASP_TC_ISSUERS", 2), p->dev_err);
+      p->last_spmm = "tcgen05-smem";
       impl(h)->launches++;
       return status_of(cudaGetLastError());
     }
@@ -1163,6 +1915,7 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
       tm, A->const_row_data, A->const_col_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
       reinterpret_cast<float*>(C->values), C->ld, alpha, beta, A->rows, A->nnz, n, tp->chunk_off, tp->chunk_cnt,
       tp->chunk_list, p->dev_err);
+  p->last_spmm = "tcgen05-simple";
   impl(h)->launches++;
   return status_of(cudaGetLastError());
 }

@@ -20,7 +20,26 @@ def bits(t):
     return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
 
 
-def run_tc(handle, A, X, Y0, alpha, beta, ldx=None, ldy=None):
+# The three kernels of the path: A in tensor memory (the default up to N = 128), A tiles in shared
+# memory (N = 256, or on request), one CTA per row block (on request, or for blocks with many chunks).
+KERNELS = {"tcgen05": {}, "tcgen05-smem": {"ASP_TC_A_TMEM": "0"}, "tcgen05-simple": {"ASP_TC_PERSISTENT": "0"}}
+
+
+def run_tc(handle, A, X, Y0, alpha, beta, ldx=None, ldy=None, kernel=None):
+    env = KERNELS.get(kernel, {})
+    old = {k: os.environ.get(k) for k in env}
+    os.environ.update(env)
+    try:
+        return _run_tc(handle, A, X, Y0, alpha, beta, ldx, ldy, kernel)
+    finally:
+        for k, v in old.items():
+            if v is None:
+                del os.environ[k]
+            else:
+                os.environ[k] = v
+
+
+def _run_tc(handle, A, X, Y0, alpha, beta, ldx, ldy, kernel):
     dev = "cuda"
     Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr.to(dev), A.col_idx.to(dev), A.val.to(dev))
     n = X.shape[1]
@@ -41,14 +60,18 @@ def run_tc(handle, A, X, Y0, alpha, beta, ldx=None, ldy=None):
     torch.cuda.synchronize()
     stats, _, _ = Am.plan(handle)
     assert stats["device_error"] == 0
+    if kernel:
+        want_name = "tcgen05-smem" if (kernel == "tcgen05" and n > 128) else kernel
+        assert api.spmm_last_variant(Am) == want_name
     if ldy:
         assert bool((buf2[:, n:] == 3.0).all())
     return Yd.cpu().numpy()
 
 
+@pytest.mark.parametrize("kernel", list(KERNELS))
 @pytest.mark.parametrize("n", [64, 128, 256])
 @pytest.mark.parametrize("grid", [16, 10])
-def test_stencil_bf16(handle, n, grid):
+def test_stencil_bf16(handle, n, grid, kernel):
     A = G.stencil_3d_27pt(grid, seed=4)          # grid 10: 1000 rows, last row block partial
     A.val = A.val.to(torch.bfloat16)
     X = G.uniform((A.cols, n), -1, 1, dtype=torch.bfloat16, seed=70 + n)
@@ -56,12 +79,13 @@ def test_stencil_bf16(handle, n, grid):
     rp, ci = A.row_ptr.numpy(), A.col_idx.numpy()
     for alpha, beta in ((1.0, 0.0), (0.5, -1.5)):
         want = oracle.spmm(rp, ci, bits(A.val), bits(X), alpha, beta, Y0.numpy())
-        got = run_tc(handle, A, X, Y0, alpha, beta)
+        got = run_tc(handle, A, X, Y0, alpha, beta, kernel=kernel)
         err = rel_l2(got, want)
         assert err <= 1e-2 and err <= 1e-5, err
 
 
-def test_dense_blocks_and_empty_rows_bf16(handle):
+@pytest.mark.parametrize("kernel", list(KERNELS))
+def test_dense_blocks_and_empty_rows_bf16(handle, kernel):
     """Block-dense matrix (every touched 64-column chunk well filled) with empty rows and an empty
     row block in the middle."""
     rng = np.random.default_rng(3)
@@ -88,8 +112,34 @@ def test_dense_blocks_and_empty_rows_bf16(handle):
     X = G.uniform((cols, 128), -1, 1, dtype=torch.bfloat16, seed=80)
     Y0 = G.uniform((rows, 128), -1, 1, seed=81)
     want = oracle.spmm(rp, A.col_idx.numpy(), bits(A.val), bits(X), 2.0, 1.0, Y0.numpy())
-    got = run_tc(handle, A, X, Y0, 2.0, 1.0, ldx=136, ldy=132)
+    got = run_tc(handle, A, X, Y0, 2.0, 1.0, ldx=136, ldy=132, kernel=kernel)
     assert rel_l2(got, want) <= 1e-5
+
+
+@pytest.mark.parametrize("half", [12, 20])
+def test_many_row_blocks_per_cta_bf16(handle, half):
+    """More row blocks than SMs (every CTA of the persistent kernels walks several, the staging buffers and
+    both accumulators wrap around) and rows whose run inside a chunk is long (a banded matrix): 25 entries
+    per row are staged in shared memory, 41 per row (5,248 per row block) are read from global memory."""
+    rows = 128 * 700 + 37
+    r = np.arange(rows, dtype=np.int64)
+    lo = np.maximum(r - half, 0)
+    hi = np.minimum(r + half, rows - 1)
+    rp = np.zeros(rows + 1, dtype=np.int32)
+    rp[1:] = np.cumsum(hi - lo + 1)
+    ci = np.concatenate([np.arange(a, b + 1, dtype=np.int32) for a, b in zip(lo[:4096], hi[:4096])]
+                        + [(np.arange(-half, half + 1, dtype=np.int64)[None, :] + r[4096:rows - 4096, None]).reshape(-1).astype(np.int32)]
+                        + [np.arange(a, b + 1, dtype=np.int32) for a, b in zip(lo[rows - 4096:], hi[rows - 4096:])])
+    rng = np.random.default_rng(12)
+    v = torch.from_numpy(rng.standard_normal(len(ci)).astype(np.float32)).to(torch.bfloat16)
+    A = G.Csr(rows, rows, torch.from_numpy(rp), torch.from_numpy(ci), v)
+    n = 128
+    X = G.uniform((rows, n), -1, 1, dtype=torch.bfloat16, seed=85)
+    Y0 = G.uniform((rows, n), -1, 1, seed=86)
+    want = oracle.spmm(rp, ci, bits(A.val), bits(X), 1.0, 0.5, Y0.numpy())
+    for kernel in ("tcgen05", "tcgen05-smem"):
+        got = run_tc(handle, A, X, Y0, 1.0, 0.5, kernel=kernel)
+        assert rel_l2(got, want) <= 1e-5, kernel
 
 
 def test_sparse_random_matrix_is_refused(handle):
