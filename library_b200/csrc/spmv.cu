@@ -440,6 +440,17 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 
 // The same copy with an L2 evict-first policy: A is read once, so its lines should be the first to
 // leave L2 and x, which is gathered over and over, should stay.
+// One lane of the converged warp, chosen by elect.sync: the compiler then knows that a single
+// thread runs the guarded code (the bulk copies take their operands from uniform registers).
+__device__ __forceinline__ bool elect_one_lane() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void bulk_g2s_stream(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   uint64_t pol;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
@@ -500,7 +511,7 @@ spmv_tile_kernel(const OffT* __restrict__ rp, const int* __restrict__ col, const
   const int64_t a0 = nz_s & ~(int64_t)(GA - 1);
   const int lo = (int)(nz_s - a0);
 
-  if (tid == 0) {
+  if (tid < 32 && elect_one_lane()) {
     mbar_init(&s_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     const int64_t nnz4 = nnz & ~(int64_t)(GA - 1);
