@@ -25,7 +25,6 @@
 #include <cub/device/device_reduce.cuh>
 #include <cub/device/device_scan.cuh>
 
-#include <cstdio>
 #include <new>
 
 #include "asp_internal.h"
@@ -612,6 +611,28 @@ __device__ __forceinline__ bool elect_one(uint32_t mask = 0xffffffffu) {
   return pred != 0;
 }
 
+#ifndef ASP_TCT_PARK_NS
+#define ASP_TCT_PARK_NS 2000u
+#endif
+// Bounded wait that leaves the waiting to the hardware: try_wait with a suspend-time hint parks the
+// thread until the phase completes or the time is over, so a long wait costs a few polls instead
+// of one every hundred cycles (every poll is a shared-memory access, and shared-memory bandwidth
+// is what bounds the tensor-memory kernel).
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (TC_MAX_TRIES >> 4); ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ASP_TCT_PARK_NS)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
 // One non-blocking test of a barrier's phase.
 __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
@@ -1013,25 +1034,33 @@ spmm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmB, const int32_t
 // tensor memory as well as from shared memory: lane = row, a 32-bit column = two consecutive bf16
 // of the row.  A builder thread then owns one row of the chunk: it drops the row's few entries
 // into a private 128-byte line of shared memory (no other thread touches it: no barrier, no
-// async-proxy fence, no clear of a 16 KB tile), reads the line back as 32 registers, zeroes what
-// it wrote and hands the registers to tensor memory with one tcgen05.st.  What that frees:
+// async-proxy fence, no clear of a 16 KB tile), reads back the 16-byte pieces it touched, zeroes
+// what it wrote and hands 32 registers to tensor memory with one tcgen05.st.  What that frees:
 //   * the A tiles' shared memory goes to B slices: six ring stages at N = 128 instead of four;
-//   * the MMAs read half as much shared memory (B only);
+//   * the MMAs read half as much shared memory (B only) - the unit that bounds this kernel is the
+//     SM's shared-memory / L1 data pipe, which the B slices alone (written by TMA, read by the
+//     MMAs) keep busy for 256 of a chunk's cycles at N = 128;
 //   * one warp issues (all lanes walk the loop, one elected lane issues: its stream keeps up with
 //     the tensor core), so two accumulators are enough and tensor memory has room for the A stages:
 //     columns [0, 2 acc) accumulators of two row blocks, then 32 columns per ring stage.
 //   warps 0-11  builders : three groups of 128 threads (thread = row = tensor-memory lane) take
 //                          chunks in turn; a group owns ring stages g and g + 3
-//   warps 12-15 epilogue, warp 16 producer (values, column bytes and chunk ids of the next row
-//   block by bulk copies), warp 17 MMA.
-// The plan holds, per chunk and row, where the row's run of entries inside the chunk starts and
-// how long it is (tc_runs_kernel), and per entry its column modulo 64 as a byte.
+//   warps 12-15 epilogue : tcgen05.ld, alpha; with beta = 0 the 32 x 32 blocks of C leave by TMA
+//                          stores from a swizzled tile, else through a transposition tile and
+//                          128-byte row stores
+//   warp 16     producer : values, column bytes, per-row run words and the scalars of the next
+//                          row block by bulk copies (the builders load nothing from global memory)
+//   warp 17     MMA
+//   warps 18-20 B loaders: warp g asks for the B slices of the chunks g modulo 3 as soon as their
+//                          ring stage is free
+// Waits that may be long park in hardware (try_wait with a suspend-time hint): every poll is a
+// shared-memory access.  The plan holds, per chunk and row, where the row's run of entries inside
+// the chunk starts and how long it is (tc_runs_kernel), and per entry its column modulo 64 as a byte.
 // ------------------------------------------------------------------------------------------
 constexpr int TCT_GROUPS = 3;
 constexpr int TCT_BWARPS = TCT_GROUPS * 4;
 constexpr int TCT_STAGES = 2 * TCT_GROUPS;
-constexpr int TCT_THREADS = (TCT_BWARPS + 6 + TCT_GROUPS + 1) * 32;
-constexpr int TCT_MMA2 = TCT_BWARPS + 6 + TCT_GROUPS;   // the second issuing warp
+constexpr int TCT_THREADS = (TCT_BWARPS + 6 + TCT_GROUPS) * 32;
 constexpr int TCT_CSR = 2;
 constexpr int TCT_CAPB = TC_CAP + 16;      // staged entries of a row block (slice widened to multiples of 16)
 constexpr int TCT_RUNCH = 32;              // chunks of a row block whose run words are staged (the rest: global loads)
@@ -1039,12 +1068,6 @@ constexpr int TCT_PRIV = TC_M * 128;       // a group's private lines: 128 rows 
 constexpr uint32_t TCT_TMEM_COLS = 512;
 constexpr int TCT_TRLD = 36;               // floats per row of an epilogue warp's transposition tile
 constexpr int TCT_TRBYTES = 5120;          // an epilogue warp's tile: 32 x TCT_TRLD floats, or 32 x 128 bytes for a TMA store
-#ifndef ASP_TCT_TRACE_ON
-#define ASP_TCT_TRACE_ON 0
-#endif
-#ifndef ASP_TCT_ISSUE_FENCE
-#define ASP_TCT_ISSUE_FENCE 0
-#endif
 static_assert(TC_KC == 64, "a row of a chunk is one 128-byte line / 32 tensor-memory columns");
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -1076,20 +1099,6 @@ __device__ __forceinline__ uint32_t ldg_here_u32(const void* p) {
   asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-// Generic loads (shared or global memory) that stay where they are written.
-__device__ __forceinline__ uint32_t ld_here_u8(const void* p) {
-  uint32_t v;
-  asm volatile("ld.u8 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint32_t ld_here_u16(const void* p) {
-  uint32_t v;
-  asm volatile("ld.u16 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void sts_b32(uint32_t saddr, uint32_t v) {
-  asm volatile("st.shared.b32 [%0], %1;" ::"r"(saddr), "r"(v) : "memory");
-}
 __device__ __forceinline__ void sts_b16(uint32_t saddr, uint16_t v) {
   asm volatile("st.shared.b16 [%0], %1;" ::"r"(saddr), "h"(v) : "memory");
 }
@@ -1111,8 +1120,7 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
                     float beta, int64_t rows, int64_t nnz, int n, int nblocks,
                     const int32_t* __restrict__ chunk_off, const int32_t* __restrict__ chunk_cnt,
                     const int32_t* __restrict__ chunk_list, const uint32_t* __restrict__ runs,
-                    const uint8_t* __restrict__ kcol, int one_box, int issuers_max, int dbg, long long* __restrict__ trace,
-                    int* __restrict__ err) {
+                    const uint8_t* __restrict__ kcol, int one_box, int* __restrict__ err) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int nblk = n / 64;
@@ -1137,11 +1145,6 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
   const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
   const uint32_t acc_cols = n <= 64 ? 64u : 128u;
   const uint32_t a_col0 = 2u * acc_cols;
-  // The tensor core's queue is short: what an issuing warp does between two chunks (the wait for the
-  // next stage, votes, the loop) is time the core idles.  At N = 128 two warps therefore issue, each
-  // the MMAs of one 64-column half of every chunk (same A, its own half of the B slice and of the
-  // accumulator): one warp's bookkeeping runs under the other's MMAs.
-  const int issuers = (n == 128 && issuers_max >= 2) ? 2 : 1;
 
   for (int i = tid; i < TCT_GROUPS * TCT_PRIV / 16; i += TCT_THREADS)
     reinterpret_cast<uint4*>(sP)[i] = make_uint4(0, 0, 0, 0);
@@ -1151,12 +1154,12 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
       mbar_init(&csr_empty[i], TCT_BWARPS);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&acc_full[i], (uint32_t)issuers);
+      mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], 4);
     }
     for (int i = 0; i < TCT_STAGES; ++i) {
       mbar_init(&st_full[i], 4 + 1);   // the group's warps and the thread that announces the B slice's bytes
-      mbar_init(&st_empty[i], (uint32_t)issuers);
+      mbar_init(&st_empty[i], 1);
     }
     *s_fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -1234,18 +1237,15 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
     for (int i = 0; i < n_my && ok; ++i)
       if (i + 1 < n_my) ok = stage_csr(i + 1);
     if (!ok) *s_fail = 1;
-  } else if (warp == TCT_BWARPS + 5 || warp == TCT_MMA2) {
+  } else if (warp == TCT_BWARPS + 5) {
     // ---------------- MMA: the whole warp walks the loop, one elected lane issues ----------------
-    const int half = warp == TCT_MMA2 ? 1 : 0;
-    const int n_mma = n / issuers;   // columns of an MMA
-    if (half < issuers) {
-    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(n_mma >> 3) << 17) |
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(n >> 3) << 17) |
                            ((uint32_t)(TC_M >> 4) << 24);
     bool ok = true, ready = false;
-    int st = 0, tn = 0;
+    int st = 0;
     uint32_t ph = 0;
     const uint64_t bd0 = umma_desc(smem_u32(sB), TC_BBLK, 1024, 2);
-    const uint32_t b_hi = (uint32_t)(bd0 >> 32), b_lo0 = (uint32_t)bd0 + (uint32_t)half * (TC_BBLK >> 4);
+    const uint32_t b_hi = (uint32_t)(bd0 >> 32), b_lo0 = (uint32_t)bd0;
     const uint32_t b_step = (uint32_t)b_stage_bytes >> 4;
     int nch_next = n_my > 0 ? chunk_cnt[first] : 0;
     for (int i = 0; i < n_my && ok; ++i) {
@@ -1256,23 +1256,16 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t d = tmem + (uint32_t)(i & 1) * acc_cols + (uint32_t)(half * n_mma);
+      const uint32_t d = tmem + (uint32_t)(i & 1) * acc_cols;
       uint32_t first_acc = 0u;  // the block's first MMA overwrites the accumulator
       for (int j = 0; j < nch; ++j) {
-        const bool TR = ASP_TCT_TRACE_ON && trace && blockIdx.x == 0 && lane == 0 && tn < 144;
-        if (TR) trace[512 + tn * 4 + 0] = clock64();
-        if (!ready && !__all_sync(0xffffffffu, (dbg & 64) ? mbar_wait(&st_full[st], ph) : mbar_spin(&st_full[st], ph))) {
+        if (!ready && !__all_sync(0xffffffffu, mbar_spin(&st_full[st], ph))) {
           ok = false;
           break;
         }
-        if (TR) trace[512 + tn * 4 + 1] = clock64();
-        // No tcgen05.fence::after_thread_sync here (it changed nothing in the measured time, and the
-        // kernel that reads A from shared memory has none either): the builders' tcgen05.st have
-        // completed (their wait::st) before they arrive on the barrier, and the MMAs are issued
-        // after the wait on it has returned.
-#if ASP_TCT_ISSUE_FENCE
+        // the builders' tcgen05.st have completed (their wait::st, then fence::before_thread_sync)
+        // before they arrive on the barrier; this fence orders the MMAs after the wait on it
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#endif
         const uint32_t a_t = tmem + a_col0 + (uint32_t)st * 32u, b_lo = b_lo0 + (uint32_t)st * b_step;
         // The tensor core takes the next MMA while it works on one, but its queue is short: what the
         // warp does between a chunk's last MMA and the next chunk's first one is time the core
@@ -1281,18 +1274,16 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
         const int st_n = st + 1 == TCT_STAGES ? 0 : st + 1;
         const uint32_t ph_n = st + 1 == TCT_STAGES ? ph ^ 1u : ph;
         const bool early = mbar_test(&st_full[st_n], ph_n);
-        if (elect_one() && !(dbg & 8)) {
+        if (elect_one()) {
           umma_bf16_ts(d, a_t, b_lo, b_hi, idesc, first_acc);
           umma_bf16_ts(d, a_t + 8u, b_lo + 128u, b_hi, idesc, 1u);
           umma_bf16_ts(d, a_t + 16u, b_lo + 256u, b_hi, idesc, 1u);
         }
         ready = __all_sync(0xffffffffu, early);
         if (elect_one()) {
-          if (!(dbg & 8)) umma_bf16_ts(d, a_t + 24u, b_lo + 384u, b_hi, idesc, 1u);
+          umma_bf16_ts(d, a_t + 24u, b_lo + 384u, b_hi, idesc, 1u);
           umma_commit(&st_empty[st]);
         }
-        if (TR) trace[512 + tn * 4 + 2] = clock64();
-        ++tn;
         first_acc = 1u;
         st = st_n;
         ph = ph_n;
@@ -1301,7 +1292,6 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
       __syncwarp();
     }
     if (!ok) *s_fail = 1;
-    }
   } else if (warp >= TCT_BWARPS + 6) {
     // ---------------- B loaders: warp g asks for the slices of the chunks g modulo TCT_GROUPS ----------------
     // (into ring stages g and g + TCT_GROUPS, as soon as the stage is free: issuing a copy keeps a
@@ -1339,21 +1329,17 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
         }
         const int brow = id * TC_KC;
         // (a warp that polls flat out costs shared-memory bandwidth, which is what bounds this kernel)
-        if (!__all_sync(0xffffffffu, (dbg & 32) ? mbar_spin(&st_empty[sa], ph ^ 1u) : mbar_wait_backoff(&st_empty[sa], ph ^ 1u))) {
+        if (!__all_sync(0xffffffffu, mbar_wait_parked(&st_empty[sa], ph ^ 1u))) {
           ok = false;
           break;
         }
         if (elect_one()) {
-          if (dbg & 4) {
-            mbar_arrive(&st_full[sa]);
+          mbar_expect_tx(&st_full[sa], (uint32_t)b_stage_bytes);
+          if (one_box) {
+            tma_load_3d(sB + (size_t)sa * b_stage_bytes, &tmB, 0, brow, 0, &st_full[sa]);
           } else {
-            mbar_expect_tx(&st_full[sa], (uint32_t)b_stage_bytes);
-            if (one_box) {
-              tma_load_3d(sB + (size_t)sa * b_stage_bytes, &tmB, 0, brow, 0, &st_full[sa]);
-            } else {
-              for (int q = 0; q < nblk; ++q)
-                tma_load_2d(sB + (size_t)sa * b_stage_bytes + q * TC_BBLK, &tmB, q * 64, brow, &st_full[sa]);
-            }
+            for (int q = 0; q < nblk; ++q)
+              tma_load_2d(sB + (size_t)sa * b_stage_bytes + q * TC_BBLK, &tmB, q * 64, brow, &st_full[sa]);
           }
         }
         __syncwarp();
@@ -1383,10 +1369,9 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
     uint32_t ph = 0;
     uint32_t cnum0 = 0;              // running number of the block's first chunk
     uint32_t mine = (uint32_t)grp;   // running number of the group's next chunk
-    int tn = 0;
     for (int i = 0; i < n_my; ++i) {
       const int cs = i % TCT_CSR;
-      ok = __all_sync(0xffffffffu, mbar_wait_backoff(&csr_full[cs], (uint32_t)((i / TCT_CSR) & 1)));
+      ok = __all_sync(0xffffffffu, mbar_wait_parked(&csr_full[cs], (uint32_t)((i / TCT_CSR) & 1)));
       if (!ok) break;   // the other roles then run into their own limits
       const int* hdr = s_hdr + cs * 4;
       const int e0 = hdr[0], e1 = hdr[1], nch = hdr[2], j0 = hdr[3];
@@ -1397,17 +1382,13 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
       const uint32_t* prun = s_runs + cs * (TCT_RUNCH * TC_M) + gt;
       for (int j = (int)(mine - cnum0); j < nch; j += TCT_GROUPS, mine += (uint32_t)TCT_GROUPS) {
         const uint32_t word = j < TCT_RUNCH ? prun[j * TC_M] : ldg_here_u32(runs + (size_t)(j0 + j) * TC_M + gt);
-        const bool TR = ASP_TCT_TRACE_ON && trace && blockIdx.x == 0 && tid == 0 && tn < 48;
-        if (TR) trace[tn * 8 + 0] = clock64();
-        ok = __all_sync(0xffffffffu, (dbg & 128) ? mbar_wait(&st_empty[sa], ph ^ 1u) : mbar_wait_backoff(&st_empty[sa], ph ^ 1u));
-        if (TR) trace[tn * 8 + 1] = clock64();
+        ok = __all_sync(0xffffffffu, mbar_wait_parked(&st_empty[sa], ph ^ 1u));
         if (!ok) break;
         {
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          if (TR) trace[tn * 8 + 6] = clock64();
           // The first four entries of the run are read side by side (all loads issued before the first
           // store: a run of a stencil matrix has at most three), longer runs go on in a loop.
-          const int start = (int)(word >> 7), cnt = (dbg & 1) ? 0 : (int)(word & 127u);
+          const int start = (int)(word >> 7), cnt = (int)(word & 127u);
           uint32_t off[4];
           uint16_t vv[4];
           uint32_t touched = 0u;   // the 16-byte pieces of the line that hold an entry: only those are read back
@@ -1418,7 +1399,6 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
             off[e] = priv + (((k >> 3) ^ swz) << 4) + ((k & 7u) << 1);
             if (e < cnt) touched |= 1u << (k >> 3);
           }
-          if (TR) trace[tn * 8 + 2] = clock64();
 #pragma unroll
           for (int e = 0; e < 4; ++e)
             if (e < cnt) sts_b16(off[e], vv[e]);
@@ -1441,18 +1421,12 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
             sts_b16(priv + (((k >> 3) ^ swz) << 4) + ((k & 7u) << 1), (uint16_t)0);
           }
           __syncwarp();
-          if (TR) trace[tn * 8 + 3] = clock64() + (a[0] & 0u);
-          if (!(dbg & 2)) {
           tmem_st32(t_lane + (uint32_t)sa * 32u, a);
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-          }
-          if (TR) trace[tn * 8 + 4] = clock64();
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
           if (lane == 0) mbar_arrive(&st_full[sa]);
-          if (TR) trace[tn * 8 + 5] = clock64();
-          ++tn;
-        }
+          }
         sa += TCT_GROUPS;
         if (sa >= TCT_STAGES) {
           sa -= TCT_STAGES;
@@ -1476,13 +1450,10 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
       const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
       const int nch = nch_next;
       if (i + 1 < n_my) nch_next = chunk_cnt[first + (i + 1) * stride];
-      const bool TR = ASP_TCT_TRACE_ON && trace && blockIdx.x == 0 && tid == TCT_BWARPS * 32 && i < 8;
-      if (TR) trace[1200 + i * 4 + 0] = clock64();
-      if (!__all_sync(0xffffffffu, mbar_wait_backoff(&acc_full[acc], (uint32_t)((i >> 1) & 1)))) {
+      if (!__all_sync(0xffffffffu, mbar_wait_parked(&acc_full[acc], (uint32_t)((i >> 1) & 1)))) {
         ok = false;
         break;
       }
-      if (TR) trace[1200 + i * 4 + 1] = clock64();
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // tcgen05.ld hands lane l the 32 columns of row l; a per-warp 32 x 36 shared-memory tile turns
       // that around (16-byte accesses both ways, free of bank conflicts) so that a store instruction
@@ -1514,7 +1485,7 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
                          : "memory");
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
-          if (lane == 0 && wrow0 < nr && !(dbg & 16)) {
+          if (lane == 0 && wrow0 < nr) {
             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&tmC),
                          "r"(cb), "r"((int)(r0 + wrow0)), "r"(smem_u32(tr))
                          : "memory");
@@ -1524,10 +1495,9 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
-        if (TR) trace[1200 + i * 4 + 2] = clock64();
         continue;
       }
-      const int rmax = (dbg & 16) ? 0 : (nr - wrow0 < 32 ? nr - wrow0 : 32);
+      const int rmax = nr - wrow0 < 32 ? nr - wrow0 : 32;
       const int rsub = lane >> 3, c4 = (lane & 7) * 4;
       for (int cb = 0; cb < n; cb += 32) {
         uint32_t a[32];
@@ -1538,14 +1508,12 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
 #pragma unroll
           for (int q = 0; q < 32; ++q) a[q] = 0u;
         }
-        if (TR) trace[1300 + i * 16 + (cb >> 5) * 4 + 0] = clock64() + (a[0] & 0u);
 #pragma unroll
         for (int q = 0; q < 32; q += 4)
           *reinterpret_cast<float4*>(tr + lane * TCT_TRLD + q) =
               make_float4(alpha * __uint_as_float(a[q]), alpha * __uint_as_float(a[q + 1]),
                           alpha * __uint_as_float(a[q + 2]), alpha * __uint_as_float(a[q + 3]));
         __syncwarp();
-        if (TR) trace[1300 + i * 16 + (cb >> 5) * 4 + 1] = clock64();
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
           const int rr = it * 4 + rsub;
@@ -1563,12 +1531,10 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
           }
         }
         __syncwarp();
-        if (TR) trace[1300 + i * 16 + (cb >> 5) * 4 + 2] = clock64();
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
-      if (TR) trace[1200 + i * 4 + 2] = clock64();
     }
     if (c_by_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     if (!ok) *s_fail = 1;
@@ -1835,29 +1801,12 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
                            enc(&tmc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, C->values, dimsc, stridesc, boxc, estr,
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-      static long long* g_trace = nullptr;
-      const char* tpath = getenv("ASP_TCT_TRACE");
-      if (tpath && !g_trace) {
-        cudaMalloc(&g_trace, 2048 * sizeof(long long));
-        cudaMemset(g_trace, 0, 2048 * sizeof(long long));
-      }
       spmm_tc_tmem_kernel<<<(unsigned)g, TCT_THREADS, smem, h->stream>>>(
           one_box ? tm3 : tm, tmc, c_by_tma, A->const_row_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
           reinterpret_cast<float*>(C->values), C->ld, alpha, beta, A->rows, A->nnz, n, (int)tp->blocks,
-          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, tp->runs, tp->kcol, one_box, env_int("ASP_TCT_ISSUERS", 1),
-          env_int("ASP_TCT_DBG", 0), g_trace, p->dev_err);
+          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, tp->runs, tp->kcol, one_box, p->dev_err);
       p->last_spmm = "tcgen05";
       impl(h)->launches++;
-      if (tpath) {
-        static long long host[2048];
-        cudaStreamSynchronize(h->stream);
-        cudaMemcpy(host, g_trace, sizeof host, cudaMemcpyDeviceToHost);
-        FILE* f = fopen(tpath, "w");
-        if (f) {
-          for (int i = 0; i < 2048; ++i) fprintf(f, "%lld\n", host[i]);
-          fclose(f);
-        }
-      }
       return status_of(cudaGetLastError());
     }
   }
