@@ -564,20 +564,29 @@ constexpr int TCP_GTHREADS = TCP_GWARPS * 32;
 constexpr int TCP_THREADS = (TCP_BWARPS + 7) * 32;    // builders, 4 epilogue warps, producer, 2 MMA warps
 static_assert(TCP_GROUPS * TCP_GWARPS == TCP_BWARPS && TC_M % TCP_GTHREADS == 0, "builder groups");
 constexpr int TCP_CSR = 3;  // row-block CSR buffers: staging block i+1 never waits for the builders of block i-1
-#ifndef ASP_TC_BACKOFF_NS
-#define ASP_TC_BACKOFF_NS 64
+#ifndef ASP_TCT_PARK_NS
+#define ASP_TCT_PARK_NS 2000u
 #endif
-
-// Bounded wait with back-off for the roles whose waits are long (builders at a block boundary,
-// epilogue): a warp that spins flat out takes issue slots from the single-thread producer and
-// MMA roles that share its scheduler.
-__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < TC_MAX_TRIES; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(ASP_TC_BACKOFF_NS);
+// Bounded wait that leaves the waiting to the hardware, for the roles whose waits are long
+// (builders, loaders, epilogue): try_wait with a suspend-time hint parks the thread until the phase
+// completes or the time is over, so a long wait costs a few polls instead of one every hundred
+// cycles.  Every poll is a shared-memory access, and a warp that spins takes issue slots from the
+// roles that share its scheduler.
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (TC_MAX_TRIES >> 4); ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ASP_TCT_PARK_NS)
+        : "memory");
+    if (ok) return true;
   }
   return false;
 }
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity) { return mbar_wait_parked(bar, parity); }
 
 // Bounded spin on the non-blocking test: lowest wake-up latency, for the waits that sit on the
 // per-chunk critical path (try_wait may park the thread for a scheduler time slice).
@@ -609,28 +618,6 @@ __device__ __forceinline__ bool elect_one(uint32_t mask = 0xffffffffu) {
       : "=r"(pred)
       : "r"(mask));
   return pred != 0;
-}
-
-#ifndef ASP_TCT_PARK_NS
-#define ASP_TCT_PARK_NS 2000u
-#endif
-// Bounded wait that leaves the waiting to the hardware: try_wait with a suspend-time hint parks the
-// thread until the phase completes or the time is over, so a long wait costs a few polls instead
-// of one every hundred cycles (every poll is a shared-memory access, and shared-memory bandwidth
-// is what bounds the tensor-memory kernel).
-__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < (TC_MAX_TRIES >> 4); ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(ASP_TCT_PARK_NS)
-        : "memory");
-    if (ok) return true;
-  }
-  return false;
 }
 
 // One non-blocking test of a barrier's phase.
