@@ -68,7 +68,7 @@ TRAFFIC_RATIO = {
     "spmm_s27_128_f32_n8": 580.7e6 / 588.5e6,
     "spmm_s27_128_f32_n32": 969.5e6 / 991.2e6,
     "spmm_s27_128_f32_n128": 2647.0e6 / 2601.8e6,
-    "spmm_s27_128_bf16_n128": 1900.8e6 / 1946.0e6,
+    "spmm_s27_128_bf16_n128": 1895.3e6 / 1953.5e6,
     "spmv_lap3d_f16_i64": 933.6e6 / 937.0e6,
 }
 
