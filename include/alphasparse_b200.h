@@ -17,9 +17,11 @@
  * Supported beyond the plain case: opA = TRANSPOSE for SpMV and SpMM (on a transposed copy the
  * plan builds on the device, A itself untouched), column-major B and C in SpMM (through
  * row-major copies in the caller's buffer), fp16 / bf16 A and x with fp32 arithmetic in SpMV,
- * bf16 A and B with fp32 C in SpMM (the tcgen05 kernel), 32- or 64-bit row offsets.
+ * complex (C_32F, C_64F) and int8 (to int32 or fp32) SpMV, bf16 A and B with fp32 C in SpMM
+ * (the tcgen05 kernels), 32- or 64-bit row offsets.
  * Not supported (ALPHA_SPARSE_STATUS_NOT_SUPPORTED): transposed B, index base one, formats
- * other than CSR, complex and int8 values, device pointer mode.  There is no CPU fallback.
+ * other than CSR, complex and int8 SpMM, half-precision complex, device pointer mode.  There is
+ * no CPU fallback.
  */
 #ifndef ALPHASPARSE_B200_H
 #define ALPHASPARSE_B200_H
@@ -249,7 +251,11 @@ alphasparseStatus_t alphasparseDnMatSetValues(alphasparseDnMatDescr_t descr, voi
  * (A and x / y / computeType, alpha and beta host pointers of the compute type):
  *   R_32F / R_32F / R_32F  (:234)      R_64F / R_64F / R_64F  (:240)
  *   R_16F / R_32F / R_32F  (:288-292)  R_16BF / R_16BF / R_32F (:294-300)
- * with 32- or 64-bit row offsets.  The reference's complex and int8 instances are not provided.
+ *   C_32F / C_32F / C_32F  (:246-253)  C_64F / C_64F / C_64F  (:255-262)
+ *   R_8I  / R_32I / R_32I  (:276-281)  R_8I  / R_32F / R_32F  (:282-287)
+ * with 32- or 64-bit row offsets (complex and int8: opA = NON_TRANSPOSE only, one plain
+ * kernel over the plan's row classes).  The reference's half-precision complex instances are
+ * not provided.
  * opA = TRANSPOSE (or CONJUGATE_TRANSPOSE, the same for real types): x has A's row count, y its
  * column count; the first such call (or alphasparseSpMV_analysis with that opA) builds a
  * transposed copy of A on the device, which allocates and synchronises; A itself is not
