@@ -247,9 +247,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false if the phase did not complete within TC_MAX_TRIES polls.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < TC_MAX_TRIES; ++i)
+// Bounded wait: false if the phase did not complete within `limit` polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = TC_MAX_TRIES) {
+  for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
@@ -572,8 +572,8 @@ constexpr int TCP_CSR = 3;  // row-block CSR buffers: staging block i+1 never wa
 // completes or the time is over, so a long wait costs a few polls instead of one every hundred
 // cycles.  Every poll is a shared-memory access, and a warp that spins takes issue slots from the
 // roles that share its scheduler.
-__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < (TC_MAX_TRIES >> 4); ++i) {
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, uint32_t limit = TC_MAX_TRIES) {
+  for (uint32_t i = 0; i < (limit >> 4) + 1u; ++i) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -590,8 +590,8 @@ __device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity
 
 // Bounded spin on the non-blocking test: lowest wake-up latency, for the waits that sit on the
 // per-chunk critical path (try_wait may park the thread for a scheduler time slice).
-__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < (TC_MAX_TRIES << 4); ++i) {
+__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity, uint32_t limit = TC_MAX_TRIES) {
+  for (uint32_t i = 0; i < (limit << 4); ++i) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -1107,7 +1107,7 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
                     float beta, int64_t rows, int64_t nnz, int n, int nblocks,
                     const int32_t* __restrict__ chunk_off, const int32_t* __restrict__ chunk_cnt,
                     const int32_t* __restrict__ chunk_list, const uint32_t* __restrict__ runs,
-                    const uint8_t* __restrict__ kcol, int one_box, int* __restrict__ err) {
+                    const uint8_t* __restrict__ kcol, int one_box, uint32_t wait_cfg, int* __restrict__ err) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int nblk = n / 64;
@@ -1130,6 +1130,10 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
   volatile int* s_fail = reinterpret_cast<volatile int*>(s_tmem + 1);
 
   const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
+  // the plan's wait settings: how many polls a wait may take, and the test hook that announces the
+  // B slices' bytes to the barriers without asking for the copies (every wait then runs out)
+  const uint32_t lim = wait_cfg & kWaitPollMask;
+  const bool drop_copies = (wait_cfg & kWaitDropCopy) != 0u;
   const uint32_t acc_cols = n <= 64 ? 64u : 128u;
   const uint32_t a_col0 = 2u * acc_cols;
 
@@ -1179,7 +1183,7 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
     };
     auto stage_csr = [&](int i) -> bool {
       const int cs = i % TCT_CSR;
-      if (!__all_sync(0xffffffffu, mbar_wait(&csr_empty[cs], (uint32_t)(((i / TCT_CSR) & 1) ^ 1)))) return false;
+      if (!__all_sync(0xffffffffu, mbar_wait(&csr_empty[cs], (uint32_t)(((i / TCT_CSR) & 1) ^ 1), lim))) return false;
       const int e0 = p_e0, e1 = p_e1, j0 = p_j0, nch = p_nch;
       if (i + 1 < n_my) prefetch(i + 1);
       if (elect_one()) {
@@ -1238,7 +1242,7 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
     for (int i = 0; i < n_my && ok; ++i) {
       const int nch = nch_next;  // fetched one block ahead: no global latency between blocks
       if (i + 1 < n_my) nch_next = chunk_cnt[first + (i + 1) * stride];
-      if (!__all_sync(0xffffffffu, mbar_wait(&acc_empty[i & 1], (uint32_t)(((i >> 1) & 1) ^ 1)))) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&acc_empty[i & 1], (uint32_t)(((i >> 1) & 1) ^ 1), lim))) {
         ok = false;
         break;
       }
@@ -1246,7 +1250,7 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
       const uint32_t d = tmem + (uint32_t)(i & 1) * acc_cols;
       uint32_t first_acc = 0u;  // the block's first MMA overwrites the accumulator
       for (int j = 0; j < nch; ++j) {
-        if (!ready && !__all_sync(0xffffffffu, mbar_spin(&st_full[st], ph))) {
+        if (!ready && !__all_sync(0xffffffffu, mbar_spin(&st_full[st], ph, lim))) {
           ok = false;
           break;
         }
@@ -1316,13 +1320,14 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
         }
         const int brow = id * TC_KC;
         // (a warp that polls flat out costs shared-memory bandwidth, which is what bounds this kernel)
-        if (!__all_sync(0xffffffffu, mbar_wait_parked(&st_empty[sa], ph ^ 1u))) {
+        if (!__all_sync(0xffffffffu, mbar_wait_parked(&st_empty[sa], ph ^ 1u, lim))) {
           ok = false;
           break;
         }
         if (elect_one()) {
           mbar_expect_tx(&st_full[sa], (uint32_t)b_stage_bytes);
-          if (one_box) {
+          if (drop_copies) {
+          } else if (one_box) {
             tma_load_3d(sB + (size_t)sa * b_stage_bytes, &tmB, 0, brow, 0, &st_full[sa]);
           } else {
             for (int q = 0; q < nblk; ++q)
@@ -1358,7 +1363,7 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
     uint32_t mine = (uint32_t)grp;   // running number of the group's next chunk
     for (int i = 0; i < n_my; ++i) {
       const int cs = i % TCT_CSR;
-      ok = __all_sync(0xffffffffu, mbar_wait_parked(&csr_full[cs], (uint32_t)((i / TCT_CSR) & 1)));
+      ok = __all_sync(0xffffffffu, mbar_wait_parked(&csr_full[cs], (uint32_t)((i / TCT_CSR) & 1), lim));
       if (!ok) break;   // the other roles then run into their own limits
       const int* hdr = s_hdr + cs * 4;
       const int e0 = hdr[0], e1 = hdr[1], nch = hdr[2], j0 = hdr[3];
@@ -1369,7 +1374,7 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
       const uint32_t* prun = s_runs + cs * (TCT_RUNCH * TC_M) + gt;
       for (int j = (int)(mine - cnum0); j < nch; j += TCT_GROUPS, mine += (uint32_t)TCT_GROUPS) {
         const uint32_t word = j < TCT_RUNCH ? prun[j * TC_M] : ldg_here_u32(runs + (size_t)(j0 + j) * TC_M + gt);
-        ok = __all_sync(0xffffffffu, mbar_wait_parked(&st_empty[sa], ph ^ 1u));
+        ok = __all_sync(0xffffffffu, mbar_wait_parked(&st_empty[sa], ph ^ 1u, lim));
         if (!ok) break;
         {
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -1437,7 +1442,7 @@ spmm_tc_tmem_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_consta
       const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
       const int nch = nch_next;
       if (i + 1 < n_my) nch_next = chunk_cnt[first + (i + 1) * stride];
-      if (!__all_sync(0xffffffffu, mbar_wait_parked(&acc_full[acc], (uint32_t)((i >> 1) & 1)))) {
+      if (!__all_sync(0xffffffffu, mbar_wait_parked(&acc_full[acc], (uint32_t)((i >> 1) & 1), lim))) {
         ok = false;
         break;
       }
@@ -1791,7 +1796,7 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
       spmm_tc_tmem_kernel<<<(unsigned)g, TCT_THREADS, smem, h->stream>>>(
           one_box ? tm3 : tm, tmc, c_by_tma, A->const_row_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
           reinterpret_cast<float*>(C->values), C->ld, alpha, beta, A->rows, A->nnz, n, (int)tp->blocks,
-          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, tp->runs, tp->kcol, one_box, p->dev_err);
+          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, tp->runs, tp->kcol, one_box, p->wait_cfg, p->dev_err);
       p->last_spmm = "tcgen05";
       impl(h)->launches++;
       return status_of(cudaGetLastError());

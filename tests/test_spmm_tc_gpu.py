@@ -228,3 +228,31 @@ def test_repeated_and_unsorted_columns(handle):
     with pytest.raises(api.AlphaSparseError) as e:
         api.spmm(handle, Ab2, api.DnMat(torch.from_numpy(X).cuda().to(torch.bfloat16)), api.DnMat(Y), 1.0, 0.0)
     assert e.value.status == 6
+
+
+def test_waits_that_run_out_are_reported_bf16(handle, monkeypatch):
+    """Failure detection without a fault, on the tensor-memory kernel: with ASP_TEST_DROP_COPY the loader warps
+    announce the B slices' bytes to the stage barriers but never ask for the copies, so no stage ever fills.
+    Every role's bounded wait runs out (ASP_WAIT_POLLS polls), the CTA raises the plan's flag, frees its tensor
+    memory and leaves: nothing faults, the context stays usable, the flag shows in the plan statistics, and a
+    fresh plan computes the right product."""
+    A = G.stencil_3d_27pt(16, seed=4)
+    A.val = A.val.to(torch.bfloat16)
+    n = 128
+    X = G.uniform((A.cols, n), -1, 1, dtype=torch.bfloat16, seed=95)
+    Y0 = G.uniform((A.rows, n), -1, 1, seed=96)
+    handle.use_torch_stream()
+    Am = api.CsrMatrix(A.rows, A.cols, A.row_ptr.cuda(), A.col_idx.cuda(), A.val.cuda())
+    B, C = api.DnMat(X.cuda()), api.DnMat(Y0.clone().cuda())
+    monkeypatch.setenv("ASP_TEST_DROP_COPY", "1")
+    monkeypatch.setenv("ASP_WAIT_POLLS", "64")
+    api.spmm_preprocess(handle, Am, B, C)             # the plan takes the wait settings from the environment
+    monkeypatch.delenv("ASP_TEST_DROP_COPY")
+    monkeypatch.delenv("ASP_WAIT_POLLS")
+    api.spmm(handle, Am, B, C, 1.0, 0.0)              # launches; every role gives up and the CTAs leave
+    torch.cuda.synchronize()                          # no error from the runtime: nothing faulted
+    assert api.spmm_last_variant(Am) == "tcgen05"
+    assert Am.plan(handle)[0]["device_error"] == 1
+    want = oracle.spmm(A.row_ptr.numpy(), A.col_idx.numpy(), bits(A.val), bits(X), 1.0, 0.0, Y0.numpy())
+    got = run_tc(handle, A, X, Y0, 1.0, 0.0, kernel="tcgen05")     # a new descriptor: new plan, normal waits
+    assert rel_l2(got, want) <= 1e-5
