@@ -1740,7 +1740,9 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
   const double t_mma = (double)tp->total_chunks * TC_M * TC_KC * n * 2.0 / impl(h)->bf16_flops;
   const double t_hbm = ((double)A->nnz * 6.0 + (double)A->cols * n * 2.0 + (double)A->rows * n * 4.0) / impl(h)->hbm_bytes;
   if (!tp->usable || t_mma > 3.0 * t_hbm) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
-  const bool want_tmem = n <= 128 && env_int("ASP_TC_A_TMEM", 1) && env_int("ASP_TC_PERSISTENT", 1) &&
+  // N = 256 runs the tensor-memory kernel as two passes over the matrix, 128 columns of B and C each
+  // (A's lists are read twice, B and C once: measured faster than one pass with A in shared memory).
+  const bool want_tmem = env_int("ASP_TC_A_TMEM", 1) && env_int("ASP_TC_PERSISTENT", 1) &&
                          p->max_block_nnz + 16 < (int64_t(1) << 25);
   if (want_tmem && !tp->runs_tried) {
     alphasparseStatus_t s = build_runs(h, A, tp);
@@ -1762,7 +1764,9 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
 
   const size_t b_stage = (size_t)(n / 64) * TC_BBLK;
   if (want_tmem && tp->runs && tp->kcol) {
-    const size_t smem = 1024 + TCT_STAGES * b_stage + TCT_GROUPS * (size_t)TCT_PRIV + TCT_CSR * (size_t)TCT_CAPB * 3 +
+    const int np = n > 128 ? 128 : n;   // columns of a pass
+    const size_t b_stage_p = (size_t)(np / 64) * TC_BBLK;
+    const size_t smem = 1024 + TCT_STAGES * b_stage_p + TCT_GROUPS * (size_t)TCT_PRIV + TCT_CSR * (size_t)TCT_CAPB * 3 +
                         TCT_CSR * (size_t)TCT_RUNCH * TC_M * 4 + TCT_CSR * 16 + 4 * TCT_TRBYTES +
                         (12 + 2 * TCT_STAGES) * 8 + 16;
     const size_t smem_max = impl(h)->smem_optin ? impl(h)->smem_optin : 232448;
@@ -1775,30 +1779,35 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
       }
       int64_t g = impl(h)->sm_count;
       if (g > tp->blocks) g = tp->blocks;
-      CUtensorMap tm3;
-      const cuuint64_t dims3[3] = {64, (cuuint64_t)B->rows, (cuuint64_t)(n / 64)};
-      const cuuint64_t strides3[2] = {(cuuint64_t)B->ld * 2, 128};
-      const cuuint32_t box3[3] = {64, (cuuint32_t)TC_KC, (cuuint32_t)(n / 64)};
-      const cuuint32_t estr3[3] = {1, 1, 1};
-      const int one_box = n > 64 &&
-                          enc(&tm3, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, B->values, dims3, strides3, box3, estr3,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-      // C leaves by TMA stores of 32 x 32 blocks when it is only written (beta = 0)
-      CUtensorMap tmc = tm;
-      const cuuint64_t dimsc[2] = {(cuuint64_t)n, (cuuint64_t)A->rows};
-      const cuuint64_t stridesc[1] = {(cuuint64_t)C->ld * 4};
-      const cuuint32_t boxc[2] = {32, 32};
-      const int c_by_tma = beta == 0.f && env_int("ASP_TC_C_TMA", 1) &&
-                           enc(&tmc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, C->values, dimsc, stridesc, boxc, estr,
-                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-      spmm_tc_tmem_kernel<<<(unsigned)g, TCT_THREADS, smem, h->stream>>>(
-          one_box ? tm3 : tm, tmc, c_by_tma, A->const_row_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
-          reinterpret_cast<float*>(C->values), C->ld, alpha, beta, A->rows, A->nnz, n, (int)tp->blocks,
-          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, tp->runs, tp->kcol, one_box, p->wait_cfg, p->dev_err);
+      for (int c0 = 0; c0 < n; c0 += np) {
+        void* bp = reinterpret_cast<__nv_bfloat16*>(B->values) + c0;
+        float* cp = reinterpret_cast<float*>(C->values) + c0;
+        CUtensorMap tm3;
+        const cuuint64_t dims3[3] = {64, (cuuint64_t)B->rows, (cuuint64_t)(np / 64)};
+        const cuuint64_t strides3[2] = {(cuuint64_t)B->ld * 2, 128};
+        const cuuint32_t box3[3] = {64, (cuuint32_t)TC_KC, (cuuint32_t)(np / 64)};
+        const cuuint32_t estr3[3] = {1, 1, 1};
+        const int one_box = np > 64 &&
+                            enc(&tm3, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, bp, dims3, strides3, box3, estr3,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+        if (!one_box && np > 64) return ALPHA_SPARSE_STATUS_INVALID_VALUE;   // the 2-D map covers a single pass only
+        // C leaves by TMA stores of 32 x 32 blocks when it is only written (beta = 0)
+        CUtensorMap tmc = tm;
+        const cuuint64_t dimsc[2] = {(cuuint64_t)np, (cuuint64_t)A->rows};
+        const cuuint64_t stridesc[1] = {(cuuint64_t)C->ld * 4};
+        const cuuint32_t boxc[2] = {32, 32};
+        const int c_by_tma = beta == 0.f && env_int("ASP_TC_C_TMA", 1) &&
+                             enc(&tmc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, cp, dimsc, stridesc, boxc, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+        spmm_tc_tmem_kernel<<<(unsigned)g, TCT_THREADS, smem, h->stream>>>(
+            one_box ? tm3 : tm, tmc, c_by_tma, A->const_row_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
+            cp, C->ld, alpha, beta, A->rows, A->nnz, np, (int)tp->blocks, tp->chunk_off, tp->chunk_cnt, tp->chunk_list,
+            tp->runs, tp->kcol, one_box, p->wait_cfg, p->dev_err);
+        impl(h)->launches++;
+      }
       p->last_spmm = "tcgen05";
-      impl(h)->launches++;
       return status_of(cudaGetLastError());
     }
   }
