@@ -17,11 +17,11 @@
  * Supported beyond the plain case: opA = TRANSPOSE for SpMV and SpMM (on a transposed copy the
  * plan builds on the device, A itself untouched), column-major B and C in SpMM (through
  * row-major copies in the caller's buffer), fp16 / bf16 A and x with fp32 arithmetic in SpMV,
- * complex (C_32F, C_64F) and int8 (to int32 or fp32) SpMV, bf16 A and B with fp32 C in SpMM
- * (the tcgen05 kernels), 32- or 64-bit row offsets.
+ * complex (C_32F, C_64F) and int8 (to int32 or fp32) SpMV and SpMM, fp16 A and B with fp32 or
+ * fp16 C in SpMM, bf16 A and B with fp32 C in SpMM (the tcgen05 kernels), 32- or 64-bit row
+ * offsets.
  * Not supported (ALPHA_SPARSE_STATUS_NOT_SUPPORTED): transposed B, index base one, formats
- * other than CSR, complex and int8 SpMM, half-precision complex, device pointer mode.  There is
- * no CPU fallback.
+ * other than CSR, half-precision complex, device pointer mode.  There is no CPU fallback.
  */
 #ifndef ALPHASPARSE_B200_H
 #define ALPHASPARSE_B200_H
@@ -325,7 +325,14 @@ alphasparseStatus_t alphasparseSpMVCsrNoAlloc(cudaStream_t stream, int64_t rows,
  * (no external buffer needed) or both column-major: then externalBuffer must hold
  * alphasparseSpMM_bufferSize bytes, into which row-major copies of B and C are made (the
  * reference transposes B and C in place with buffers it allocates per call, :131-285); B is
- * left untouched and C keeps its layout. */
+ * left untouched and C keeps its layout.  Type combinations (A and B / C / computeType, alpha and
+ * beta host pointers of the compute type), the reference's table at :546-596:
+ *   R_32F / R_32F / R_32F      R_64F / R_64F / R_64F      R_16BF / R_32F / R_32F (tcgen05)
+ *   C_32F / C_32F / C_32F      C_64F / C_64F / C_64F
+ *   R_8I  / R_32I / R_32I      R_8I  / R_32F / R_32F
+ *   R_16F / R_32F / R_32F      R_16F / R_16F / R_32F
+ * with 32- or 64-bit row offsets; the complex, int8 and fp16 rows run one plain kernel
+ * (opA = NON_TRANSPOSE only). */
 alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t handle, alphasparseOperation_t opA,
                                     alphasparseOperation_t opB, const void* alpha,
                                     alphasparseSpMatDescr_t matA, alphasparseDnMatDescr_t matB,

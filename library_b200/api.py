@@ -265,8 +265,13 @@ def spmv(handle: Handle, A: CsrMatrix, x: DnVec, y: DnVec, alpha=1.0, beta=0.0,
            "alphasparseSpMV")
 
 
+def _spmm_compute_code(dt: torch.dtype) -> int:
+    """The compute type of an SpMM is C's type; a 16-bit C is computed in fp32."""
+    return R_32F if dt in (torch.float16, torch.bfloat16) else _dtype_code(dt)
+
+
 def spmm_buffer_size(handle: Handle, A: CsrMatrix, B: DnMat, Cm: DnMat, alg=SPMM_ALG_DEFAULT) -> int:
-    code = _dtype_code(Cm.t.dtype)
+    code = _spmm_compute_code(Cm.t.dtype)
     a, b = _scalar(1.0, code), _scalar(0.0, code)
     size = C.c_size_t(0)
     _check(load().alphasparseSpMM_bufferSize(handle.h, OP_N, OP_N, C.byref(a), A.d, B.d, C.byref(b), Cm.d,
@@ -278,7 +283,7 @@ def spmm(handle: Handle, A: CsrMatrix, B: DnMat, Cm: DnMat, alpha=1.0, beta=0.0,
          alg=SPMM_ALG_DEFAULT, compute=None, buffer: torch.Tensor | None = None):
     """C = alpha*A*B + beta*C on handle's stream (asynchronous).  B and C both row-major, or both
     column-major with a ``buffer`` of spmm_buffer_size bytes."""
-    code = _dtype_code(Cm.t.dtype) if compute is None else compute
+    code = _spmm_compute_code(Cm.t.dtype) if compute is None else compute
     a, b = _scalar(alpha, code), _scalar(beta, code)
     buf = C.c_void_p(buffer.data_ptr()) if buffer is not None else C.c_void_p()
     _check(load().alphasparseSpMM(handle.h, OP_N, OP_N, C.byref(a), A.d, B.d, C.byref(b), Cm.d, code,
@@ -290,7 +295,7 @@ def spmm_last_variant(A: CsrMatrix) -> str:
 
 
 def spmm_preprocess(handle: Handle, A: CsrMatrix, B: DnMat, Cm: DnMat, alg=SPMM_ALG_DEFAULT):
-    code = _dtype_code(Cm.t.dtype)
+    code = _spmm_compute_code(Cm.t.dtype)
     a, b = _scalar(1.0, code), _scalar(0.0, code)
     size = C.c_size_t(0)
     _check(load().alphasparseSpMM_preprocess(handle.h, OP_N, OP_N, C.byref(a), A.d, B.d, C.byref(b),

@@ -11,7 +11,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libalphasparse_b200.so")
-SOURCES = ["handle.cu", "analysis.cu", "spmv.cu", "spmv_lowp.cu", "spmv_types.cu", "spmm.cu", "spmm_balanced.cu", "spmm_stage.cu", "spmm_tc.cu", "io.cu", "mg.cu"]
+SOURCES = ["handle.cu", "analysis.cu", "spmv.cu", "spmv_lowp.cu", "spmv_types.cu", "spmm.cu", "spmm_balanced.cu", "spmm_stage.cu", "spmm_types.cu", "spmm_tc.cu", "io.cu", "mg.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"),

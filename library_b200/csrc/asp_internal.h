@@ -155,6 +155,11 @@ alphasparseStatus_t spmv_lowp_run(alphasparseHandle_t h, alphasparseSpMatDescr_t
 
 
 // spmv_types.cu: complex and int8 instances of the reference's SpMV type table
+// spmm_types.cu: complex, int8 and fp16 SpMM instances
+bool spmm_other_types(alphasparseDataType a, alphasparseDataType b, alphasparseDataType c, alphasparseDataType compute);
+bool spmm_other_reads_c(alphasparseDataType compute, const void* beta);
+alphasparseStatus_t spmm_other_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A, alphasparseDnMatDescr_t B,
+                                   alphasparseDnMatDescr_t C, const void* alpha, const void* beta);
 bool spmv_other_types(alphasparseDataType a, alphasparseDataType x, alphasparseDataType y, alphasparseDataType compute);
 alphasparseStatus_t spmv_other_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A, const Plan* p, const void* x,
                                    void* y, alphasparseDataType y_type, const void* alpha, const void* beta);

@@ -349,7 +349,7 @@ alphasparseStatus_t launch_tile(alphasparseHandle_t h, alphasparseSpMatDescr_t A
 // Bytes of the balanced kernel's carry array for this matrix and N.
 inline size_t balanced_carry_bytes(alphasparseSpMatDescr_t A, int64_t n) {
   const size_t es = elem_size(A->data_type);
-  if (es < 4) return 0;
+  if (A->data_type != ALPHA_R_32F && A->data_type != ALPHA_R_64F) return 0;  // only the fp32 / fp64 kernels carry
   const int64_t tiles = (A->rows + A->nnz + kMergeItems - 1) / kMergeItems;
   return round256((size_t)(tiles > 0 ? tiles : 1) * (size_t)spmm_balanced_carry_ld(n, es) * es);
 }
@@ -477,6 +477,10 @@ alphasparseStatus_t transpose_any(alphasparseHandle_t h, const void* src, int64_
     transpose_kernel<uint16_t><<<grid, 256, 0, h->stream>>>((const uint16_t*)src, ld_src, r_n, c_n, (uint16_t*)dst, ld_dst);
   else if (elem == 4)
     transpose_kernel<uint32_t><<<grid, 256, 0, h->stream>>>((const uint32_t*)src, ld_src, r_n, c_n, (uint32_t*)dst, ld_dst);
+  else if (elem == 1)
+    transpose_kernel<uint8_t><<<grid, 256, 0, h->stream>>>((const uint8_t*)src, ld_src, r_n, c_n, (uint8_t*)dst, ld_dst);
+  else if (elem == 16)
+    transpose_kernel<uint4><<<grid, 256, 0, h->stream>>>((const uint4*)src, ld_src, r_n, c_n, (uint4*)dst, ld_dst);
   else
     transpose_kernel<uint64_t><<<grid, 256, 0, h->stream>>>((const uint64_t*)src, ld_src, r_n, c_n, (uint64_t*)dst, ld_dst);
   impl(h)->launches++;
@@ -508,7 +512,9 @@ alphasparseStatus_t check_spmm_args(alphasparseHandle_t h, alphasparseOperation_
                      computeType == A->data_type;
   const bool mixed = A->data_type == ALPHA_R_16BF && B->data_type == ALPHA_R_16BF &&
                      C->data_type == ALPHA_R_32F && computeType == ALPHA_R_32F;
-  if (!plain && !mixed) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+  // complex, int8 and fp16 instances: one plain kernel, opA = N only (no transposed copy is built for them)
+  const bool other = !tr && spmm_other_types(A->data_type, B->data_type, C->data_type, computeType);
+  if (!plain && !mixed && !other) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
   return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
@@ -552,7 +558,9 @@ alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t h, alphasparseOperation_
     Ct.values = reinterpret_cast<unsigned char*>(externalBuffer) + round256((size_t)B->rows * n * eb);
     void* rest = reinterpret_cast<unsigned char*>(Ct.values) + round256((size_t)C->rows * n * ec);  // the carry array's place
     s = transpose_any(h, B->values, B->ld, n, B->rows, Bt.values, n, eb);
-    const bool reads_c = computeType == ALPHA_R_64F ? *(const double*)beta != 0.0 : *(const float*)beta != 0.f;
+    const bool reads_c = spmm_other_types(A->data_type, B->data_type, C->data_type, computeType)
+                             ? spmm_other_reads_c(computeType, beta)
+                             : (computeType == ALPHA_R_64F ? *(const double*)beta != 0.0 : *(const float*)beta != 0.f);
     if (s == ALPHA_SPARSE_STATUS_SUCCESS && reads_c) s = transpose_any(h, C->values, C->ld, n, C->rows, Ct.values, n, ec);
     if (s == ALPHA_SPARSE_STATUS_SUCCESS)
       s = alphasparseSpMM(h, opA, opB, alpha, A, &Bt, beta, &Ct, computeType, alg, rest);
@@ -560,6 +568,10 @@ alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t h, alphasparseOperation_
     return s;
   }
   const int64_t n = C->cols;
+  if (spmm_other_types(A->data_type, B->data_type, C->data_type, computeType)) {
+    plan_of(A)->last_spmm = "types";
+    return spmm_other_run(h, A, B, C, alpha, beta);
+  }
   if (A->data_type == ALPHA_R_16BF) {
     // bf16 operands exist only for the tensor-core variant.
     if (!spmm_tc_applicable(A, B, C)) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
@@ -594,7 +606,7 @@ alphasparseStatus_t alphasparseSpMM_bufferSize(alphasparseHandle_t h, alphaspars
   if (opA != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) {  // the product runs on the transposed matrix: cols + nnz items
     const size_t es = elem_size(A->data_type);
     const int64_t tiles = (A->cols + A->nnz + kMergeItems - 1) / kMergeItems;
-    if (es >= 4) carry = round256((size_t)(tiles > 0 ? tiles : 1) * (size_t)spmm_balanced_carry_ld(C->cols, es) * es);
+    if (A->data_type == ALPHA_R_32F || A->data_type == ALPHA_R_64F) carry = round256((size_t)(tiles > 0 ? tiles : 1) * (size_t)spmm_balanced_carry_ld(C->cols, es) * es);
   }
   *bufferSize = carry > 256 ? carry : 256;
   if (B->order == ALPHASPARSE_ORDER_COL)
@@ -629,6 +641,7 @@ alphasparseStatus_t alphasparseSpMM_preprocess(alphasparseHandle_t h, alphaspars
     s = analyse(h, A);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   }
+  if (spmm_other_types(A->data_type, B->data_type, C->data_type, computeType)) return ALPHA_SPARSE_STATUS_SUCCESS;
   if (A->data_type == ALPHA_R_16BF) {
     _alphasparse_dnmat_descr Bt = *B, Ct = *C;
     if (B->order == ALPHASPARSE_ORDER_COL) {  // the kernel will see the row-major copies (aligned, ld = N)

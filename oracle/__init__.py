@@ -153,6 +153,47 @@ def spmm(row_ptr, col_idx, val, X, alpha, beta, Y0=None):
     return Y
 
 
+def spmm_complex(row_ptr, col_idx, val, X, alpha, beta, Y0=None):
+    """Complex row-major Y = alpha*A*X + beta*Y0 (numpy complex64 / complex128, Python complex scalars)."""
+    rows = row_ptr.shape[0] - 1
+    row_ptr = np.ascontiguousarray(row_ptr)
+    col_idx = np.ascontiguousarray(col_idx, dtype=np.int32)
+    val = np.ascontiguousarray(val)
+    X = np.ascontiguousarray(X, dtype=val.dtype)
+    n = X.shape[1]
+    Y = np.zeros((rows, n), val.dtype) if Y0 is None else np.array(Y0, dtype=val.dtype, copy=True)
+    tn, rt = {np.dtype(np.complex64): ("c32", np.float32), np.dtype(np.complex128): ("c64", np.float64)}[val.dtype]
+    a = np.array([complex(alpha).real, complex(alpha).imag], dtype=rt)
+    b = np.array([complex(beta).real, complex(beta).imag], dtype=rt)
+    fn = getattr(lib(), f"oracle_spmm_{tn}_" + _off_suffix(row_ptr))
+    fn.restype = None
+    fn(C.c_int64(rows), _p(row_ptr), _p(col_idx), _p(val), _p(X), C.c_int64(n), C.c_int64(n), _p(a), _p(b), _p(Y),
+       C.c_int64(n))
+    return Y
+
+
+def spmm_wide(row_ptr, col_idx, val, X, alpha, beta, Y0):
+    """int8 or fp16 A and X with a wider (or, for fp16, equal) Y: (int8, int32), (int8, float32), (float16, float32),
+    (float16, float16).  Y0's dtype selects the instance; float16 arrays travel as their bit patterns."""
+    rows = row_ptr.shape[0] - 1
+    row_ptr = np.ascontiguousarray(row_ptr)
+    col_idx = np.ascontiguousarray(col_idx, dtype=np.int32)
+    val = np.ascontiguousarray(val)
+    X = np.ascontiguousarray(X, dtype=val.dtype)
+    n = X.shape[1]
+    Y = np.array(Y0, copy=True, order="C")
+    key = (val.dtype, Y.dtype)
+    name, ct = {(np.dtype(np.int8), np.dtype(np.int32)): ("i8_i32", C.c_int32),
+                (np.dtype(np.int8), np.dtype(np.float32)): ("i8_f32", C.c_float),
+                (np.dtype(np.float16), np.dtype(np.float32)): ("f16_f32", C.c_float),
+                (np.dtype(np.float16), np.dtype(np.float16)): ("f16_f16", C.c_float)}[key]
+    fn = getattr(lib(), f"oracle_spmm_{name}_" + _off_suffix(row_ptr))
+    fn.restype = None
+    fn(C.c_int64(rows), _p(row_ptr), _p(col_idx), _p(val), _p(X), C.c_int64(n), C.c_int64(n), ct(alpha), ct(beta),
+       _p(Y), C.c_int64(n))
+    return Y
+
+
 def partition_rows_by_nnz(row_ptr, parts: int) -> np.ndarray:
     row_ptr = np.ascontiguousarray(row_ptr)
     rows = row_ptr.shape[0] - 1
@@ -243,3 +284,23 @@ def ref_spmm(row_ptr, col_idx, val, X, alpha, beta, Y0=None, repeats=1):
     if st != 0:
         raise RuntimeError(f"reference mm returned status {st}")
     return Y, times
+
+
+def ref_spmm_complex(row_ptr, col_idx, val, X, alpha, beta, Y0=None):
+    """The reference's alphasparse_{c,z}_mm, row-major."""
+    rows = row_ptr.shape[0] - 1
+    row_ptr = np.ascontiguousarray(row_ptr, dtype=np.int32)
+    col_idx = np.ascontiguousarray(col_idx, dtype=np.int32)
+    val = np.ascontiguousarray(val)
+    X = np.ascontiguousarray(X, dtype=val.dtype)
+    cols, n = X.shape
+    Y = np.zeros((rows, n), val.dtype) if Y0 is None else np.array(Y0, dtype=val.dtype, copy=True)
+    fn, rt = (ref_lib().ref_c_mm, np.float32) if val.dtype == np.complex64 else (ref_lib().ref_z_mm, np.float64)
+    a = np.array([complex(alpha).real, complex(alpha).imag], dtype=rt)
+    b = np.array([complex(beta).real, complex(beta).imag], dtype=rt)
+    fn.restype = C.c_int
+    st = fn(C.c_int(rows), C.c_int(cols), _p(row_ptr), _p(col_idx), _p(val), _p(X), C.c_int(n), C.c_int(n), _p(a),
+            _p(b), _p(Y), C.c_int(n))
+    if st != 0:
+        raise RuntimeError(f"reference complex mm returned status {st}")
+    return Y

@@ -176,6 +176,110 @@ void oracle_spmm_bf16_i32(int64_t rows, const int32_t* row_ptr, const int32_t* c
   }
 }
 
+/* Complex SpMM (interleaved re, im), the generic row kernel of the reference's CPU backend
+ * (hygon/kernel/level3/mm/gemm/gemm_csr_row.hpp:76-122 with J = complex): Y[r,:] = Y[r,:]*beta,
+ * then for each entry of row r in storage order t = alpha*a and Y[r,c] = X[col,c]*t + Y[r,c].
+ * Checked against the compiled reference within rounding (the compiler is free to contract its
+ * complex products), not bit for bit. */
+#define DEF_SPMM_CPLX(NAME, T, OFF_T, FMA)                                                 \
+  void NAME(int64_t rows, const OFF_T* row_ptr, const int32_t* col, const T* val,          \
+            const T* X, int64_t n, int64_t ldx, const T* alpha, const T* beta, T* Y,       \
+            int64_t ldy) {                                                                 \
+    _Pragma("omp parallel for schedule(static)")                                           \
+    for (int64_t i = 0; i < rows; ++i) {                                                   \
+      T* yr = Y + 2 * i * ldy;                                                             \
+      for (int64_t c = 0; c < n; ++c) {                                                    \
+        const T a = yr[2 * c], b = yr[2 * c + 1];                                          \
+        yr[2 * c] = FMA(-b, beta[1], a * beta[0]);                                         \
+        yr[2 * c + 1] = FMA(b, beta[0], a * beta[1]);                                      \
+      }                                                                                    \
+      for (int64_t k = (int64_t)row_ptr[i]; k < (int64_t)row_ptr[i + 1]; ++k) {            \
+        const T ar = val[2 * k], ai = val[2 * k + 1];                                      \
+        const T tr = FMA(-alpha[1], ai, alpha[0] * ar), ti = FMA(alpha[1], ar, alpha[0] * ai); \
+        const T* xr = X + 2 * (int64_t)col[k] * ldx;                                       \
+        for (int64_t c = 0; c < n; ++c) {                                                  \
+          const T xa = xr[2 * c], xb = xr[2 * c + 1];                                      \
+          yr[2 * c] = FMA(-xb, ti, FMA(xa, tr, yr[2 * c]));                                \
+          yr[2 * c + 1] = FMA(xb, tr, FMA(xa, ti, yr[2 * c + 1]));                         \
+        }                                                                                  \
+      }                                                                                    \
+    }                                                                                      \
+  }
+DEF_SPMM_CPLX(oracle_spmm_c32_i32, float, int32_t, fmaf)
+DEF_SPMM_CPLX(oracle_spmm_c32_i64, float, int64_t, fmaf)
+DEF_SPMM_CPLX(oracle_spmm_c64_i32, double, int32_t, fma)
+DEF_SPMM_CPLX(oracle_spmm_c64_i64, double, int64_t, fma)
+
+/* int8 and fp16 SpMM.  The reference has no CPU path for these instances, so nothing pins them
+ * beyond the arithmetic its CUDA dispatcher instantiates (cuda/kernel/level3/alphasparse_spmm.cu:
+ * 572-596): per element of Y a sum over the row's entries in storage order, then
+ * alpha*sum + beta*y -  int32 products and sums (wrapping, as the device's), or values widened to
+ * float with float sums, alpha and beta; the fp16 -> fp16 instance rounds once at the end (to
+ * nearest even).  Parity unpinned for these four. */
+static inline float f16_to_f32(uint16_t h) {
+  const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  uint32_t exp = (h >> 10) & 0x1Fu, man = h & 0x3FFu, u;
+  if (exp == 0) {
+    if (man == 0) u = sign;
+    else {                                  /* subnormal: normalise */
+      int sh = 0;
+      while (!(man & 0x400u)) { man <<= 1; ++sh; }
+      man &= 0x3FFu;
+      u = sign | ((uint32_t)(127 - 15 - sh + 1) << 23) | (man << 13);
+    }
+  } else if (exp == 31) u = sign | 0x7F800000u | (man << 13);
+  else u = sign | ((exp + 127 - 15) << 23) | (man << 13);
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+static inline uint16_t f32_to_f16(float f) {   /* round to nearest even */
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  const uint16_t sign = (uint16_t)((u >> 16) & 0x8000u);
+  const uint32_t a = u & 0x7FFFFFFFu;
+  if (a >= 0x7F800000u) return (uint16_t)(sign | 0x7C00u | (a > 0x7F800000u ? 0x200u : 0u));
+  if (a >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u);            /* rounds to infinity */
+  if (a < 0x33000001u) return sign;                                    /* rounds to zero */
+  int e = (int)(a >> 23) - 127;
+  uint32_t m = (a & 0x7FFFFFu) | 0x800000u;
+  int shift = e < -14 ? 13 + (-14 - e) : 13;                           /* subnormal halves lose more bits */
+  uint32_t q = m >> shift, rem = m & ((1u << shift) - 1u), half = 1u << (shift - 1);
+  if (rem > half || (rem == half && (q & 1u))) ++q;
+  if (e < -14) return (uint16_t)(sign | q);                            /* q may carry into the exponent: still right */
+  return (uint16_t)(sign | (uint16_t)((((uint32_t)(e + 15)) << 10) + (q - 0x400u)));
+}
+#define DEF_SPMM_WIDE(NAME, OFF_T, TA, TY, TS, LOAD, MAD, FINISH)                          \
+  void NAME(int64_t rows, const OFF_T* row_ptr, const int32_t* col, const TA* val,         \
+            const TA* X, int64_t n, int64_t ldx, TS alpha, TS beta, TY* Y, int64_t ldy) {  \
+    _Pragma("omp parallel for schedule(static)")                                           \
+    for (int64_t i = 0; i < rows; ++i)                                                     \
+      for (int64_t c = 0; c < n; ++c) {                                                    \
+        TS s = 0;                                                                          \
+        for (int64_t k = (int64_t)row_ptr[i]; k < (int64_t)row_ptr[i + 1]; ++k) {          \
+          const TS a = LOAD(val[k]), x = LOAD(X[(int64_t)col[k] * ldx + c]);               \
+          s = MAD;                                                                         \
+        }                                                                                  \
+        TY* y = Y + i * ldy + c;                                                           \
+        *y = FINISH;                                                                       \
+      }                                                                                    \
+  }
+#define ID_(v) (v)
+#define I32_(v) ((int32_t)(v))
+#define F32_(v) ((float)(v))
+#define WRAP_MAD_ (int32_t)((uint32_t)s + (uint32_t)a * (uint32_t)x)
+#define WRAP_FIN_ (int32_t)((uint32_t)alpha * (uint32_t)s + (beta == 0 ? 0u : (uint32_t)beta * (uint32_t)*y))
+#define F_FIN_ (beta == 0.f ? alpha * s : fmaf(alpha, s, beta * *y))
+#define H_FIN_ f32_to_f16(beta == 0.f ? alpha * s : fmaf(alpha, s, beta * f16_to_f32(*y)))
+DEF_SPMM_WIDE(oracle_spmm_i8_i32_i32, int32_t, int8_t, int32_t, int32_t, I32_, WRAP_MAD_, WRAP_FIN_)
+DEF_SPMM_WIDE(oracle_spmm_i8_i32_i64, int64_t, int8_t, int32_t, int32_t, I32_, WRAP_MAD_, WRAP_FIN_)
+DEF_SPMM_WIDE(oracle_spmm_i8_f32_i32, int32_t, int8_t, float, float, F32_, fmaf(a, x, s), F_FIN_)
+DEF_SPMM_WIDE(oracle_spmm_i8_f32_i64, int64_t, int8_t, float, float, F32_, fmaf(a, x, s), F_FIN_)
+DEF_SPMM_WIDE(oracle_spmm_f16_f32_i32, int32_t, uint16_t, float, float, f16_to_f32, fmaf(a, x, s), F_FIN_)
+DEF_SPMM_WIDE(oracle_spmm_f16_f32_i64, int64_t, uint16_t, float, float, f16_to_f32, fmaf(a, x, s), F_FIN_)
+DEF_SPMM_WIDE(oracle_spmm_f16_f16_i32, int32_t, uint16_t, uint16_t, float, f16_to_f32, fmaf(a, x, s), H_FIN_)
+DEF_SPMM_WIDE(oracle_spmm_f16_f16_i64, int64_t, uint16_t, uint16_t, float, f16_to_f32, fmaf(a, x, s), H_FIN_)
+
 /* Contiguous row ranges of near-equal nnz: bound[0]=0, bound[parts]=rows and
  * bound[i] = first index j in [0, rows-1] with row_end[j] >= (nnz/parts)*i, where
  * row_end = row_ptr+1 (hygon/util/partition.cpp:83-96 with lower_bound_int :41-57). */

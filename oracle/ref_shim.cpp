@@ -91,4 +91,25 @@ REF_MV_CPLX(ref_z_mv, double, ALPHA_Complex16, alphasparse_z_create_csr, alphasp
 REF_MM(ref_s_mm, float, alphasparse_s_create_csr, alphasparse_s_mm)
 REF_MM(ref_d_mm, double, alphasparse_d_create_csr, alphasparse_d_mm)
 
+#define REF_MM_CPLX(NAME, T, CT, CREATE, MM)                                               \
+  int NAME(int rows, int cols, const int* row_ptr, const int* col_idx, const T* val,       \
+           const T* X, int n, int ldx, const T* alpha, const T* beta, T* Y, int ldy) {     \
+    alphasparse_matrix_t A = nullptr;                                                      \
+    int st = (int)CREATE(&A, ALPHA_SPARSE_INDEX_BASE_ZERO, rows, cols, (int*)row_ptr,      \
+                         (int*)row_ptr + 1, (int*)col_idx, (CT*)val);                      \
+    if (st != 0) return 100 + st;                                                          \
+    struct alpha_matrix_descr d;                                                           \
+    d.type = ALPHA_SPARSE_MATRIX_TYPE_GENERAL;                                             \
+    d.mode = ALPHA_SPARSE_FILL_MODE_LOWER;                                                 \
+    d.diag = ALPHA_SPARSE_DIAG_NON_UNIT;                                                   \
+    CT a, b;                                                                               \
+    a.real = alpha[0]; a.imag = alpha[1]; b.real = beta[0]; b.imag = beta[1];              \
+    st = (int)MM(ALPHA_SPARSE_OPERATION_NON_TRANSPOSE, a, A, d, ALPHA_SPARSE_LAYOUT_ROW_MAJOR,\
+                 (const CT*)X, n, ldx, b, (CT*)Y, ldy);                                    \
+    alphasparse_destroy(A);                                                                \
+    return st;                                                                             \
+  }
+REF_MM_CPLX(ref_c_mm, float, ALPHA_Complex8, alphasparse_c_create_csr, alphasparse_c_mm)
+REF_MM_CPLX(ref_z_mm, double, ALPHA_Complex16, alphasparse_z_create_csr, alphasparse_z_mm)
+
 }  // extern "C"

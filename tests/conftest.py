@@ -47,8 +47,9 @@ def golden():
 
 
 def rel_l2(a, b):
-    a = np.asarray(a, dtype=np.float64).ravel()
-    b = np.asarray(b, dtype=np.float64).ravel()
+    wide = np.complex128 if (np.iscomplexobj(a) or np.iscomplexobj(b)) else np.float64
+    a = np.asarray(a, dtype=wide).ravel()
+    b = np.asarray(b, dtype=wide).ravel()
     d = np.linalg.norm(b)
     return float(np.linalg.norm(a - b) / d) if d > 0 else float(np.linalg.norm(a - b))
 
