@@ -1764,8 +1764,8 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
 
   const size_t b_stage = (size_t)(n / 64) * TC_BBLK;
   if (want_tmem && tp->runs && tp->kcol) {
-    const int np = n > 128 ? 128 : n;   // columns of a pass
-    const size_t b_stage_p = (size_t)(np / 64) * TC_BBLK;
+    const int np_max = n > 128 ? 128 : n;   // columns of a pass: 128, and what is left (N = 192: 128 + 64)
+    const size_t b_stage_p = (size_t)(np_max / 64) * TC_BBLK;
     const size_t smem = 1024 + TCT_STAGES * b_stage_p + TCT_GROUPS * (size_t)TCT_PRIV + TCT_CSR * (size_t)TCT_CAPB * 3 +
                         TCT_CSR * (size_t)TCT_RUNCH * TC_M * 4 + TCT_CSR * 16 + 4 * TCT_TRBYTES +
                         (12 + 2 * TCT_STAGES) * 8 + 16;
@@ -1779,7 +1779,8 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
       }
       int64_t g = impl(h)->sm_count;
       if (g > tp->blocks) g = tp->blocks;
-      for (int c0 = 0; c0 < n; c0 += np) {
+      for (int c0 = 0; c0 < n; c0 += np_max) {
+        const int np = n - c0 < np_max ? n - c0 : np_max;
         void* bp = reinterpret_cast<__nv_bfloat16*>(B->values) + c0;
         float* cp = reinterpret_cast<float*>(C->values) + c0;
         CUtensorMap tm3;
@@ -1791,7 +1792,16 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
                             enc(&tm3, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, bp, dims3, strides3, box3, estr3,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-        if (!one_box && np > 64) return ALPHA_SPARSE_STATUS_INVALID_VALUE;   // the 2-D map covers a single pass only
+        CUtensorMap tm2 = tm;   // a 64-column pass: one 2-D box per chunk
+        if (!one_box) {
+          const cuuint64_t dims2[2] = {(cuuint64_t)np, (cuuint64_t)B->rows};
+          const cuuint64_t strides2[1] = {(cuuint64_t)B->ld * 2};
+          const cuuint32_t box2[2] = {64, (cuuint32_t)TC_KC};
+          if (np > 64 || enc(&tm2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, bp, dims2, strides2, box2, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+        }
         // C leaves by TMA stores of 32 x 32 blocks when it is only written (beta = 0)
         CUtensorMap tmc = tm;
         const cuuint64_t dimsc[2] = {(cuuint64_t)np, (cuuint64_t)A->rows};
@@ -1802,7 +1812,7 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
         spmm_tc_tmem_kernel<<<(unsigned)g, TCT_THREADS, smem, h->stream>>>(
-            one_box ? tm3 : tm, tmc, c_by_tma, A->const_row_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
+            one_box ? tm3 : tm2, tmc, c_by_tma, A->const_row_data, reinterpret_cast<const __nv_bfloat16*>(A->const_val_data),
             cp, C->ld, alpha, beta, A->rows, A->nnz, np, (int)tp->blocks, tp->chunk_off, tp->chunk_cnt, tp->chunk_list,
             tp->runs, tp->kcol, one_box, p->wait_cfg, p->dev_err);
         impl(h)->launches++;

@@ -68,7 +68,7 @@ def _run_tc(handle, A, X, Y0, alpha, beta, ldx, ldy, kernel):
 
 
 @pytest.mark.parametrize("kernel", list(KERNELS))
-@pytest.mark.parametrize("n", [64, 128, 256])
+@pytest.mark.parametrize("n", [64, 128, 192, 256])
 @pytest.mark.parametrize("grid", [16, 10])
 def test_stencil_bf16(handle, n, grid, kernel):
     A = G.stencil_3d_27pt(grid, seed=4)          # grid 10: 1000 rows, last row block partial
