@@ -255,3 +255,31 @@ def test_waits_that_run_out_are_reported_bf16(handle, monkeypatch):
     want = oracle.spmm(A.row_ptr.numpy(), A.col_idx.numpy(), bits(A.val), bits(X), 1.0, 0.0, Y0.numpy())
     got = run_tc(handle, A, X, Y0, 1.0, 0.0, kernel="tcgen05")     # a new descriptor: new plan, normal waits
     assert rel_l2(got, want) <= 1e-5
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05-smem"])
+def test_row_blocks_with_many_chunks_bf16(handle, kernel):
+    """Row blocks that touch 40 column chunks each: more than the tensor-memory kernel stages run words for
+    (the rest come from global memory), few entries per chunk, a partial last block; B is tall, so the
+    density test still accepts the matrix."""
+    rng = np.random.default_rng(21)
+    rows, cols = 1024 + 17, 65536
+    cis, lens = [], []
+    for r in range(rows):
+        b = r // 128
+        js = np.sort(rng.choice(40, size=30, replace=False))
+        c = 64 * ((b * 37 + js * 53) % 1024) + (r * 7 + js) % 64
+        c = np.sort(c)
+        cis.append(c.astype(np.int32))
+        lens.append(len(c))
+    rp = np.zeros(rows + 1, dtype=np.int32)
+    rp[1:] = np.cumsum(lens)
+    ci = np.concatenate(cis)
+    v = torch.from_numpy(rng.standard_normal(len(ci)).astype(np.float32)).to(torch.bfloat16)
+    A = G.Csr(rows, cols, torch.from_numpy(rp), torch.from_numpy(ci), v)
+    n = 128
+    X = G.uniform((cols, n), -1, 1, dtype=torch.bfloat16, seed=87)
+    Y0 = G.uniform((rows, n), -1, 1, seed=88)
+    want = oracle.spmm(rp, ci, bits(A.val), bits(X), 0.75, -0.5, Y0.numpy())
+    got = run_tc(handle, A, X, Y0, 0.75, -0.5, kernel=kernel)
+    assert rel_l2(got, want) <= 1e-5
