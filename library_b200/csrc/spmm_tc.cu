@@ -64,13 +64,13 @@ struct TcPlan {
   uint32_t* runs = nullptr;       // device, 128 words per chunk slot: (first entry of the row's run in the chunk,
                                   // counted from the block's first entry rounded down to 16) << 7 | entries in the run
   uint8_t* kcol = nullptr;        // device, nnz bytes: the entry's column modulo 64 (its position in the chunk)
-  bool runs_tried = false;
+  bool runs_tried = false, scatter_tried = false;
 };
 
 // ---- preprocessing -------------------------------------------------------------------------
 // One CTA per row block.  FILL = false: counts[b] = number of non-empty chunks, flags[0] |= 1 if
 // the block spans more chunks than the bitmap, flags[1] |= 1 if a row's columns are not
-// ascending.  FILL = true: writes the chunk ids, ascending, at chunk_off[b].
+// strictly ascending (out of order, or a column twice: two entries would land on one tile element).  FILL = true: writes the chunk ids, ascending, at chunk_off[b].
 template <bool FILL>
 __global__ void __launch_bounds__(256) tc_chunks_kernel(const int32_t* __restrict__ rp,
                                                         const int32_t* __restrict__ col, int64_t rows,
@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(256) tc_chunks_kernel(const int32_t* __restric
     bool unsorted = false;
     if (tid < (int)(r1 - r0)) {
       const int s = rp[r0 + tid], e = rp[r0 + tid + 1];
-      for (int k = s + 1; k < e; ++k) unsorted |= col[k] < col[k - 1];
+      for (int k = s + 1; k < e; ++k) unsorted |= col[k] <= col[k - 1];   // descending, or a column twice
     }
     if (over) atomicOr(&flags[0], 1);
     if (unsorted) atomicOr(&flags[1], 1);
@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(128) tc_scatter_kernel(const int32_t* __restri
                                                          const int32_t* __restrict__ chunk_list,
                                                          int32_t* __restrict__ counts,
                                                          const int32_t* __restrict__ chunk_ent,
-                                                         uint32_t* __restrict__ scatter, int* __restrict__ flags) {
+                                                         uint32_t* __restrict__ scatter) {
   __shared__ int s_rp[TC_M + 1];
   const int64_t r0 = (int64_t)blockIdx.x * TC_M;
   const int nr = (int)(r0 + TC_M < rows ? TC_M : rows - r0);
@@ -187,9 +187,6 @@ __global__ void __launch_bounds__(128) tc_scatter_kernel(const int32_t* __restri
         }
       } else {
         n += hi - lo;
-        // two entries of a row in one column would land on one tile element
-        for (int e = lo + 1; e < hi; ++e)
-          if (col[e] == col[e - 1]) atomicOr(&flags[1], 1);
       }
     }
     if (!FILL) counts[j0 + j] = n;
@@ -1619,34 +1616,6 @@ alphasparseStatus_t build_plan(alphasparseHandle_t h, alphasparseSpMatDescr_t A,
     impl(h)->launches++;
     e = cudaStreamSynchronize(st);
   }
-  // the scatter list: count per chunk, scan, fill
-  if (e == cudaSuccess && tp->usable && total_padded > 0 && A->nnz > 0) {
-    int32_t* ent_cnt = nullptr;
-    size_t sb_bytes = 0;
-    cub::DeviceScan::ExclusiveSum(nullptr, sb_bytes, ent_cnt, tp->chunk_ent, total_padded, st);
-    if (cudaMalloc(&ent_cnt, sizeof(int32_t) * (size_t)total_padded) != cudaSuccess ||
-        cudaMalloc(&tp->chunk_ent, sizeof(int32_t) * (size_t)total_padded) != cudaSuccess ||
-        cudaMalloc(&tp->scatter, sizeof(uint32_t) * (size_t)A->nnz) != cudaSuccess ||
-        (sb_bytes > tmp_bytes && (cudaFree(tmp), tmp = nullptr, tmp_bytes = sb_bytes,
-                                  cudaMalloc(&tmp, sb_bytes) != cudaSuccess))) {
-      cudaFree(ent_cnt);
-      cleanup();
-      return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
-    }
-    cudaMemsetAsync(ent_cnt, 0, sizeof(int32_t) * (size_t)total_padded, st);
-    tc_scatter_kernel<false><<<(unsigned)nb, 128, 0, st>>>(A->const_row_data, A->const_col_data, A->rows,
-                                                          tp->chunk_off, tp->chunk_cnt, tp->chunk_list, ent_cnt,
-                                                          nullptr, nullptr, flags);
-    cub::DeviceScan::ExclusiveSum(tmp, sb_bytes, ent_cnt, tp->chunk_ent, total_padded, st);
-    tc_scatter_kernel<true><<<(unsigned)nb, 128, 0, st>>>(A->const_row_data, A->const_col_data, A->rows,
-                                                         tp->chunk_off, tp->chunk_cnt, tp->chunk_list, nullptr,
-                                                         tp->chunk_ent, tp->scatter, nullptr);
-    impl(h)->launches += 3;
-    e = cudaMemcpyAsync(hflags, flags, sizeof hflags, cudaMemcpyDeviceToHost, st);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-    cudaFree(ent_cnt);
-    if (e == cudaSuccess && hflags[1]) tp->usable = false;  // a repeated column inside a row
-  }
   // the largest chunk count of a block decides whether chunk ids fit the persistent kernel's staging
   if (e == cudaSuccess && tp->usable) {
     size_t rb = 0;
@@ -1660,6 +1629,49 @@ alphasparseStatus_t build_plan(alphasparseHandle_t h, alphasparseSpMatDescr_t A,
     }
   }
   cleanup();
+  return status_of(e);
+}
+
+// The scatter list of the kernels that build A tiles in shared memory: count per chunk, scan,
+// fill.  Built when one of those kernels is first chosen (the default kernel keeps A in tensor
+// memory and needs the run list instead).
+alphasparseStatus_t build_scatter(alphasparseHandle_t h, alphasparseSpMatDescr_t A, TcPlan* tp) {
+  tp->scatter_tried = true;
+  if (!tp->usable || !tp->chunk_list || A->nnz == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+  cudaStream_t st = h->stream;
+  const int nb = (int)tp->blocks;
+  int32_t total_padded = 0;
+  cudaError_t e = cudaMemcpyAsync(&total_padded, tp->chunk_off + nb, sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return status_of(e);
+  if (total_padded <= 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+  int32_t* ent_cnt = nullptr;
+  void* tmp = nullptr;
+  size_t sb_bytes = 0;
+  cub::DeviceScan::ExclusiveSum(nullptr, sb_bytes, ent_cnt, tp->chunk_ent, total_padded, st);
+  if (cudaMalloc(&ent_cnt, sizeof(int32_t) * (size_t)total_padded) != cudaSuccess ||
+      cudaMalloc(&tp->chunk_ent, sizeof(int32_t) * (size_t)total_padded) != cudaSuccess ||
+      cudaMalloc(&tp->scatter, sizeof(uint32_t) * (size_t)A->nnz) != cudaSuccess ||
+      cudaMalloc(&tmp, sb_bytes ? sb_bytes : 16) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(ent_cnt);
+    cudaFree(tmp);
+    cudaFree(tp->chunk_ent);
+    cudaFree(tp->scatter);
+    tp->chunk_ent = nullptr;
+    tp->scatter = nullptr;
+    return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+  }
+  cudaMemsetAsync(ent_cnt, 0, sizeof(int32_t) * (size_t)total_padded, st);
+  tc_scatter_kernel<false><<<(unsigned)nb, 128, 0, st>>>(A->const_row_data, A->const_col_data, A->rows, tp->chunk_off,
+                                                        tp->chunk_cnt, tp->chunk_list, ent_cnt, nullptr, nullptr);
+  cub::DeviceScan::ExclusiveSum(tmp, sb_bytes, ent_cnt, tp->chunk_ent, total_padded, st);
+  tc_scatter_kernel<true><<<(unsigned)nb, 128, 0, st>>>(A->const_row_data, A->const_col_data, A->rows, tp->chunk_off,
+                                                       tp->chunk_cnt, tp->chunk_list, nullptr, tp->chunk_ent, tp->scatter);
+  impl(h)->launches += 3;
+  e = cudaStreamSynchronize(st);
+  cudaFree(ent_cnt);
+  cudaFree(tmp);
   return status_of(e);
 }
 
@@ -1746,6 +1758,10 @@ alphasparseStatus_t spmm_tc_run(alphasparseHandle_t h, alphasparseSpMatDescr_t A
                          p->max_block_nnz + 16 < (int64_t(1) << 25);
   if (want_tmem && !tp->runs_tried) {
     alphasparseStatus_t s = build_runs(h, A, tp);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+  }
+  if (!(want_tmem && tp->runs && tp->kcol) && env_int("ASP_TC_PERSISTENT", 1) && !tp->scatter_tried) {
+    alphasparseStatus_t s = build_scatter(h, A, tp);   // the kernel with A tiles in shared memory will run
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   }
   if (preprocess_only || A->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
