@@ -46,6 +46,22 @@ def golden():
     return load_golden()
 
 
+def load_golden_complex():
+    """tests/golden/csr_golden_complex.npz: complex mv / mm cases from the reference's alphasparse_{c,z}_mv / _mm
+    (same generator script)."""
+    z = np.load(os.path.join(ROOT, "tests", "golden", "csr_golden_complex.npz"))
+    out = {}
+    for key in z.files:
+        case, field = key.split("/")
+        out.setdefault(case, {})[field] = z[key]
+    for c in out.values():
+        for f in ("alpha", "beta"):
+            c[f] = complex(c[f])
+        c["kind"] = str(c["kind"])
+        c["cols"] = int(c["cols"])
+    return out
+
+
 def rel_l2(a, b):
     wide = np.complex128 if (np.iscomplexobj(a) or np.iscomplexobj(b)) else np.float64
     a = np.asarray(a, dtype=wide).ravel()

@@ -1,5 +1,5 @@
-"""Generates tests/golden/csr_golden.npz by running the REFERENCE's own hygon CSR mv / mm
-code (oracle/_ref/libasp_ref.so, built by `make -C oracle ref` from the mounted reference
+"""Generates tests/golden/csr_golden.npz and tests/golden/csr_golden_complex.npz by running the REFERENCE's own
+hygon CSR mv / mm code (oracle/_ref/libasp_ref.so, built by `make -C oracle ref` from the mounted reference
 tree) on small seeded inputs.  Inputs and the reference's outputs are both stored, so the
 fixture pins the oracle restatement and the CUDA path on machines without the reference.
 
@@ -55,17 +55,49 @@ def cases():
     return out
 
 
+def complex_cases():
+    """Complex mv / mm through the reference's alphasparse_{c,z}_mv and alphasparse_{c,z}_mm.  These pin the
+    oracle's complex restatements within rounding (the reference's kernels unroll their sums), not bit for bit."""
+    out = {}
+    rng = np.random.default_rng(77)
+
+    def cplx(shape, dtype):
+        return (rng.uniform(-1, 1, shape) + 1j * rng.uniform(-1, 1, shape)).astype(dtype)
+
+    mats = {"rmat_9": G.rmat(9, 8, seed=21), "lap2d_20": G.laplacian_2d_5pt(20),
+            "poisson_400x300": G.poisson_random(400, 300, mean_len=6, seed=22)}
+    for mname, A in mats.items():
+        rp, ci, _ = A.numpy()
+        for dtype, tag in ((np.complex64, "c32"), (np.complex128, "c64")):
+            v = cplx(A.nnz, dtype)
+            alpha, beta = 1.5 - 0.5j, 0.25 + 2.0j
+            x, y0 = cplx(A.cols, dtype), cplx(A.rows, dtype)
+            y = oracle.ref_spmv_complex(rp, ci, v, x, alpha, beta, y0, cols=A.cols)
+            out[f"{mname}_{tag}_mv"] = dict(kind="mv", rp=rp, ci=ci, v=v, x=x, y0=y0, alpha=alpha, beta=beta, y=y,
+                                            cols=A.cols)
+            X, Y0 = cplx((A.cols, 7), dtype), cplx((A.rows, 7), dtype)
+            Y = oracle.ref_spmm_complex(rp, ci, v, X, alpha, beta, Y0)
+            out[f"{mname}_{tag}_mm"] = dict(kind="mm", rp=rp, ci=ci, v=v, x=X, y0=Y0, alpha=alpha, beta=beta, y=Y,
+                                            cols=A.cols)
+    return out
+
+
+def save(name, cs):
+    flat = {}
+    for cname, c in cs.items():
+        for k, val in c.items():
+            flat[f"{cname}/{k}"] = np.asarray(val)
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), name)
+    np.savez_compressed(path, **flat)
+    print(path, os.path.getsize(path), "bytes,", len(cs), "cases")
+
+
 def main():
     if not oracle.have_ref():
         raise SystemExit("oracle/_ref/libasp_ref.so is missing: run `make -C oracle ref` first")
     oracle.ref_set_threads(4)
-    flat = {}
-    for name, c in cases().items():
-        for k, val in c.items():
-            flat[f"{name}/{k}"] = np.asarray(val)
-    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csr_golden.npz")
-    np.savez_compressed(path, **flat)
-    print(path, os.path.getsize(path), "bytes,", len(cases()), "cases")
+    save("csr_golden.npz", cases())
+    save("csr_golden_complex.npz", complex_cases())
 
 
 if __name__ == "__main__":

@@ -39,6 +39,40 @@ def test_complex_spmm_restatement_against_the_compiled_reference(dtype, tol):
                 assert np.linalg.norm(got - want) <= tol * np.linalg.norm(want)
 
 
+def test_complex_restatements_against_the_golden_vectors():
+    """The committed outputs of the reference's complex mv / mm (tests/golden/csr_golden_complex.npz) pin the oracle's
+    complex restatements where the reference itself is not at hand."""
+    from conftest import load_golden_complex
+    for name, c in load_golden_complex().items():
+        tol = 1e-6 if c["v"].dtype == np.complex64 else 1e-14
+        if c["kind"] == "mv":
+            got = oracle.spmv_complex(c["rp"], c["ci"], c["v"], c["x"], c["alpha"], c["beta"], c["y0"])
+        else:
+            got = oracle.spmm_complex(c["rp"], c["ci"], c["v"], c["x"], c["alpha"], c["beta"], c["y0"])
+        assert rel_l2(got, c["y"]) <= tol, name
+
+
+@pytest.mark.gpu
+def test_complex_kernels_against_the_golden_vectors(handle):
+    """The CUDA complex SpMV and SpMM against the reference's committed outputs."""
+    from conftest import load_golden_complex
+    from library_b200 import api
+    handle.use_torch_stream()
+    for name, c in load_golden_complex().items():
+        tol = 1e-5 if c["v"].dtype == np.complex64 else 1e-12
+        dev = "cuda"
+        Am = api.CsrMatrix(len(c["rp"]) - 1, c["cols"], torch.from_numpy(c["rp"]).to(dev), torch.from_numpy(c["ci"]).to(dev),
+                           torch.from_numpy(c["v"]).to(dev))
+        y = torch.from_numpy(np.array(c["y0"], copy=True)).to(dev)
+        x = torch.from_numpy(c["x"]).to(dev)
+        if c["kind"] == "mv":
+            api.spmv(handle, Am, api.DnVec(x), api.DnVec(y), c["alpha"], c["beta"])
+        else:
+            api.spmm(handle, Am, api.DnMat(x), api.DnMat(y), c["alpha"], c["beta"])
+        torch.cuda.synchronize()
+        assert rel_l2(y.cpu().numpy(), c["y"]) <= tol, name
+
+
 def test_fp16_conversions_of_the_oracle_match_numpy():
     """Every half bit pattern widens to numpy's float32, and rounding back (through the fp16 -> fp16 instance with an
     identity matrix) is numpy's round-to-nearest-even, ties and subnormals included."""
