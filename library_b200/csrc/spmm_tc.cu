@@ -7,17 +7,24 @@
 // keeps the idea - treat the non-empty column blocks of a row block as small dense matrices -
 // and rebuilds it for tcgen05:
 //   * preprocessing (device): for every block of 128 rows, the ascending list of 64-column
-//     chunks that hold at least one entry (a bitmap per row block, a scan, a fill);
-//   * the kernel (spmm_tc_persistent_kernel, the default): one persistent, warp-specialised CTA per
-//     SM walks row blocks.  Per 64-column chunk a TMA warp fetches the 64 x N slice of B
-//     (cp.async.bulk.tensor, 128-byte swizzle, completion on an mbarrier) into a ring of stages,
-//     builder warps clear a 128 x 64 bf16 tile of A in shared memory and scatter the chunk's
-//     entries into it from a per-chunk scatter list the plan holds, one issuing thread per
-//     accumulator runs four tcgen05.mma (M=128, N, K=16) into tensor memory and tcgen05.commit
-//     hands the stage back; an epilogue warp group reads the fp32 accumulators with tcgen05.ld and
-//     writes alpha*acc + beta*C while the next row block's chunks are already in the ring.
-//     spmm_tc_kernel (one CTA per row block, three B stages, two A tiles) is the simple form kept
-//     for matrices whose blocks hold more chunks than the persistent kernel's staging.
+//     chunks that hold at least one entry (a bitmap per row block, a scan, a fill); per chunk and
+//     row where the row's run of entries inside the chunk starts and how long it is, and per entry
+//     its column modulo 64 (or, for the kernels below the first, a per-chunk scatter list);
+//   * spmm_tc_tmem_kernel (the default): one persistent, warp-specialised CTA per SM walks row
+//     blocks.  The 128 x 64 chunk of A goes to the MMAs from TENSOR MEMORY: a builder thread owns a
+//     row, gathers the row's few entries of the chunk and stores 32 registers with tcgen05.st;
+//     loader warps fetch the chunk's 64 x N slice of B (cp.async.bulk.tensor, 128-byte swizzle,
+//     completion on an mbarrier) into a ring of six stages; one warp issues four tcgen05.mma
+//     (M=128, N, K=16) per chunk through an elected lane and tcgen05.commit hands the stage back;
+//     an epilogue warp group reads the fp32 accumulators with tcgen05.ld and writes C (TMA stores
+//     when beta = 0) while the next row block's chunks are already in the ring.  N = 192 and 256
+//     run as two passes over 128 columns of B and C and the rest.
+//   * spmm_tc_persistent_kernel (ASP_TC_A_TMEM=0, or when the run list cannot be built): the same
+//     pipeline with builder warps clearing a 128 x 64 bf16 tile of A in shared memory and
+//     scattering the chunk's entries into it.
+//   * spmm_tc_kernel (ASP_TC_PERSISTENT=0): one CTA per row block, three B stages, two A tiles -
+//     the simple form, also for matrices whose blocks hold more chunks than the persistent
+//     shared-memory kernel stages.
 // Every mbarrier wait is bounded; on expiry the CTA raises *err, frees its tensor memory and
 // leaves.  No TMA load here uses cluster multicast.
 #include <cuda.h>
