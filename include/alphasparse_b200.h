@@ -253,8 +253,9 @@ alphasparseStatus_t alphasparseDnMatSetValues(alphasparseDnMatDescr_t descr, voi
  *   R_16F / R_32F / R_32F  (:288-292)  R_16BF / R_16BF / R_32F (:294-300)
  *   C_32F / C_32F / C_32F  (:246-253)  C_64F / C_64F / C_64F  (:255-262)
  *   R_8I  / R_32I / R_32I  (:276-281)  R_8I  / R_32F / R_32F  (:282-287)
- * with 32- or 64-bit row offsets (complex and int8: opA = NON_TRANSPOSE only, one plain
- * kernel over the plan's row classes).  The reference's half-precision complex instances are
+ * with 32- or 64-bit row offsets (complex and int8: one plain kernel over the plan's row
+ * classes; opA = TRANSPOSE on the transposed copy, CONJUGATE_TRANSPOSE of a complex matrix
+ * NOT_SUPPORTED - the copy keeps the values as they are).  The reference's half-precision complex instances are
  * not provided.
  * opA = TRANSPOSE (or CONJUGATE_TRANSPOSE, the same for real types): x has A's row count, y its
  * column count; the first such call (or alphasparseSpMV_analysis with that opA) builds a
@@ -332,7 +333,8 @@ alphasparseStatus_t alphasparseSpMVCsrNoAlloc(cudaStream_t stream, int64_t rows,
  *   R_8I  / R_32I / R_32I      R_8I  / R_32F / R_32F
  *   R_16F / R_32F / R_32F      R_16F / R_16F / R_32F
  * with 32- or 64-bit row offsets; the complex, int8 and fp16 rows run one plain kernel
- * (opA = NON_TRANSPOSE only). */
+ * (opA = TRANSPOSE on the transposed copy; CONJUGATE_TRANSPOSE of a complex matrix
+ * NOT_SUPPORTED). */
 alphasparseStatus_t alphasparseSpMM(alphasparseHandle_t handle, alphasparseOperation_t opA,
                                     alphasparseOperation_t opB, const void* alpha,
                                     alphasparseSpMatDescr_t matA, alphasparseDnMatDescr_t matB,

@@ -280,13 +280,13 @@ def spmm_buffer_size(handle: Handle, A: CsrMatrix, B: DnMat, Cm: DnMat, alg=SPMM
 
 
 def spmm(handle: Handle, A: CsrMatrix, B: DnMat, Cm: DnMat, alpha=1.0, beta=0.0,
-         alg=SPMM_ALG_DEFAULT, compute=None, buffer: torch.Tensor | None = None):
+         alg=SPMM_ALG_DEFAULT, compute=None, buffer: torch.Tensor | None = None, op=OP_N):
     """C = alpha*A*B + beta*C on handle's stream (asynchronous).  B and C both row-major, or both
     column-major with a ``buffer`` of spmm_buffer_size bytes."""
     code = _spmm_compute_code(Cm.t.dtype) if compute is None else compute
     a, b = _scalar(alpha, code), _scalar(beta, code)
     buf = C.c_void_p(buffer.data_ptr()) if buffer is not None else C.c_void_p()
-    _check(load().alphasparseSpMM(handle.h, OP_N, OP_N, C.byref(a), A.d, B.d, C.byref(b), Cm.d, code,
+    _check(load().alphasparseSpMM(handle.h, op, OP_N, C.byref(a), A.d, B.d, C.byref(b), Cm.d, code,
                                   alg, buf), "alphasparseSpMM")
 
 

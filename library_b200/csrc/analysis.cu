@@ -498,12 +498,16 @@ alphasparseStatus_t transposed_of(alphasparseHandle_t h, alphasparseSpMatDescr_t
   transpose_fill_kernel<OFF, W><<<g, 256, 0, st>>>((const OFF*)A->row_offsets, A->rows, perm, nnz,                \
                                                   (const W*)A->const_val_data, t->col, (W*)t->val)
     if (o64) {
-      if (es == 2) ASP_FILL(int64_t, uint16_t);
+      if (es == 1) ASP_FILL(int64_t, uint8_t);
+      else if (es == 2) ASP_FILL(int64_t, uint16_t);
       else if (es == 4) ASP_FILL(int64_t, uint32_t);
+      else if (es == 16) ASP_FILL(int64_t, uint4);
       else ASP_FILL(int64_t, uint64_t);
     } else {
-      if (es == 2) ASP_FILL(int32_t, uint16_t);
+      if (es == 1) ASP_FILL(int32_t, uint8_t);
+      else if (es == 2) ASP_FILL(int32_t, uint16_t);
       else if (es == 4) ASP_FILL(int32_t, uint32_t);
+      else if (es == 16) ASP_FILL(int32_t, uint4);
       else ASP_FILL(int32_t, uint64_t);
     }
 #undef ASP_FILL

@@ -512,8 +512,11 @@ alphasparseStatus_t check_spmm_args(alphasparseHandle_t h, alphasparseOperation_
                      computeType == A->data_type;
   const bool mixed = A->data_type == ALPHA_R_16BF && B->data_type == ALPHA_R_16BF &&
                      C->data_type == ALPHA_R_32F && computeType == ALPHA_R_32F;
-  // complex, int8 and fp16 instances: one plain kernel, opA = N only (no transposed copy is built for them)
-  const bool other = !tr && spmm_other_types(A->data_type, B->data_type, C->data_type, computeType);
+  // complex, int8 and fp16 instances: one plain kernel; complex: the transposed copy holds the values as
+  // they are, so the conjugate transpose is not offered
+  const bool conj_c = opA == ALPHA_SPARSE_OPERATION_CONJUGATE_TRANSPOSE &&
+                      (A->data_type == ALPHA_C_32F || A->data_type == ALPHA_C_64F);
+  const bool other = !conj_c && spmm_other_types(A->data_type, B->data_type, C->data_type, computeType);
   if (!plain && !mixed && !other) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
   return ALPHA_SPARSE_STATUS_SUCCESS;
 }

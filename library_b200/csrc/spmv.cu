@@ -837,8 +837,8 @@ alphasparseStatus_t check_spmv_args(alphasparseHandle_t h, alphasparseOperation_
   alphasparseStatus_t s = validate_csr(A);
   if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
   if (!x->init || !y->init) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
-  // the complex and int8 instances exist for opA = N only (no transposed copy is built for them)
-  if (tr && (A->data_type == ALPHA_C_32F || A->data_type == ALPHA_C_64F || A->data_type == ALPHA_R_8I))
+  // complex: the transposed copy holds the values as they are, so the conjugate transpose is not offered
+  if (opA == ALPHA_SPARSE_OPERATION_CONJUGATE_TRANSPOSE && (A->data_type == ALPHA_C_32F || A->data_type == ALPHA_C_64F))
     return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
   if (!spmv_lowp_types(A->data_type, x->data_type, y->data_type, computeType) &&
       !spmv_other_types(A->data_type, x->data_type, y->data_type, computeType)) {

@@ -177,3 +177,59 @@ def test_fp16_spmm_on_the_gpu(handle):
                 got = _run(handle, A, v, X, Y16, alpha, beta, ld_pad=pad)
                 want = oracle.spmm_wide(rp, ci, v, X, alpha, beta, Y16)
                 assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+def _transposed(A, v):
+    """CSR of the transpose (numpy), entries of a row in ascending column order like the device copy."""
+    rp, ci, _ = A.numpy()
+    rows_of = np.repeat(np.arange(A.rows, dtype=np.int64), np.diff(rp))
+    order = np.lexsort((rows_of, ci))
+    trp = np.zeros(A.cols + 1, dtype=np.int32)
+    np.add.at(trp, ci + 1, 1)
+    trp = np.cumsum(trp).astype(np.int32)
+    return trp, rows_of[order].astype(np.int32), v[order]
+
+
+@pytest.mark.gpu
+def test_transposed_a_for_complex_and_int8(handle):
+    """opA = TRANSPOSE runs on a transposed copy the plan builds on the device (values moved as they are, 1- to
+    16-byte elements): SpMV and SpMM against the oracle on the explicitly transposed matrix.  The conjugate
+    transpose of a complex matrix is refused."""
+    from library_b200 import api
+    handle.use_torch_stream()
+    dev = "cuda"
+    rng = np.random.default_rng(66)
+    A = G.poisson_random(900, 1300, 6.0, seed=67)
+    rp, ci, _ = A.numpy()
+    for dtype, tol in ((np.complex64, 1e-5), (np.complex128, 1e-12)):
+        v = _cplx(rng, A.nnz, dtype)
+        trp, tci, tv = _transposed(A, v)
+        Am = api.CsrMatrix(A.rows, A.cols, torch.from_numpy(rp).to(dev), torch.from_numpy(ci).to(dev), torch.from_numpy(v).to(dev))
+        x, y0 = _cplx(rng, A.rows, dtype), _cplx(rng, A.cols, dtype)
+        y = torch.from_numpy(y0.copy()).to(dev)
+        api.spmv(handle, Am, api.DnVec(torch.from_numpy(x).to(dev)), api.DnVec(y), 0.5 - 1j, 2.0 + 0.5j, op=api.OP_T)
+        torch.cuda.synchronize()
+        assert rel_l2(y.cpu().numpy(), oracle.spmv_complex(trp, tci, tv, x, 0.5 - 1j, 2.0 + 0.5j, y0)) <= tol
+        X, Y0 = _cplx(rng, (A.rows, 12), dtype), _cplx(rng, (A.cols, 12), dtype)
+        Y = torch.from_numpy(Y0.copy()).to(dev)
+        api.spmm(handle, Am, api.DnMat(torch.from_numpy(X).to(dev)), api.DnMat(Y), 1.5, -0.5j, op=api.OP_T)
+        torch.cuda.synchronize()
+        assert rel_l2(Y.cpu().numpy(), oracle.spmm_complex(trp, tci, tv, X, 1.5, -0.5j, Y0)) <= tol
+        with pytest.raises(api.AlphaSparseError) as e:
+            api.spmv(handle, Am, api.DnVec(torch.from_numpy(x).to(dev)), api.DnVec(y), 1.0, 0.0, op=api.OP_C)
+        assert e.value.status == 6
+    v8 = rng.integers(-128, 128, A.nnz).astype(np.int8)
+    trp, tci, tv = _transposed(A, v8)
+    Am = api.CsrMatrix(A.rows, A.cols, torch.from_numpy(rp).to(dev), torch.from_numpy(ci).to(dev), torch.from_numpy(v8).to(dev))
+    x8 = rng.integers(-128, 128, A.rows).astype(np.int8)
+    y0 = rng.integers(-1000, 1000, A.cols).astype(np.int32)
+    y = torch.from_numpy(y0.copy()).to(dev)
+    api.spmv(handle, Am, api.DnVec(torch.from_numpy(x8).to(dev)), api.DnVec(y), 3, -2, op=api.OP_T)
+    torch.cuda.synchronize()
+    assert np.array_equal(y.cpu().numpy(), oracle.spmv_int8(trp, tci, tv, x8, 3, -2, y0))
+    X8 = rng.integers(-128, 128, (A.rows, 9)).astype(np.int8)
+    Y0 = rng.integers(-1000, 1000, (A.cols, 9)).astype(np.int32)
+    Y = torch.from_numpy(Y0.copy()).to(dev)
+    api.spmm(handle, Am, api.DnMat(torch.from_numpy(X8).to(dev)), api.DnMat(Y), 3, -2, op=api.OP_T)
+    torch.cuda.synchronize()
+    assert np.array_equal(Y.cpu().numpy(), oracle.spmm_wide(trp, tci, tv, X8, 3, -2, Y0))

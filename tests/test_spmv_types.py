@@ -68,9 +68,9 @@ def test_complex_spmv_on_the_gpu(handle, dtype, tol, off):
             torch.cuda.synchronize()
             got = y.cpu().numpy()
             assert np.linalg.norm(got - want) <= tol * np.linalg.norm(want)
-        with pytest.raises(api.AlphaSparseError):      # no transposed product for these instances
+        with pytest.raises(api.AlphaSparseError):      # no conjugate transpose (the transposed copy keeps the values)
             api.spmv(handle, Am, api.DnVec(torch.zeros(A.rows, dtype=y.dtype, device="cuda")),
-                     api.DnVec(torch.zeros(A.cols, dtype=y.dtype, device="cuda")), 1.0, 0.0, op=api.OP_T)
+                     api.DnVec(torch.zeros(A.cols, dtype=y.dtype, device="cuda")), 1.0, 0.0, op=api.OP_C)
 
 
 @pytest.mark.gpu
