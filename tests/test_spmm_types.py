@@ -93,11 +93,11 @@ def test_fp16_conversions_of_the_oracle_match_numpy():
     assert np.array_equal(back[:, 0].view(np.uint16), want.view(np.uint16))
 
 
-def _run(handle, A, v, X, Y0, alpha, beta, ld_pad=0, col_major=False):
+def _run(handle, A, v, X, Y0, alpha, beta, ld_pad=0, col_major=False, off=np.int32):
     from library_b200 import api
     dev = "cuda"
     rp, ci, _ = A.numpy()
-    Am = api.CsrMatrix(A.rows, A.cols, torch.from_numpy(rp).to(dev), torch.from_numpy(ci).to(dev),
+    Am = api.CsrMatrix(A.rows, A.cols, torch.from_numpy(rp.astype(off)).to(dev), torch.from_numpy(ci).to(dev),
                        torch.from_numpy(v).to(dev))
     n = X.shape[1]
     Xt, Yt = torch.from_numpy(X).to(dev), torch.from_numpy(np.array(Y0, copy=True)).to(dev)
@@ -155,6 +155,8 @@ def test_int8_spmm_on_the_gpu(handle):
             Yi = rng.integers(-10**6, 10**6, (A.rows, n)).astype(np.int32)
             for alpha, beta in ((1, 0), (3, -2)):
                 assert np.array_equal(_run(handle, A, v, X, Yi, alpha, beta), oracle.spmm_wide(rp, ci, v, X, alpha, beta, Yi))
+                assert np.array_equal(_run(handle, A, v, X, Yi, alpha, beta, off=np.int64),      # 64-bit row offsets
+                                      oracle.spmm_wide(rp.astype(np.int64), ci, v, X, alpha, beta, Yi))
                 Yf = Yi.astype(np.float32) / 1000
                 got = _run(handle, A, v, X, Yf, float(alpha), float(beta))
                 assert np.array_equal(got, oracle.spmm_wide(rp, ci, v, X, float(alpha), float(beta), Yf))
