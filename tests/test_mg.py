@@ -180,6 +180,34 @@ def _gpu_worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
+def _spawn_bounded(fn, args, nprocs, seconds):
+    """mp.spawn with a limit: ranks that wait for one another in a collective never return by themselves, so a
+    stalled run is ended here (the processes are terminated) and reported as a failure instead of lasting as long
+    as whoever runs the tests lets it."""
+    import time
+    ctx = mp.spawn(fn, args=args, nprocs=nprocs, join=False)
+    deadline = time.monotonic() + seconds
+    while not ctx.join(timeout=5):
+        if time.monotonic() > deadline:
+            for proc in ctx.processes:
+                if proc.is_alive():
+                    proc.terminate()
+            pytest.fail(f"the {nprocs} ranks did not finish within {seconds} s")
+
+
+def _sleep_worker(rank, seconds):
+    import time
+    time.sleep(seconds if rank == 1 else 0.1)
+
+
+def test_a_stalled_multi_rank_run_is_ended():
+    """The limit of _spawn_bounded: ranks that finish pass, a rank that does not come back fails the test after
+    the limit instead of holding it."""
+    _spawn_bounded(_sleep_worker, (0.2,), 2, seconds=60)
+    with pytest.raises(pytest.fail.Exception):
+        _spawn_bounded(_sleep_worker, (600,), 2, seconds=6)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("world", [2, 4])
 def test_every_mode_on_several_gpus_against_the_oracle(tmp_path, world):
@@ -190,7 +218,7 @@ def test_every_mode_on_several_gpus_against_the_oracle(tmp_path, world):
     import oracle
     from conftest import rel_l2
     from library_b200 import generators as G
-    mp.spawn(_gpu_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    _spawn_bounded(_gpu_worker, (world, _free_port(), str(tmp_path)), world, seconds=240)
     for name, (make, dt, tol, (xlo, xhi)) in _cases().items():
         A = make()
         rp, ci, v = A.numpy()
