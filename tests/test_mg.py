@@ -110,6 +110,18 @@ def _cases():
 
 
 def _gpu_worker(rank, world, port, out_dir):
+    """A rank whose check fails leaves at once, without running finalisers: tearing down its communicator would
+    wait for the other ranks, which wait for it in their next collective, and nobody would ever report."""
+    try:
+        _gpu_worker_body(rank, world, port, out_dir)
+    except BaseException:
+        import traceback
+        traceback.print_exc()
+        sys.stderr.flush()
+        os._exit(1)
+
+
+def _gpu_worker_body(rank, world, port, out_dir):
     sys.path.insert(0, ROOT)
     from library_b200 import api
     from library_b200 import generators as G
